@@ -1,0 +1,51 @@
+// Shared device helpers for the sm_100a kernels of this engine.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define CRANE_API extern "C" __attribute__((visibility("default")))
+
+// Bits of the device-side error word.  Kernels never trap: they record what
+// went wrong, skip the access and return; the host reads the word after a step.
+enum CraneErr : int {
+    CRANE_ERR_TOKEN_RANGE = 1,      // token id outside the vocabulary
+    CRANE_ERR_PAGE_RANGE = 2,       // block-table entry outside the page pool
+    CRANE_ERR_POSITION_RANGE = 4,   // position outside the rotary table
+    CRANE_ERR_WAIT_TIMEOUT = 8,     // a bounded mbarrier wait ran out
+    CRANE_ERR_SLOT_RANGE = 16,
+};
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a whole block of up to 1024 threads; every thread gets the result.
+__device__ __forceinline__ float block_sum(float v, float* scratch32) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();                 // scratch may still be read from an earlier call
+    if (lane == 0) scratch32[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarps) ? scratch32[lane] : 0.f;
+    return warp_sum(t);
+}
+
+static inline int crane_launch_status() { return (int)cudaGetLastError(); }

@@ -1,0 +1,264 @@
+// Memory-bound kernels of a decoder step: embedding gather, residual-add +
+// RMSNorm, rotary encoding + per-head RMSNorm + write of K/V into cache pages,
+// SiLU-gated product.  All arithmetic in 32-bit; T is the storage type of
+// activations, weights and cache (float or bf16).  The residual stream itself
+// is always float.
+//
+// Formulas: RMSNorm y = x * rsqrt(mean(x^2) + eps) * w
+// (crane-core/kernels/fused_ops.cu:45-51); SiLU-mul silu(g) * u with
+// silu(x) = x / (1 + exp(-x)) (fused_ops.cu:39-42, 112-130); rotary encoding
+// in the contiguous-halves convention, applied before the per-head norm
+// (crane-core/src/models/hunyuan_dense/modeling.rs:541-555).
+#include "common.cuh"
+
+// A GEMM result is either one tensor of T or `n_parts` float partial sums
+// (split-K), laid out [part][row][col]; readers add the partials in a fixed
+// order and round once to T, so that both forms give the same value.
+template <typename T>
+struct GemmOut {
+    const T* whole;
+    const float* parts;
+    int n_parts;
+    long long part_stride;
+    __device__ __forceinline__ float load(long long idx) const {
+        if (parts == nullptr) return to_f32(whole[idx]);
+        float s = 0.f;
+        for (int i = 0; i < n_parts; ++i) s += parts[(long long)i * part_stride + idx];
+        return to_f32(from_f32<T>(s));
+    }
+};
+
+// ---------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embed_gather_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+                                    float* __restrict__ x, int hidden, int vocab, int* err) {
+    const int t = blockIdx.x;
+    int tok = tokens[t];
+    if (tok < 0 || tok >= vocab) {
+        if (threadIdx.x == 0) atomicOr(err, CRANE_ERR_TOKEN_RANGE);
+        tok = 0;
+    }
+    const T* src = table + (long long)tok * hidden;
+    float* dst = x + (long long)t * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = to_f32(src[c]);
+}
+
+// ------------------------------------------------------ residual + RMSNorm
+// x[row] += delta[row] (if any); out[r] = rmsnorm(x[row]) * w.
+// rows == nullptr: row = r = blockIdx.x, x is updated in place.
+// rows != nullptr: row = rows[r]; x is left untouched (used for the final norm
+// over the wanted positions only).
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, GemmOut<T> delta, int has_delta,
+                                   const float* __restrict__ w, const int* __restrict__ rows,
+                                   T* __restrict__ out, int hidden, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int row = rows ? rows[r] : r;
+    float* xr = x + (long long)row * hidden;
+    const long long dbase = (long long)row * hidden;
+    const bool write_x = (rows == nullptr) && has_delta;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float v = xr[c];
+        if (has_delta) v += delta.load(dbase + c);
+        if (write_x) xr[c] = v;
+        ss += v * v;
+    }
+    const float total = block_sum(ss, scratch);
+    const float rstd = rsqrtf(total / (float)hidden + eps);
+    T* o = out + (long long)r * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float v = xr[c];
+        if (has_delta && !write_x) v += delta.load(dbase + c);
+        o[c] = from_f32<T>(v * rstd * w[c]);
+    }
+}
+
+// ------------------------------------- rotary + per-head norm + cache write
+// One warp per (token, head).  Heads 0..nq-1 are queries, then nkv keys, then
+// nkv values (values are only copied).  `qkv` rows hold [q | k | v]; with
+// has_kv == 0 they hold q alone (a layer that reads another layer's cache).
+template <typename T>
+__global__ void rope_norm_cache_kernel(GemmOut<T> qkv, int qkv_stride,
+                                       const int* __restrict__ positions,
+                                       const int* __restrict__ tok_entry,
+                                       const int* __restrict__ block_table, int max_blocks,
+                                       const float* __restrict__ cos_tab,
+                                       const float* __restrict__ sin_tab, int table_len,
+                                       const float* __restrict__ q_norm_w,
+                                       const float* __restrict__ k_norm_w, float eps,
+                                       T* __restrict__ q_out, T* __restrict__ k_pool,
+                                       T* __restrict__ v_pool, int num_pages, int page_size,
+                                       int n_tokens, int nq, int nkv, int d, int has_kv,
+                                       int rotary, int* err) {
+    const int heads = nq + (has_kv ? 2 * nkv : 0);
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= n_tokens * heads) return;
+    const int t = warp / heads, h = warp % heads;
+    const int pos = positions[t];
+    const int half = d >> 1;
+    const long long src = (long long)t * qkv_stride + (long long)h * d;   // q,k,v are consecutive
+
+    T* dst;
+    const float* nw = nullptr;
+    bool rotate = rotary != 0;
+    if (h < nq) {
+        dst = q_out + ((long long)t * nq + h) * d;
+        nw = q_norm_w;
+    } else {
+        const int e = tok_entry[t];
+        const int page = block_table[(long long)e * max_blocks + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (lane == 0) atomicOr(err, CRANE_ERR_PAGE_RANGE);
+            return;
+        }
+        const bool is_v = h >= nq + nkv;
+        const int g = is_v ? h - nq - nkv : h - nq;
+        T* pool = is_v ? v_pool : k_pool;
+        dst = pool + (((long long)page * nkv + g) * page_size + pos % page_size) * d;
+        if (is_v) {
+            for (int c = lane; c < d; c += 32) dst[c] = from_f32<T>(qkv.load(src + c));
+            return;
+        }
+        nw = k_norm_w;
+    }
+    if (rotate && (pos < 0 || pos >= table_len)) {
+        if (lane == 0) atomicOr(err, CRANE_ERR_POSITION_RANGE);
+        rotate = false;
+    }
+    // each lane owns the pairs (j, j + d/2) for j = lane, lane + 32, ...
+    constexpr int MAXP = 8;                       // d <= 512
+    float a[MAXP], b[MAXP];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXP; ++i) {
+        const int j = lane + 32 * i;
+        a[i] = b[i] = 0.f;
+        if (j < half) {
+            const float x1 = qkv.load(src + j), x2 = qkv.load(src + j + half);
+            if (rotate) {
+                const float c = cos_tab[(long long)pos * half + j];
+                const float s = sin_tab[(long long)pos * half + j];
+                a[i] = x1 * c - x2 * s;
+                b[i] = x2 * c + x1 * s;
+            } else {
+                a[i] = x1;
+                b[i] = x2;
+            }
+            ss += a[i] * a[i] + b[i] * b[i];
+        }
+    }
+    float rstd = 1.f;
+    if (nw != nullptr) {
+        ss = warp_sum(ss);
+        rstd = rsqrtf(ss / (float)d + eps);
+    }
+#pragma unroll
+    for (int i = 0; i < MAXP; ++i) {
+        const int j = lane + 32 * i;
+        if (j < half) {
+            float y1 = a[i], y2 = b[i];
+            if (nw != nullptr) {
+                y1 = y1 * rstd * nw[j];
+                y2 = y2 * rstd * nw[j + half];
+            }
+            dst[j] = from_f32<T>(y1);
+            dst[j + half] = from_f32<T>(y2);
+        }
+    }
+}
+
+// ------------------------------------------------------------ SiLU(g) * u
+// gu rows hold [gate (inter) | up (inter)].
+template <typename T>
+__global__ void silu_mul_kernel(GemmOut<T> gu, T* __restrict__ out, long long n_rows, int inter) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_rows * inter) return;
+    const long long r = i / inter;
+    const int c = (int)(i % inter);
+    const float g = gu.load(r * 2 * inter + c);
+    const float u = gu.load(r * 2 * inter + inter + c);
+    out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
+}
+
+// a T tensor to float (logits of a bf16 head, test helpers)
+template <typename T>
+__global__ void to_float_kernel(const T* __restrict__ in, float* __restrict__ out, long long n) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = to_f32(in[i]);
+}
+
+// ------------------------------------------------------------------ C ABI
+// dtype: 0 = float, 1 = bf16.  Every function returns the CUDA launch status.
+#define DISPATCH_T(dtype, ...)                                   \
+    if ((dtype) == 0) { using T = float; __VA_ARGS__; }          \
+    else { using T = __nv_bfloat16; __VA_ARGS__; }
+
+CRANE_API int crane_embed_gather(int dtype, const int* tokens, const void* table, float* x,
+                                 int n_tokens, int hidden, int vocab, int* err, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    DISPATCH_T(dtype, (embed_gather_kernel<T><<<n_tokens, 256, 0, st>>>(
+        tokens, (const T*)table, x, hidden, vocab, err)));
+    return crane_launch_status();
+}
+
+CRANE_API int crane_add_rmsnorm(int dtype, float* x, const void* delta, const float* delta_parts,
+                                int n_parts, long long part_stride, const float* w,
+                                const int* rows, void* out, int n_rows, int hidden, float eps,
+                                cudaStream_t st) {
+    if (n_rows <= 0) return 0;
+    const int has_delta = (delta != nullptr || delta_parts != nullptr) ? 1 : 0;
+    const int threads = hidden >= 2048 ? 512 : 256;
+    DISPATCH_T(dtype, {
+        GemmOut<T> d{(const T*)delta, delta_parts, n_parts, part_stride};
+        add_rmsnorm_kernel<T><<<n_rows, threads, 0, st>>>(x, d, has_delta, w, rows, (T*)out,
+                                                          hidden, eps);
+    });
+    return crane_launch_status();
+}
+
+CRANE_API int crane_rope_norm_cache(int dtype, const void* qkv, const float* qkv_parts, int n_parts,
+                                    long long part_stride, int qkv_stride, const int* positions,
+                                    const int* tok_entry, const int* block_table, int max_blocks,
+                                    const float* cos_tab, const float* sin_tab, int table_len,
+                                    const float* q_norm_w, const float* k_norm_w, float eps,
+                                    void* q_out, void* k_pool, void* v_pool, int num_pages,
+                                    int page_size, int n_tokens, int nq, int nkv, int d, int has_kv,
+                                    int rotary, int* err, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (d > 512 || (d & 1)) return (int)cudaErrorInvalidValue;
+    const int heads = nq + (has_kv ? 2 * nkv : 0);
+    const long long warps = (long long)n_tokens * heads;
+    const int threads = 128;
+    const int blocks = (int)((warps * 32 + threads - 1) / threads);
+    DISPATCH_T(dtype, {
+        GemmOut<T> src{(const T*)qkv, qkv_parts, n_parts, part_stride};
+        rope_norm_cache_kernel<T><<<blocks, threads, 0, st>>>(
+            src, qkv_stride, positions, tok_entry, block_table, max_blocks, cos_tab, sin_tab,
+            table_len, q_norm_w, k_norm_w, eps, (T*)q_out, (T*)k_pool, (T*)v_pool, num_pages,
+            page_size, n_tokens, nq, nkv, d, has_kv, rotary, err);
+    });
+    return crane_launch_status();
+}
+
+CRANE_API int crane_silu_mul(int dtype, const void* gu, const float* gu_parts, int n_parts,
+                             long long part_stride, void* out, int n_rows, int inter,
+                             cudaStream_t st) {
+    if (n_rows <= 0) return 0;
+    const long long n = (long long)n_rows * inter;
+    const int blocks = (int)((n + 255) / 256);
+    DISPATCH_T(dtype, {
+        GemmOut<T> src{(const T*)gu, gu_parts, n_parts, part_stride};
+        silu_mul_kernel<T><<<blocks, 256, 0, st>>>(src, (T*)out, n_rows, inter);
+    });
+    return crane_launch_status();
+}
+
+CRANE_API int crane_to_float(int dtype, const void* in, float* out, long long n, cudaStream_t st) {
+    if (n <= 0) return 0;
+    const int blocks = (int)((n + 255) / 256);
+    DISPATCH_T(dtype, (to_float_kernel<T><<<blocks, 256, 0, st>>>((const T*)in, out, n)));
+    return crane_launch_status();
+}

@@ -1,0 +1,270 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A batch may hold portions of prompts beside single decoded tokens, cut
+anywhere.  Only the tokens given are run; everything earlier comes from the
+cache.  The reference has two separate calls instead, one whole prompt of one
+sequence (``forward``, crane-core/src/models/hunyuan_dense/modeling.rs:990-1066)
+or one token of each of N sequences (``step_batch_decode``, :1225-1259), and
+copies caches together and apart around the latter (:1150-1210, 1270-1311).
+
+Per step the host builds one block of int32 metadata (token ids, positions,
+the entry of each token, wanted rows, per entry the block-table row of every
+layer group and the state slot), copies it to the device in one transfer and
+runs the model's schedule.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheError, OutOfPages
+from ..cache.pools import CachePools, bytes_per_page, group_layers
+from ..config import EngineConfig, read_config_json, resolve
+from ..config.engine_config import parse_memory_limit
+from ..parts import DecoderModel, Runtime
+from ..weights.loader import open_folder
+from ..weights.safetensors_io import DictSource
+
+
+@dataclass
+class StepEntry:
+    """A request's next tokens in this step and the places among them whose
+    logits are wanted."""
+    request_id: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class StepContext:
+    """What the parts see of a step.  Device tensors are views into buffers
+    whose addresses do not change from step to step."""
+    n_tokens: int
+    n_entries: int
+    n_want: int
+    max_q_len: int
+    max_kv_len: int
+    max_positions: int
+    tokens: torch.Tensor        # int32 [n_tokens]
+    positions: torch.Tensor     # int32 [n_tokens]
+    tok_entry: torch.Tensor     # int32 [n_tokens]  index of the token's entry
+    want_rows: torch.Tensor     # int32 [n_want]    rows whose logits are wanted
+    cu_q: torch.Tensor          # int32 [n_entries + 1]  first row of each entry
+    kv_len: torch.Tensor        # int32 [n_entries]  cached length after this step
+    slots: torch.Tensor         # int32 [n_entries]  state slot of each entry
+    block_tables: List[torch.Tensor]   # per layer group int32 [n_entries, max_blocks]
+    # host copies for parts that plan on the host
+    h_cu_q: np.ndarray
+    h_kv_len: np.ndarray
+    h_slots: np.ndarray
+
+
+class _MetaBuffers:
+    """One pinned host block and one device block with the same fixed layout."""
+
+    def __init__(self, cap_tokens: int, cap_entries: int, max_blocks: List[int], device):
+        self.cap_tokens, self.cap_entries, self.max_blocks = cap_tokens, cap_entries, max_blocks
+        off = 0
+        self.off: Dict[str, int] = {}
+        for name, size in (("tokens", cap_tokens), ("positions", cap_tokens),
+                           ("tok_entry", cap_tokens), ("want_rows", cap_tokens),
+                           ("cu_q", cap_entries + 1), ("kv_len", cap_entries),
+                           ("slots", cap_entries)):
+            self.off[name] = off
+            off += (size + 3) // 4 * 4              # keep every array 16-byte aligned
+        self.bt_off = []
+        for mb in max_blocks:
+            self.bt_off.append(off)
+            off += (cap_entries * mb + 3) // 4 * 4
+        self.total = off
+        self.host = torch.empty(off, dtype=torch.int32).pin_memory()
+        self.np = self.host.numpy()
+        self.dev = torch.zeros(off, dtype=torch.int32, device=device)
+        self.copied = torch.cuda.Event()
+        self.copied.record()
+
+    def view(self, name: str, n: int, device: bool):
+        o = self.off[name]
+        return (self.dev if device else self.np)[o:o + n]
+
+    def table(self, g: int, n: int, device: bool):
+        o, mb = self.bt_off[g], self.max_blocks[g]
+        flat = (self.dev if device else self.np)[o:o + n * mb]
+        return flat.view(n, mb) if device else flat.reshape(n, mb)
+
+
+class ModelRunner:
+    """Owns model, cache and buffers; ``step`` is the one way tokens get through."""
+
+    def __init__(self, model_dir: Optional[str] = None, engine_config: Optional[EngineConfig] = None,
+                 *, config: Optional[dict] = None, tensors=None, model_type: Optional[str] = None):
+        self.cfg = engine_config or EngineConfig()
+        if model_dir is not None:
+            cfg_dict = read_config_json(model_dir)
+            source, where = open_folder(model_dir), model_dir
+        elif config is not None and tensors is not None:
+            cfg_dict, source, where = config, DictSource(tensors), "the given tensors"
+        else:
+            raise ValueError("give a model folder, or a config dict with its tensors")
+        arch = resolve(cfg_dict, model_type)
+        self.model_config = arch.config_from_dict(cfg_dict)
+        self.spec = arch.build_spec(self.model_config)
+        dtype = torch.float32 if self.cfg.dtype == "float32" else torch.bfloat16
+        self.max_seq_len = min(self.cfg.max_seq_len or self.spec.max_positions, self.spec.max_positions)
+        self.cap_tokens = self.cfg.max_batched_tokens
+        self.cap_entries = max(self.cfg.max_concurrent, 1)
+        self.rt = Runtime(self.cfg.device, dtype, self.cfg.workspace_rows or self.cap_tokens)
+        torch.cuda.set_device(self.rt.device)
+        self.model = DecoderModel(self.spec, source, self.rt, where)
+        self._build_cache()
+        self.steps = 0
+
+    # ---- cache geometry -------------------------------------------------
+    def _build_cache(self) -> None:
+        needs = self.model.cache_needs()
+        ps = self.cfg.page_size
+        keys, _ = group_layers(needs)
+        elem = 4 if self.rt.exact else 2
+        per_page = bytes_per_page(needs, ps, elem)
+        full = self.cap_entries * ((self.max_seq_len + ps - 1) // ps)    # every request at the limit
+        if self.cfg.num_pages > 0:
+            pages = self.cfg.num_pages
+        elif self.cfg.max_cache_tokens > 0:
+            pages = (self.cfg.max_cache_tokens + ps - 1) // ps
+        else:
+            free, total = torch.cuda.mem_get_info(self.rt.device)
+            limit = parse_memory_limit(self.cfg.gpu_memory_limit, total)
+            budget = int(free * 0.85)
+            if limit > 0:
+                budget = min(budget, max(0, limit - (total - free)))
+            cost = max(1, sum(per_page))
+            pages = max(1, min(full, budget // cost))
+        self.pools = CachePools(needs, [pages] * len(keys), ps, self.cap_entries, self.rt.dtype,
+                                self.rt.device)
+        self.table = self.pools.table
+        self.max_blocks = [(self.max_seq_len + ps - 1) // ps for _ in keys] or [1]
+        self.meta = _MetaBuffers(self.cap_tokens, self.cap_entries, self.max_blocks if keys else [],
+                                 self.rt.device)
+        self.num_groups = len(keys)
+
+    # ---- requests -------------------------------------------------------
+    def is_live(self, rid: int) -> bool:
+        return self.table.is_live(rid)
+
+    def end(self, rid: int) -> None:
+        """The request is finished: its pages and slot are given back."""
+        self.table.release(rid)
+
+    def length(self, rid: int) -> int:
+        return self.table.length(rid)
+
+    # ---- the step -------------------------------------------------------
+    def prepare(self, entries: Sequence[StepEntry], reserved: bool = False) -> StepContext:
+        """Takes pages for the step's tokens (unless the caller has: ``reserved``)
+        and lays the metadata out on host and device."""
+        n_entries = len(entries)
+        if n_entries == 0:
+            raise ValueError("a step needs at least one entry")
+        if n_entries > self.cap_entries:
+            raise ValueError(f"{n_entries} entries in one step, the engine holds {self.cap_entries}")
+        counts = [len(e.tokens) for e in entries]
+        n_tokens = sum(counts)
+        if min(counts) <= 0:
+            raise ValueError("an entry without tokens")
+        if n_tokens > self.cap_tokens:
+            raise ValueError(f"{n_tokens} tokens in one step exceed max_batched_tokens={self.cap_tokens}")
+        if len({e.request_id for e in entries}) != n_entries:
+            raise ValueError("a request appears twice in one step")
+        vocab = self.spec.vocab_size
+        arrays = []
+        for e, c in zip(entries, counts):
+            t = np.asarray(e.tokens, dtype=np.int64)
+            if t.min() < 0 or t.max() >= vocab:
+                raise ValueError(f"request {e.request_id}: token id outside [0, {vocab})")
+            for w in e.want:
+                if not 0 <= w < c:
+                    raise ValueError(f"request {e.request_id}: wanted place {w} outside its {c} tokens")
+            arrays.append(t)
+        if not reserved:
+            # check everything first, so that a refused step changes nothing
+            ps = self.cfg.page_size
+            need = [0] * self.num_groups
+            new_requests = 0
+            for e, c in zip(entries, counts):
+                live = self.table.is_live(e.request_id)
+                before = self.table.length(e.request_id) if live else 0
+                if before + c > self.max_seq_len:
+                    raise CacheError(f"request {e.request_id} would pass the sequence limit "
+                                     f"{self.max_seq_len}")
+                new_requests += 0 if live else 1
+                for g in range(self.num_groups):
+                    need[g] += (self.table.pages_needed(e.request_id, c, g) if live
+                                else (c + ps - 1) // ps)
+            if new_requests > self.table.free_slots():
+                raise CacheError(f"{new_requests} new requests, {self.table.free_slots()} free slots")
+            for g in range(self.num_groups):
+                if need[g] > self.table.free_pages(g):
+                    raise OutOfPages(f"the step needs {need[g]} pages of group {g}, "
+                                     f"{self.table.free_pages(g)} are free")
+            for e, c in zip(entries, counts):
+                if not self.table.is_live(e.request_id):
+                    self.table.admit(e.request_id)
+                self.table.extend(e.request_id, c)
+        m = self.meta
+        m.copied.synchronize()                      # the last step's copy has left the host block
+        tok = m.view("tokens", n_tokens, False)
+        pos = m.view("positions", n_tokens, False)
+        ent = m.view("tok_entry", n_tokens, False)
+        cu = m.view("cu_q", n_entries + 1, False)
+        kvl = m.view("kv_len", n_entries, False)
+        slots = m.view("slots", n_entries, False)
+        want_rows: List[int] = []
+        row = 0
+        cu[0] = 0
+        for i, (e, c) in enumerate(zip(entries, counts)):
+            after = self.table.length(e.request_id)
+            start = after - c
+            tok[row:row + c] = arrays[i]
+            pos[row:row + c] = np.arange(start, after, dtype=np.int32)
+            ent[row:row + c] = i
+            want_rows.extend(row + w for w in e.want)
+            row += c
+            cu[i + 1] = row
+            kvl[i] = after
+            slots[i] = self.table.slot(e.request_id)
+            for g in range(self.num_groups):
+                self.table.block_table_into(e.request_id, g, m.table(g, n_entries, False)[i])
+        n_want = len(want_rows)
+        if n_want:
+            m.view("want_rows", n_want, False)[:] = np.asarray(want_rows, dtype=np.int32)
+        m.dev.copy_(m.host, non_blocking=True)
+        m.copied.record()
+
+        ctx = StepContext()
+        ctx.n_tokens, ctx.n_entries, ctx.n_want = n_tokens, n_entries, n_want
+        ctx.max_q_len = max(counts)
+        ctx.max_kv_len = int(kvl.max())
+        ctx.max_positions = self.max_seq_len
+        ctx.tokens = m.view("tokens", n_tokens, True)
+        ctx.positions = m.view("positions", n_tokens, True)
+        ctx.tok_entry = m.view("tok_entry", n_tokens, True)
+        ctx.want_rows = m.view("want_rows", n_want, True)
+        ctx.cu_q = m.view("cu_q", n_entries + 1, True)
+        ctx.kv_len = m.view("kv_len", n_entries, True)
+        ctx.slots = m.view("slots", n_entries, True)
+        ctx.block_tables = [m.table(g, n_entries, True) for g in range(self.num_groups)]
+        ctx.h_cu_q = cu.copy()
+        ctx.h_kv_len = kvl.copy()
+        ctx.h_slots = slots.copy()
+        return ctx
+
+    def step(self, entries: Sequence[StepEntry], reserved: bool = False) -> torch.Tensor:
+        """Runs the entries as one batch and returns float logits
+        [number of wanted places, vocab] on the device, in the order of the
+        entries and of their ``want``."""
+        ctx = self.prepare(entries, reserved)
+        logits = self.model.forward(ctx, self.pools.layers)
+        self.steps += 1
+        return logits

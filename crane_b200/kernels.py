@@ -1,0 +1,177 @@
+"""Python face of the CUDA library: one method per kernel, tensors in, tensors out.
+
+Every method launches on torch's current stream of the tensor's device and
+checks the launch status.  There is no other implementation behind these
+methods: if the library cannot be built or loaded, constructing ``Kernels``
+raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional, Union
+
+import torch
+
+from .csrc import build
+
+P, I, L, F = c_void_p, c_int, c_longlong, c_float
+
+_SIGNATURES = {
+    "crane_embed_gather": [I, P, P, P, I, I, I, P, P],
+    "crane_add_rmsnorm": [I, P, P, P, I, L, P, P, P, I, I, F, P],
+    "crane_rope_norm_cache": [I, P, P, I, L, I, P, P, P, I, P, P, I, P, P, F, P, P, P, I, I, I, I,
+                              I, I, I, I, P, P],
+    "crane_silu_mul": [I, P, P, I, L, P, I, I, P],
+    "crane_to_float": [I, P, P, L, P],
+    "crane_gemm_simt": [I, I, P, P, P, P, I, I, I, L, L, L, P],
+    "crane_paged_attention_simt": [I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P],
+    "crane_repetition_penalty": [P, L, I, I, P, I, P, P, P],
+    "crane_sample": [P, L, I, I, P, P, P, P, P, P, P],
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+class Partials:
+    """A matrix product left as ``n`` float partial sums [n, rows, cols] (split
+    along the inner dimension); the consumer adds them up in order."""
+
+    def __init__(self, parts: torch.Tensor):
+        self.parts = parts
+
+    @property
+    def shape(self):
+        return self.parts.shape[1:]
+
+
+Act = Union[torch.Tensor, Partials]
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _dt(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return 0
+    if dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"kernels take float32 or bfloat16 storage, got {dtype}")
+
+
+def _split(a: Act):
+    """(whole ptr, parts ptr, n_parts, part_stride) of a product result."""
+    if isinstance(a, Partials):
+        p = a.parts
+        return None, p.data_ptr(), p.shape[0], p.stride(0)
+    return a.data_ptr(), None, 0, 0
+
+
+class Kernels:
+    def __init__(self) -> None:
+        self.lib = build.load_kernels()
+        for name, sig in _SIGNATURES.items():
+            fn = getattr(self.lib, name)
+            fn.argtypes = sig
+            fn.restype = c_int
+
+    @staticmethod
+    def _stream(t: torch.Tensor) -> int:
+        return torch.cuda.current_stream(t.device).cuda_stream
+
+    @staticmethod
+    def _check(code: int, what: str) -> None:
+        if code != 0:
+            raise KernelError(f"{what}: CUDA error {code}")
+
+    # ---- elementwise ---------------------------------------------------
+    def embed_gather(self, tokens, table, x, err) -> None:
+        n, hidden = x.shape
+        self._check(self.lib.crane_embed_gather(_dt(table.dtype), tokens.data_ptr(), table.data_ptr(),
+                                                x.data_ptr(), n, hidden, table.shape[0],
+                                                err.data_ptr(), self._stream(x)), "embed_gather")
+
+    def add_rmsnorm(self, x, delta: Optional[Act], weight, eps: float, out, rows=None) -> None:
+        """x += delta (if given); out = rmsnorm(x) * weight.  With ``rows`` only
+        those rows of x are read (and x is not written)."""
+        whole, parts, n_parts, stride = (None, None, 0, 0) if delta is None else _split(delta)
+        n_rows = out.shape[0]
+        self._check(self.lib.crane_add_rmsnorm(_dt(out.dtype), x.data_ptr(), whole, parts, n_parts,
+                                               stride, weight.data_ptr(), _ptr(rows), out.data_ptr(),
+                                               n_rows, x.shape[1], float(eps), self._stream(x)),
+                    "add_rmsnorm")
+
+    def rope_norm_cache(self, qkv: Act, qkv_cols: int, dtype, positions, tok_entry, block_table,
+                        cos, sin, q_norm_w, k_norm_w, eps, q_out, k_pool, v_pool, page_size, nq,
+                        nkv, d, has_kv: bool, rotary: bool, err) -> None:
+        whole, parts, n_parts, stride = _split(qkv)
+        n_tokens = q_out.shape[0]
+        num_pages = k_pool.shape[0] if k_pool is not None else 0
+        max_blocks = block_table.shape[1] if block_table is not None else 0
+        self._check(self.lib.crane_rope_norm_cache(
+            _dt(dtype), whole, parts, n_parts, stride, qkv_cols, positions.data_ptr(),
+            _ptr(tok_entry), _ptr(block_table), max_blocks, _ptr(cos), _ptr(sin),
+            cos.shape[0] if cos is not None else 0, _ptr(q_norm_w), _ptr(k_norm_w), float(eps),
+            q_out.data_ptr(), _ptr(k_pool), _ptr(v_pool), num_pages, page_size, n_tokens, nq, nkv,
+            d, 1 if has_kv else 0, 1 if rotary else 0, err.data_ptr(), self._stream(q_out)),
+            "rope_norm_cache")
+
+    def silu_mul(self, gu: Act, out) -> None:
+        whole, parts, n_parts, stride = _split(gu)
+        self._check(self.lib.crane_silu_mul(_dt(out.dtype), whole, parts, n_parts, stride,
+                                            out.data_ptr(), out.shape[0], out.shape[1],
+                                            self._stream(out)), "silu_mul")
+
+    def to_float(self, t, out) -> None:
+        self._check(self.lib.crane_to_float(_dt(t.dtype), t.data_ptr(), out.data_ptr(), t.numel(),
+                                            self._stream(t)), "to_float")
+
+    # ---- matrix product on the FP32 cores ------------------------------
+    def gemm_simt(self, a, w, bias, out) -> None:
+        """out[M,N] = a[M,K] @ w[N,K]^T (+ bias); rows may be strided."""
+        M, K = a.shape
+        N = w.shape[0]
+        assert w.shape[1] == K and out.shape == (M, N)
+        assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+        self._check(self.lib.crane_gemm_simt(_dt(a.dtype), _dt(out.dtype), a.data_ptr(),
+                                             w.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K,
+                                             a.stride(0), w.stride(0), out.stride(0),
+                                             self._stream(a)), "gemm_simt")
+
+    # ---- attention ------------------------------------------------------
+    def paged_attention_simt(self, q, out, k_pool, v_pool, positions, tok_entry, block_table,
+                             page_size, nq, nkv, d, window, scale, err) -> None:
+        self._check(self.lib.crane_paged_attention_simt(
+            _dt(q.dtype), q.data_ptr(), out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+            positions.data_ptr(), tok_entry.data_ptr(), block_table.data_ptr(),
+            block_table.shape[1], k_pool.shape[0], page_size, q.shape[0], nq, nkv, d, int(window),
+            float(scale), err.data_ptr(), self._stream(q)), "paged_attention_simt")
+
+    # ---- sampling -------------------------------------------------------
+    def repetition_penalty(self, logits, context, ctx_len, penalty) -> None:
+        rows, vocab = logits.shape
+        self._check(self.lib.crane_repetition_penalty(
+            logits.data_ptr(), logits.stride(0), rows, vocab, context.data_ptr(), context.stride(0),
+            ctx_len.data_ptr(), penalty.data_ptr(), self._stream(logits)), "repetition_penalty")
+
+    def sample(self, logits, out, temperature=None, top_k=None, top_p=None, seed=None,
+               counter=None) -> None:
+        rows, vocab = logits.shape
+        if temperature is not None and (seed is None or counter is None):
+            raise KernelError("sampling with a temperature needs seed and counter per row")
+        self._check(self.lib.crane_sample(
+            logits.data_ptr(), logits.stride(0), rows, vocab, _ptr(temperature), _ptr(top_k),
+            _ptr(top_p), _ptr(seed), _ptr(counter), out.data_ptr(), self._stream(logits)), "sample")
+
+
+_kernels: Optional[Kernels] = None
+
+
+def get_kernels() -> Kernels:
+    global _kernels
+    if _kernels is None:
+        _kernels = Kernels()
+    return _kernels

@@ -1,0 +1,102 @@
+"""Grouped-query attention over the paged cache.
+
+One product for q, k and v (the three matrices merged, as in the reference,
+crane-core/src/models/hunyuan_dense/modeling.rs:349-365, 516-528); rotary
+encoding of q and k, THEN per-head RMSNorm of q and k with one [d] weight each
+(modeling.rs:541-555); the post-rotary, post-norm k and the raw v go to the
+cache (modeling.rs:557); scores q k^T / sqrt(d), causal, softmax, times v;
+query head h reads kv head h // (nq / nkv) (modeling.rs:572-636); output
+projection (modeling.rs:638-645).  A layer without keys and values of its own
+computes q only and reads the cache it is given (modeling.rs:501-514).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..weights.loader import TensorSpec
+from .base import CacheNeed, Part, build_part, register_part
+
+
+@register_part("mixer", "gqa_attention")
+class GqaAttention(Part):
+    """params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``,
+    ``bias`` (q/k/v/o biases), ``qk_norm`` + ``qk_norm_eps``, ``window`` (0: all
+    earlier positions), ``own_kv`` (False: reads another layer's cache),
+    ``position`` (a PartSpec of kind position, or None), ``scale`` (default
+    1/sqrt(head_dim)).
+    Tensors: ``<prefix>{q,k,v,o}_proj.weight`` (+ ``.bias``),
+    ``<prefix>query_layernorm.weight`` / ``key_layernorm.weight`` [head_dim]."""
+    kind = "mixer"
+
+    @classmethod
+    def manifest(cls, spec):
+        a = spec.params
+        h, nq, nkv, d = a["hidden_size"], a["num_heads"], a["num_kv_heads"], a["head_dim"]
+        p = spec.prefix
+        own = a.get("own_kv", True)
+        m = {p + "q_proj.weight": TensorSpec((nq * d, h)), p + "o_proj.weight": TensorSpec((h, nq * d))}
+        if own:
+            m[p + "k_proj.weight"] = TensorSpec((nkv * d, h))
+            m[p + "v_proj.weight"] = TensorSpec((nkv * d, h))
+        if a.get("bias"):
+            m[p + "q_proj.bias"] = TensorSpec((nq * d,), "float32")
+            m[p + "o_proj.bias"] = TensorSpec((h,), "float32")
+            if own:
+                m[p + "k_proj.bias"] = TensorSpec((nkv * d,), "float32")
+                m[p + "v_proj.bias"] = TensorSpec((nkv * d,), "float32")
+        if a.get("qk_norm"):
+            m[p + "query_layernorm.weight"] = TensorSpec((d,), "float32")
+            if own:
+                m[p + "key_layernorm.weight"] = TensorSpec((d,), "float32")
+        return m
+
+    def load(self, weights, rt):
+        a, p = self.params, self.prefix
+        self.nq, self.nkv, self.d = int(a["num_heads"]), int(a["num_kv_heads"]), int(a["head_dim"])
+        self.own_kv = bool(a.get("own_kv", True))
+        self.window = int(a.get("window") or 0)
+        self.scale = float(a.get("scale") or 1.0 / math.sqrt(self.d))
+        self.eps = float(a.get("qk_norm_eps") or 0.0)
+        if self.nq % self.nkv:
+            raise ValueError(f"{p}: {self.nq} query heads are not a multiple of {self.nkv} kv heads")
+        if self.d % 2 or self.d > 256:
+            raise ValueError(f"{p}: head_dim {self.d} is not supported by the attention kernels "
+                             "(even sizes up to 256)")
+        names = ["q_proj"] + (["k_proj", "v_proj"] if self.own_kv else [])
+        ws = [weights.pop(p + n + ".weight") for n in names]
+        self.qkv_w = torch.cat(ws, dim=0).contiguous() if len(ws) > 1 else ws[0]
+        self.qkv_b = (torch.cat([weights.pop(p + n + ".bias") for n in names]).contiguous()
+                      if a.get("bias") else None)
+        self.o_w = weights[p + "o_proj.weight"]
+        self.o_b = weights.get(p + "o_proj.bias") if a.get("bias") else None
+        self.q_norm = weights.get(p + "query_layernorm.weight") if a.get("qk_norm") else None
+        self.k_norm = weights.get(p + "key_layernorm.weight") if a.get("qk_norm") and self.own_kv else None
+        self.position = build_part(a["position"]) if a.get("position") is not None else None
+        self.qkv_cols = self.qkv_w.shape[0]
+
+    def cache_need(self) -> CacheNeed:
+        if not self.own_kv:
+            return CacheNeed("none")
+        return CacheNeed("kv", kv_heads=self.nkv, head_dim=self.d, window=self.window)
+
+    def forward(self, h, ctx, cache, rt):
+        n = h.shape[0]
+        k = rt.kernels
+        qkv = rt.linear(h, self.qkv_w, self.qkv_b, "attn_qkv")
+        q = rt.ws.get("attn_q", n, self.nq * self.d, rt.dtype)
+        cos = sin = None
+        if self.position is not None:
+            cos, sin = self.position.tables(rt, ctx.max_positions)
+        table = ctx.block_tables[cache.group]
+        k.rope_norm_cache(qkv, self.qkv_cols, rt.dtype, ctx.positions, ctx.tok_entry, table, cos,
+                          sin, self.q_norm, self.k_norm, self.eps, q, cache.k, cache.v,
+                          cache.page_size, self.nq, self.nkv, self.d, self.own_kv,
+                          self.position is not None, rt.err)
+        o = rt.ws.get("attn_o", n, self.nq * self.d, rt.dtype)
+        k.paged_attention_simt(q, o, cache.k, cache.v, ctx.positions, ctx.tok_entry, table,
+                               cache.page_size, self.nq, self.nkv, self.d, self.window, self.scale,
+                               rt.err)
+        rt.launches += 2
+        return rt.linear(o, self.o_w, self.o_b, "attn_out")

@@ -1,0 +1,77 @@
+"""A decoder put together from a ``ModelSpec``: embedding, blocks in the order
+of the schedule, final norm over the wanted rows, head.
+
+Nothing here names an architecture; the reference's counterpart is the
+hard-wired ``HunYuanDenseV1`` (crane-core/src/models/hunyuan_dense/
+modeling.rs:817-867, 990-1066).
+"""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from ..config.spec import ModelSpec
+from ..weights.loader import TensorSpec, load_weights
+from .base import CacheNeed, LayerCache, block_class, build_part, part_class
+
+
+def _block_part_specs(layer_spec):
+    return list(layer_spec.parts.values())
+
+
+def model_manifest(spec: ModelSpec) -> Dict[str, TensorSpec]:
+    """Every tensor the model expects, from the manifests of its parts."""
+    out: Dict[str, TensorSpec] = {}
+    specs = [spec.embed, spec.final_norm, spec.head]
+    for layer in spec.layers:
+        specs.extend(_block_part_specs(layer))
+    for ps in specs:
+        for name, ts in part_class(ps).manifest(ps).items():
+            if name in out and out[name] != ts:
+                raise ValueError(f"tensor {name} is claimed twice with different shapes")
+            out[name] = ts
+    return out
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, source, rt, where: str = "the model folder"):
+        self.spec = spec
+        self.rt = rt
+        weights = load_weights(source, model_manifest(spec), spec.ignored_tensors, rt.dtype,
+                               rt.device, where)
+        self.embed = build_part(spec.embed)
+        self.final_norm = build_part(spec.final_norm)
+        self.head = build_part(spec.head)
+        self.blocks = [block_class(l.block)(l) for l in spec.layers]
+        # the head may share the embedding's tensor, so it loads before any part pops tensors
+        self.embed.load(weights, rt)
+        self.head.load(weights, rt)
+        self.final_norm.load(weights, rt)
+        for b in self.blocks:
+            for part in b.parts():
+                part.load(weights, rt)
+        for step in spec.schedule:
+            if not 0 <= step.layer < len(self.blocks) or not 0 <= step.cache_layer < len(self.blocks):
+                raise ValueError(f"schedule step {step} names a layer that does not exist")
+
+    def cache_needs(self) -> List[CacheNeed]:
+        """Per layer, what its mixer keeps between steps."""
+        return [b.mixer.cache_need() for b in self.blocks]
+
+    def forward(self, ctx, caches: List[LayerCache]) -> torch.Tensor:
+        """Runs the step's tokens through the schedule and returns float logits
+        [wanted rows, vocab] (an empty tensor if nothing is wanted)."""
+        rt = self.rt
+        n = ctx.n_tokens
+        x = rt.ws.get("residual", n, self.spec.hidden_size, torch.float32)
+        self.embed.forward(ctx.tokens, x, rt)
+        pending = None
+        for step in self.spec.schedule:
+            pending = self.blocks[step.layer].forward(x, pending, ctx, caches[step.cache_layer], rt)
+        if ctx.n_want == 0:
+            if pending is not None:
+                pass   # the last block's output only feeds the head
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=rt.device)
+        h = self.final_norm.forward(x, pending, rt, rows=ctx.want_rows, name="final_normed")
+        return self.head.forward(h, rt)

@@ -1,0 +1,78 @@
+"""What parts run with: the device, the model dtype, the kernels, long-lived
+buffers, the device-side error word and the matrix product.
+
+Matrix products: on the true 32-bit path always the FP32-core kernel of this
+package (no tensor cores, so no reduced-precision mode can slip in).  On the
+bfloat16 path the tcgen05 kernel of this package where it takes the shape, and
+otherwise the vendor's library product, which is also what the reference uses
+for every product (Candle's matmul, crane-core/src/models/hunyuan_dense/
+modeling.rs:517-522, 645, 716, 732).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..kernels import Act, KernelError, Partials, get_kernels
+from .base import Workspace
+
+_ERR_NAMES = {1: "a token id outside the vocabulary", 2: "a block-table entry outside the page pool",
+              4: "a position outside the rotary table", 8: "a bounded wait on the device ran out",
+              16: "a state slot outside the pool"}
+
+
+class DeviceFault(RuntimeError):
+    pass
+
+
+class Runtime:
+    def __init__(self, device, dtype: torch.dtype, max_rows: int):
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise KernelError("the engine runs on a CUDA device only; there is no CPU path")
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise KernelError(f"model dtype must be float32 or bfloat16, got {dtype}")
+        self.dtype = dtype
+        self.exact = dtype == torch.float32
+        self.kernels = get_kernels()
+        self.ws = Workspace(self.device, max_rows)
+        self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.max_rows = max_rows
+        self.launches = 0            # kernels of this package launched (a count for reports)
+
+    # ---- device error word ---------------------------------------------
+    def check_errors(self) -> None:
+        """Reads the error word (synchronises) and raises if a kernel set it."""
+        code = int(self.err.item())
+        if code:
+            self.err.zero_()
+            what = [n for bit, n in _ERR_NAMES.items() if code & bit]
+            raise DeviceFault("a kernel reported: " + "; ".join(what or [f"code {code}"]))
+
+    # ---- matrix product -------------------------------------------------
+    def linear(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], name: str,
+               out_dtype: Optional[torch.dtype] = None, cap: Optional[int] = None) -> Act:
+        """x[M,K] @ w[N,K]^T (+ bias[N], float) -> [M,N] in ``out_dtype`` (the
+        model dtype unless stated)."""
+        M, K = x.shape
+        N = w.shape[0]
+        out_dtype = out_dtype or self.dtype
+        out = self.ws.get(name, M, N, out_dtype, cap)
+        if self.exact:
+            self.kernels.gemm_simt(x, w, bias, out)
+            self.launches += 1
+            return out
+        return self._linear_bf16(x, w, bias, out)
+
+    def _linear_bf16(self, x, w, bias, out) -> Act:
+        if out.dtype == torch.bfloat16:
+            torch.mm(x, w.t(), out=out)
+            if bias is not None:
+                out += bias.to(torch.bfloat16)
+            return out
+        # float result from bfloat16 operands: the FP32-core kernel keeps the
+        # float accumulator instead of rounding it to bfloat16 first
+        self.kernels.gemm_simt(x, w, bias, out)
+        self.launches += 1
+        return out

@@ -1,0 +1,38 @@
+"""Tiny Hunyuan Dense configurations for tests.  A and B differ in every size
+and option; C adds what neither has (biases, cross-layer cache sharing, a head
+size that is no power of two).  Weights are drawn wider than a trained model's
+initialisation (std 0.08, not 0.02) so that attention and feed-forward move the
+logits enough for a fault in them to show."""
+
+A = {
+    "architectures": ["HunYuanDenseV1ForCausalLM"], "model_type": "hunyuan_v1_dense",
+    "vocab_size": 256, "hidden_size": 64, "intermediate_size": 128, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16, "hidden_act": "silu",
+    "max_position_embeddings": 128, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+    "use_qk_norm": True, "tie_word_embeddings": True, "attention_bias": False,
+}
+
+B = {
+    "architectures": ["HunYuanDenseV1ForCausalLM"], "model_type": "hunyuan_v1_dense",
+    "vocab_size": 384, "hidden_size": 160, "intermediate_size": 352, "num_hidden_layers": 3,
+    "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 32, "hidden_act": "silu",
+    "max_position_embeddings": 512, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+    "rope_scaling": {"alpha": 1000.0, "type": "dynamic"},
+    "use_qk_norm": False, "tie_word_embeddings": False, "attention_bias": False,
+}
+
+C = {
+    "architectures": ["HunYuanDenseV1ForCausalLM"], "model_type": "hunyuan_v1_dense",
+    "vocab_size": 301, "hidden_size": 96, "intermediate_size": 200, "num_hidden_layers": 4,
+    "num_attention_heads": 6, "num_key_value_heads": 3, "head_dim": 48, "hidden_act": "silu",
+    "max_position_embeddings": 256, "rms_norm_eps": 1e-5, "rope_theta": 50000.0,
+    "rope_scaling": {"alpha": 4.0},
+    "use_qk_norm": True, "tie_word_embeddings": False, "attention_bias": True,
+    "use_cla": True, "cla_share_factor": 2,
+}
+
+TINY = {
+    "A": {"config": A, "seed": 0, "std": 0.08, "norm_std": 0.05, "page_size": 64},
+    "B": {"config": B, "seed": 1, "std": 0.08, "norm_std": 0.05, "page_size": 16},
+    "C": {"config": C, "seed": 2, "std": 0.08, "norm_std": 0.05, "page_size": 32},
+}
