@@ -1,0 +1,124 @@
+"""Choosing the next token from float logits on the device, every row with its
+own options.
+
+What the reference samples with (crane-serve/src/engine/sampling.rs:117-327,
+crane-core/src/models/hunyuan_dense/model.rs:304-339): greedy when no
+temperature is given or it is <= 0; a repetition penalty over the last
+``repeat_last_n`` tokens; temperature via the Gumbel-max trick; top-k (at most
+64 on the device) and top-p inside the top-k set.  All of it runs in the
+kernels of ``csrc/sampling.cu``; only the chosen token ids come back to the host.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+
+@dataclass
+class SamplingParams:
+    temperature: Optional[float] = None     # None or <= 0: greedy
+    top_p: Optional[float] = None           # None, <= 0 or >= 1: off
+    top_k: Optional[int] = None             # None or 0: off; clamped to 64 on the device
+    repetition_penalty: float = 1.0
+    repeat_last_n: int = 64
+    seed: Optional[int] = None              # None: from the clock, as the reference's server does
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature is None or self.temperature <= 0.0
+
+    def resolved_seed(self) -> int:
+        if self.seed is None:
+            self.seed = time.time_ns() & ((1 << 63) - 1)
+        return self.seed
+
+
+class Sampler:
+    def __init__(self, rt, max_rows: int, max_context: int = 64):
+        self.rt = rt
+        self.max_rows = max_rows
+        self.max_context = max_context
+        dev = rt.device
+        self.out = torch.zeros(max_rows, dtype=torch.int32, device=dev)
+        self.out_host = torch.zeros(max_rows, dtype=torch.int32).pin_memory()
+        self._alloc_context(max_context)
+        # per-row options, staged in one pinned block: three 4-byte arrays, two 8-byte arrays
+        r8 = (max_rows + 1) // 2 * 2
+        self._opt_bytes = r8 * 4 * 3 + max_rows * 8 * 2
+        self.h_opts = torch.zeros(self._opt_bytes, dtype=torch.uint8).pin_memory()
+        self.d_opts = torch.zeros(self._opt_bytes, dtype=torch.uint8, device=dev)
+        self._r8 = r8
+
+    def _opt_views(self, buf: torch.Tensor):
+        r8, n = self._r8, self.max_rows
+        a = r8 * 4
+        return (buf[0:a].view(torch.float32), buf[a:2 * a].view(torch.int32),
+                buf[2 * a:3 * a].view(torch.float32), buf[3 * a:3 * a + n * 8].view(torch.int64),
+                buf[3 * a + n * 8:3 * a + n * 16].view(torch.int64))
+
+    def _alloc_context(self, n: int) -> None:
+        self.max_context = n
+        self.h_ctx = torch.zeros((self.max_rows, n), dtype=torch.int32).pin_memory()
+        self.d_ctx = torch.zeros((self.max_rows, n), dtype=torch.int32, device=self.rt.device)
+        self.h_ctx_len = torch.zeros(self.max_rows, dtype=torch.int32).pin_memory()
+        self.d_ctx_len = torch.zeros(self.max_rows, dtype=torch.int32, device=self.rt.device)
+
+    def sample_device(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+                      histories: Optional[Sequence[Sequence[int]]] = None,
+                      counters: Optional[Sequence[int]] = None) -> torch.Tensor:
+        """logits [R, V] float (changed in place by a repetition penalty).
+        ``histories``: per row the request's tokens so far; ``counters``: per row
+        how many tokens the request has sampled before (keys the random
+        stream).  Returns int32 [R] on the device."""
+        rows = logits.shape[0]
+        if rows > self.max_rows:
+            raise ValueError(f"{rows} rows to sample, the sampler holds {self.max_rows}")
+        k = self.rt.kernels
+        out = self.out[:rows]
+        penal = [p.repetition_penalty != 1.0 for p in params]
+        if any(penal):
+            need = max(p.repeat_last_n for p, on in zip(params, penal) if on)
+            if need > self.max_context:
+                self._alloc_context(need)
+            pen = np.ones(rows, dtype=np.float32)
+            ctx, ctx_len = self.h_ctx.numpy(), self.h_ctx_len.numpy()
+            for r, (p, on) in enumerate(zip(params, penal)):
+                ctx_len[r] = 0
+                if on and histories is not None and p.repeat_last_n > 0:
+                    h = list(histories[r])[-p.repeat_last_n:]
+                    ctx[r, :len(h)] = h
+                    ctx_len[r] = len(h)
+                    pen[r] = p.repetition_penalty
+            self.d_ctx[:rows].copy_(self.h_ctx[:rows], non_blocking=True)
+            self.d_ctx_len[:rows].copy_(self.h_ctx_len[:rows], non_blocking=True)
+            d_pen = torch.from_numpy(pen).to(self.rt.device)
+            k.repetition_penalty(logits, self.d_ctx[:rows], self.d_ctx_len[:rows], d_pen)
+            self.rt.launches += 1
+        if all(p.greedy for p in params):
+            k.sample(logits, out)
+            self.rt.launches += 1
+            return out
+        temp, topk, topp, seed, counter = (v.numpy() for v in self._opt_views(self.h_opts))
+        for r, p in enumerate(params):
+            temp[r] = 0.0 if p.greedy else p.temperature
+            topk[r] = p.top_k or 0
+            topp[r] = 1.0 if p.top_p is None else p.top_p
+            seed[r] = p.resolved_seed()
+            counter[r] = counters[r] if counters is not None else 0
+        self.d_opts.copy_(self.h_opts, non_blocking=True)
+        d_temp, d_topk, d_topp, d_seed, d_counter = self._opt_views(self.d_opts)
+        k.sample(logits, out, temperature=d_temp, top_k=d_topk, top_p=d_topp, seed=d_seed,
+                 counter=d_counter)
+        self.rt.launches += 1
+        return out
+
+    def sample(self, logits, params, histories=None, counters=None) -> List[int]:
+        out = self.sample_device(logits, params, histories, counters)
+        n = out.shape[0]
+        self.out_host[:n].copy_(out, non_blocking=True)
+        torch.cuda.current_stream(self.rt.device).synchronize()
+        return self.out_host[:n].tolist()
