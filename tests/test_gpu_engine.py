@@ -1,0 +1,188 @@
+"""The engine above the step function: greedy generation through the Python
+entry point against the plain implementation, batches through the scheduler,
+preemption, long decoding, the first tokens of a sequence, streamers, sampling
+with a seed, and the command line."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_hunyuan as ph
+import tiny_configs
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def load(folder, dtype, **opts):
+    from crane_b200.generation import ModelForCausalLM
+    return ModelForCausalLM.from_pretrained(folder, dtype, **opts)
+
+
+def greedy_cfg(n, **kw):
+    from crane_b200.generation import GenerationConfig
+    return GenerationConfig(max_new_tokens=n, temperature=None, **kw)
+
+
+def assert_greedy_consistent(pc, pw, tokens, prompt_len, rel_tol):
+    """Every generated token is the plain argmax of its prefix, up to `rel_tol`
+    of the logit scale (bfloat16 may pick another of two near-equal logits)."""
+    logits = ph.logits_all(pc, pw, tokens[:-1])
+    for i in range(prompt_len, len(tokens)):
+        row = logits[i - 1]
+        assert row[tokens[i]] >= row.max() - rel_tol * np.abs(row).max(), (i, tokens[i], int(row.argmax()))
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_float32_equals_plain(name, model_folders):
+    folder = model_folders(name, "float32")
+    pc, pw = ph.load_folder(folder)
+    m = load(folder, "fp32", page_size=tiny_configs.TINY[name]["page_size"], num_pages=32,
+             max_concurrent=4, max_batched_tokens=64)
+    rng = np.random.default_rng(3)
+    for n in (1, 5, 17):
+        prompt = rng.integers(0, pc.vocab_size, n).tolist()
+        got = m.generate(prompt, greedy_cfg(8, eos_token_id=-1))
+        assert got == ph.greedy_generate(pc, pw, prompt, 8)
+    m.runner.table.check()
+    assert m.runner.table.live() == 0
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_bfloat16(name, model_folders):
+    folder = model_folders(name, "bfloat16")
+    pc, pw = ph.load_folder(folder)
+    m = load(folder, "bf16", page_size=16, num_pages=32, max_concurrent=4, max_batched_tokens=64)
+    prompt = np.random.default_rng(4).integers(0, pc.vocab_size, 12).tolist()
+    got = m.generate(prompt, greedy_cfg(12, eos_token_id=-1))
+    assert len(got) == 24 and got[:12] == prompt
+    assert_greedy_consistent(pc, pw, got, 12, 3e-2)
+
+
+def test_eos_streamer_and_return_value(model_folders):
+    """EOS ends generation, stays in the returned list, is not streamed; the
+    streamer is finalized exactly once (hunyuan_dense/model.rs:341-370)."""
+    from crane_b200.generation import ListStreamer
+    folder = model_folders("B", "float32")
+    pc, pw = ph.load_folder(folder)
+    m = load(folder, "fp32", page_size=16, num_pages=32, max_concurrent=2, max_batched_tokens=64)
+    prompt = [3, 1, 4, 1, 5]
+    free_run = ph.greedy_generate(pc, pw, prompt, 10)
+    eos = free_run[7]
+    first = free_run.index(eos, 5)
+    s = ListStreamer()
+    got = m.generate(prompt, greedy_cfg(10, eos_token_id=eos), s)
+    assert got == free_run[:first + 1] and s.tokens == free_run[5:first] and s.finalized
+    s2 = ListStreamer()
+    assert m.generate(prompt, greedy_cfg(3, eos_token_id=-1), s2) == free_run[:8]
+    assert s2.tokens == free_run[5:8] and s2.finalized
+
+
+def test_batch_through_the_scheduler_equals_one_by_one(model_folders):
+    folder = model_folders("B", "float32")
+    pc, pw = ph.load_folder(folder)
+    m = load(folder, "fp32", page_size=16, num_pages=64, max_concurrent=4, max_batched_tokens=48,
+             chunk_size=32)
+    rng = np.random.default_rng(5)
+    prompts = [rng.integers(0, pc.vocab_size, n).tolist() for n in (5, 40, 97, 2, 61, 33)]
+    outs = m.generate_batch(prompts, greedy_cfg(9, eos_token_id=-1))
+    for p, o in zip(prompts, outs):
+        assert o == ph.greedy_generate(pc, pw, p, 9)
+    st = m.stats()
+    assert st["finished"] == 6 and st["preemptions"] == 0 and st["kernel_launches"] > 0
+    m.runner.table.check()
+    assert m.runner.table.free_pages() == 64
+
+
+def test_preemption_recomputes_and_output_is_unchanged(model_folders):
+    folder = model_folders("B", "float32")
+    pc, pw = ph.load_folder(folder)
+    # 10 pages of 16 tokens: three requests of ~40 tokens + 30 new cannot all stay
+    m = load(folder, "fp32", page_size=16, num_pages=10, max_concurrent=3, max_batched_tokens=64,
+             chunk_size=32)
+    rng = np.random.default_rng(6)
+    prompts = [rng.integers(0, pc.vocab_size, n).tolist() for n in (40, 38, 35)]
+    outs = m.generate_batch(prompts, greedy_cfg(30, eos_token_id=-1))
+    assert m.stats()["preemptions"] > 0
+    for p, o in zip(prompts, outs):
+        assert len(o) == len(p) + 30
+        assert_greedy_consistent(pc, pw, o, len(p), 1e-4)
+    m.runner.table.check()
+    assert m.runner.table.free_pages() == 10
+
+
+@pytest.mark.parametrize("dtype,tol", [("fp32", 1e-4), ("bf16", 3e-2)])
+def test_long_decoding(dtype, tol, model_folders):
+    folder = model_folders("B", "float32" if dtype == "fp32" else "bfloat16")
+    pc, pw = ph.load_folder(folder)
+    m = load(folder, dtype, page_size=16, num_pages=40, max_concurrent=2, max_batched_tokens=64)
+    got = m.generate([7, 8, 9], greedy_cfg(400, eos_token_id=-1))
+    assert len(got) == 403
+    assert_greedy_consistent(pc, pw, got, 3, tol)
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 3e-2)])
+def test_first_tokens_of_a_sequence(dtype, tol, model_folders):
+    """Positions 0, 1, 2 one token at a time: a sequence's first token has
+    nothing before it."""
+    from crane_b200.config import EngineConfig
+    from crane_b200.engine import ModelRunner, StepEntry
+    folder = model_folders("A", dtype)
+    pc, pw = ph.load_folder(folder)
+    r = ModelRunner(folder, EngineConfig(dtype=dtype, page_size=16, num_pages=4, max_concurrent=2,
+                                         max_batched_tokens=16))
+    toks = [200, 3, 77]
+    want = ph.logits_all(pc, pw, toks)
+    for i, t in enumerate(toks):
+        got = r.step([StepEntry(1, [t], [0])]).cpu().numpy()[0]
+        assert np.abs(got - want[i]).max() / np.abs(want[i]).max() < tol
+    r.end(1)
+    r.rt.check_errors()
+
+
+def test_sampling_with_a_seed_is_reproducible(model_folders):
+    from crane_b200.generation import GenerationConfig
+    folder = model_folders("B", "float32")
+    m = load(folder, "fp32", page_size=16, num_pages=32, max_concurrent=3, max_batched_tokens=128)
+    prompts = [[1, 2, 3, 4, 5], list(range(40)), list(range(97))]      # the workload of tiny config B
+    cfg = GenerationConfig(max_new_tokens=12, temperature=0.8, eos_token_id=-1, seed=1)
+    a = m.generate_batch(prompts, cfg)
+    b = m.generate_batch(prompts, cfg)
+    assert a == b
+    c = m.generate_batch(prompts, GenerationConfig(max_new_tokens=12, temperature=0.8, eos_token_id=-1, seed=2))
+    assert a != c
+    rep = m.generate(prompts[0], GenerationConfig(max_new_tokens=12, temperature=0.8, top_p=0.9, top_k=20,
+                                                  repetition_penalty=1.3, repeat_last_n=8,
+                                                  eos_token_id=-1, seed=1))
+    assert len(rep) == 17
+
+
+def test_refusals(model_folders):
+    folder = model_folders("A", "float32")
+    m = load(folder, "fp32", page_size=16, num_pages=16, max_concurrent=2, max_batched_tokens=64)
+    with pytest.raises(ValueError, match="refused"):
+        m.generate(list(range(129)), greedy_cfg(1))            # longer than max_position_embeddings
+    with pytest.raises(ValueError, match="token id"):
+        m.generate([1, 999], greedy_cfg(1))
+    assert m.generate([1, 2], greedy_cfg(200, eos_token_id=-1))[:2] == [1, 2]   # clamped to the limit
+    assert m.runner.table.live() == 0
+
+
+def test_command_line(model_folders):
+    folder = model_folders("A", "float32")
+    pc, pw = ph.load_folder(folder)
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "crane"), "-m", folder, "--dtype", "fp32",
+           "--prompt-ids", "5,6,7", "--max-new-tokens", "6", "--eos-token-id", "-1", "--page-size", "16",
+           "--num-pages", "8", "-c", "2", "--max-batched-tokens", "32"]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr[-3000:]
+    want = ph.greedy_generate(pc, pw, [5, 6, 7], 6)[3:]
+    assert p.stdout.strip().splitlines()[-1] == ",".join(map(str, want))
+    # random weights from the folder's config.json alone
+    p = subprocess.run(cmd + ["--random-weights", "--seed", "3"], capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr[-3000:]
+    assert len(p.stdout.strip().splitlines()[-1].split(",")) == 6

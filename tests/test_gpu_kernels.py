@@ -1,0 +1,311 @@
+"""Each kernel alone against a plain float64 computation of the same formula,
+at sizes other than the tiny models': odd widths, head sizes in steps of 16,
+vocabularies that are no power of two."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_hunyuan as ph
+from gpu_helpers import DEV, attention_reference, paged_cache, rel_err
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+TOL = {torch.float32: 2e-6, torch.bfloat16: 1e-2}
+
+
+@pytest.fixture(scope="module")
+def K():
+    from crane_b200.kernels import get_kernels
+    return get_kernels()
+
+
+@pytest.fixture()
+def err():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,vocab", [(100, 301), (2048, 1000)])
+def test_embed_gather(K, err, dtype, hidden, vocab):
+    table = torch.randn(vocab, hidden, device=DEV).to(dtype)
+    tokens = torch.tensor([0, vocab - 1, 5, 5, 17], dtype=torch.int32, device=DEV)
+    x = torch.zeros(5, hidden, device=DEV)
+    K.embed_gather(tokens, table, x, err)
+    assert torch.equal(x, table[tokens.long()].float()) and int(err.item()) == 0
+    bad = torch.tensor([vocab], dtype=torch.int32, device=DEV)
+    K.embed_gather(bad, table, x[:1], err)
+    assert int(err.item()) == 1                      # reported, not read
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [96, 2048, 4100])
+def test_add_rmsnorm(K, dtype, hidden):
+    n, eps = 7, 1e-5
+    x = torch.randn(n, hidden, device=DEV)
+    delta = torch.randn(n, hidden, device=DEV).to(dtype)
+    w = 1 + 0.1 * torch.randn(hidden, device=DEV)
+    want_x = x.double() + delta.double()
+    want = torch.from_numpy(ph.rms_norm(want_x.cpu().numpy(), w.double().cpu().numpy(), eps))
+    out = torch.empty(n, hidden, device=DEV, dtype=dtype)
+    x1 = x.clone()
+    K.add_rmsnorm(x1, delta, w, eps, out)
+    assert rel_err(x1.cpu(), want_x.cpu()) < 1e-6          # the residual itself stays float
+    assert rel_err(out.cpu(), want) < TOL[dtype]
+    # norm only
+    K.add_rmsnorm(x.clone(), None, w, eps, out)
+    assert rel_err(out.cpu(), torch.from_numpy(ph.rms_norm(x.double().cpu().numpy(), w.double().cpu().numpy(), eps))) < TOL[dtype]
+    # chosen rows: x must stay as it was
+    rows = torch.tensor([5, 0, 5], dtype=torch.int32, device=DEV)
+    x2 = x.clone()
+    out3 = torch.empty(3, hidden, device=DEV, dtype=dtype)
+    K.add_rmsnorm(x2, delta, w, eps, out3, rows)
+    assert torch.equal(x2, x) and rel_err(out3.cpu(), want[[5, 0, 5]]) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_add_rmsnorm_from_partial_sums(K, dtype):
+    from crane_b200.kernels import Partials
+    n, hidden = 5, 300
+    x = torch.randn(n, hidden, device=DEV)
+    parts = torch.randn(3, n, hidden, device=DEV)
+    w = torch.ones(hidden, device=DEV)
+    whole = parts.sum(0).to(dtype)
+    a, b = torch.empty(n, hidden, device=DEV, dtype=dtype), torch.empty(n, hidden, device=DEV, dtype=dtype)
+    xa, xb = x.clone(), x.clone()
+    K.add_rmsnorm(xa, Partials(parts), w, 1e-6, a)
+    K.add_rmsnorm(xb, whole, w, 1e-6, b)
+    assert rel_err(a, b.float()) < TOL[dtype] and rel_err(xa, xb) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(K, dtype):
+    n, inter = 9, 353
+    gu = (3 * torch.randn(n, 2 * inter, device=DEV)).to(dtype)
+    out = torch.empty(n, inter, device=DEV, dtype=dtype)
+    K.silu_mul(gu, out)
+    g, u = gu[:, :inter].double().cpu().numpy(), gu[:, inter:].double().cpu().numpy()
+    assert rel_err(out.cpu(), torch.from_numpy(ph.silu(g) * u)) < TOL[dtype]
+
+
+@pytest.mark.parametrize("in_dtype,out_dtype", [(torch.float32, torch.float32),
+                                                 (torch.bfloat16, torch.bfloat16),
+                                                 (torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("M,N,K_", [(1, 301, 100), (37, 129, 352), (130, 64, 2048)])
+def test_gemm_simt(K, in_dtype, out_dtype, M, N, K_):
+    a = torch.randn(M, K_, device=DEV).to(in_dtype)
+    w = torch.randn(N, K_, device=DEV).to(in_dtype)
+    bias = torch.randn(N, device=DEV)
+    out = torch.empty(M, N, device=DEV, dtype=out_dtype)
+    K.gemm_simt(a, w, bias, out)
+    want = a.double() @ w.double().T + bias.double()
+    assert rel_err(out, want) < (3e-6 if out_dtype == torch.float32 else 1e-2)
+    K.gemm_simt(a, w, None, out)
+    assert rel_err(out, a.double() @ w.double().T) < (3e-6 if out_dtype == torch.float32 else 1e-2)
+
+
+def test_gemm_simt_row_does_not_depend_on_the_batch(K):
+    a = torch.randn(70, 333, device=DEV)
+    w = torch.randn(150, 333, device=DEV)
+    big, one = torch.empty(70, 150, device=DEV), torch.empty(1, 150, device=DEV)
+    K.gemm_simt(a, w, None, big)
+    K.gemm_simt(a[66:67], w, None, one)
+    assert torch.equal(big[66:67], one)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d,nq,nkv,qk_norm", [(16, 4, 2, True), (48, 6, 3, False), (128, 8, 2, True),
+                                              (80, 5, 5, True)])
+def test_rope_norm_cache(K, err, dtype, d, nq, nkv, qk_norm):
+    page_size, n_tok, eps = 8, 13, 1e-5
+    starts = [0, 21]                      # entry 0: positions 0..5; entry 1: positions 21..27
+    counts = [6, 7]
+    positions = torch.tensor(list(range(0, 6)) + list(range(21, 28)), dtype=torch.int32)
+    tok_entry = torch.tensor([0] * 6 + [1] * 7, dtype=torch.int32)
+    cols = (nq + 2 * nkv) * d
+    qkv = torch.randn(n_tok, cols, device=DEV).to(dtype)
+    table = torch.tensor([[3, -1, -1, -1], [7, 1, 5, 0]], dtype=torch.int32, device=DEV)
+    k_pool = torch.zeros(9, nkv, page_size, d, device=DEV, dtype=dtype)
+    v_pool = torch.zeros_like(k_pool)
+    inv = ph.rope_inv_freq(d, 10000.0, 7.0)
+    ang = ph.rope_angles(np.arange(64), inv)
+    cos = torch.from_numpy(np.cos(ang.astype(np.float64)).astype(np.float32)).to(DEV)
+    sin = torch.from_numpy(np.sin(ang.astype(np.float64)).astype(np.float32)).to(DEV)
+    qw = (1 + 0.1 * torch.randn(d)).to(DEV) if qk_norm else None
+    kw = (1 + 0.1 * torch.randn(d)).to(DEV) if qk_norm else None
+    q_out = torch.empty(n_tok, nq * d, device=DEV, dtype=dtype)
+    K.rope_norm_cache(qkv, cols, dtype, positions.to(DEV), tok_entry.to(DEV), table, cos, sin, qw, kw,
+                      eps, q_out, k_pool, v_pool, page_size, nq, nkv, d, True, True, err)
+    assert int(err.item()) == 0
+    x = qkv.double().cpu().numpy()
+    q = x[:, :nq * d].reshape(n_tok, nq, d)
+    k = x[:, nq * d:(nq + nkv) * d].reshape(n_tok, nkv, d)
+    v = x[:, (nq + nkv) * d:].reshape(n_tok, nkv, d)
+    a = ph.rope_angles(positions.numpy(), inv)
+    q, k = ph.apply_rope(q, a), ph.apply_rope(k, a)
+    if qk_norm:
+        q = ph.rms_norm(q, qw.double().cpu().numpy(), eps)
+        k = ph.rms_norm(k, kw.double().cpu().numpy(), eps)
+    assert rel_err(q_out.cpu().view(n_tok, nq, d), torch.from_numpy(q)) < TOL[dtype]
+    for t in range(n_tok):
+        p, e = int(positions[t]), int(tok_entry[t])
+        page, off = int(table[e, p // page_size]), p % page_size
+        assert rel_err(k_pool[page, :, off].cpu(), torch.from_numpy(k[t])) < TOL[dtype]
+        assert rel_err(v_pool[page, :, off].cpu(), torch.from_numpy(v[t])) < TOL[dtype]
+    # nothing else was written: 13 tokens' worth of non-zero rows
+    assert int((k_pool.float().abs().sum(-1) > 0).sum()) == n_tok * nkv
+    # a block-table entry outside the pool is reported, not followed
+    bad = table.clone(); bad[0, 0] = 99
+    K.rope_norm_cache(qkv, cols, dtype, positions.to(DEV), tok_entry.to(DEV), bad, cos, sin, qw, kw,
+                      eps, q_out, k_pool, v_pool, page_size, nq, nkv, d, True, True, err)
+    assert int(err.item()) & 2
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d,nq,nkv,page_size,window", [(16, 4, 2, 16, 0), (48, 6, 2, 8, 0),
+                                                        (128, 8, 2, 64, 0), (32, 4, 4, 16, 37),
+                                                        (256, 2, 1, 32, 0)])
+def test_paged_attention_mixed_batch(K, err, dtype, d, nq, nkv, page_size, window):
+    """Three requests: a prompt portion that starts in the middle of a page, a
+    single decoded token far into a long context, and a whole short prompt."""
+    torch.manual_seed(d + window)
+    lens = [150, 333, 9]                   # cached length after the step
+    q_lens = [45, 1, 9]
+    ks = [torch.randn(n, nkv, d) for n in lens]
+    vs = [torch.randn(n, nkv, d) for n in lens]
+    # a far key that must dominate: request 1's token reads position 17 of 333
+    qs = [torch.randn(ql, nq, d) for ql in q_lens]
+    ks[1][17] *= 0.0
+    ks[1][17, :, 0] = 40.0
+    qs[1][0, :, 0] = 8.0 / (d ** -0.5) / 40.0 + 3.0         # score(17) stands out by far
+    if dtype == torch.bfloat16:
+        ks = [k.bfloat16().float() for k in ks]; vs = [v.bfloat16().float() for v in vs]
+        qs = [q.bfloat16().float() for q in qs]
+    k_pool, v_pool, table = paged_cache(ks, vs, page_size, dtype)
+    positions, tok_entry = [], []
+    for e, (n, ql) in enumerate(zip(lens, q_lens)):
+        positions += list(range(n - ql, n)); tok_entry += [e] * ql
+    q = torch.cat(qs).to(DEV).to(dtype).reshape(-1, nq * d)
+    out = torch.empty_like(q)
+    K.paged_attention_simt(q, out, k_pool, v_pool, torch.tensor(positions, dtype=torch.int32, device=DEV),
+                           torch.tensor(tok_entry, dtype=torch.int32, device=DEV), table, page_size,
+                           nq, nkv, d, window, d ** -0.5, err)
+    assert int(err.item()) == 0
+    row = 0
+    for e, (n, ql) in enumerate(zip(lens, q_lens)):
+        for i in range(ql):
+            want = attention_reference(qs[e][i], ks[e], vs[e], n - ql + i, window)
+            got = out[row].cpu().view(nq, d)
+            assert rel_err(got, want) < (3e-6 if dtype == torch.float32 else 1.5e-2), (e, i)
+            row += 1
+    if window == 0:
+        far = out[45].cpu().view(nq, d).double()
+        assert rel_err(far[0], vs[1][17, 0].double()) < 2e-2       # the far key's value came through
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_window_edge(K, err, dtype):
+    """The key at position p - window must not be read, the one at p - window + 1 must."""
+    d, nq, nkv, ps, window, n = 32, 2, 1, 16, 24, 100
+    k = torch.zeros(n, nkv, d); v = torch.zeros(n, nkv, d)
+    k[:, 0, 0] = 1.0
+    v[:, 0, 0] = torch.arange(n).float()
+    k[n - 1 - window, 0, 0] = 30.0        # just outside: would win if read
+    k[n - window, 0, 0] = 5.0             # just inside
+    q = torch.zeros(1, nq, d); q[..., 0] = 4.0 * d ** 0.5
+    k_pool, v_pool, table = paged_cache([k], [v], ps, dtype)
+    out = torch.empty(1, nq * d, device=DEV, dtype=dtype)
+    K.paged_attention_simt(q.to(DEV).to(dtype).reshape(1, -1), out, k_pool, v_pool,
+                           torch.tensor([n - 1], dtype=torch.int32, device=DEV),
+                           torch.zeros(1, dtype=torch.int32, device=DEV), table, ps, nq, nkv, d,
+                           window, d ** -0.5, err)
+    want = attention_reference(q[0], k, v, n - 1, window)
+    assert rel_err(out.cpu().view(nq, d), want) < (3e-6 if dtype == torch.float32 else 1.5e-2)
+    assert abs(float(out[0, 0]) - (n - window)) < 1.0
+
+
+def test_argmax_ties_go_to_the_lowest_index(K):
+    vocab = 120818
+    logits = torch.randn(3, vocab, device=DEV)
+    logits[0, 77777] = 50.0; logits[0, 1234] = 50.0
+    logits[1, vocab - 1] = 60.0
+    logits[2, :] = -1.0                                   # all equal
+    out = torch.zeros(3, dtype=torch.int32, device=DEV)
+    K.sample(logits, out)
+    assert out.tolist() == [1234, vocab - 1, 0]
+
+
+def test_repetition_penalty(K):
+    vocab = 1000
+    logits = torch.randn(2, vocab, device=DEV)
+    want = logits.clone()
+    ctx = torch.tensor([[5, 7, 5, 999, 0], [1, 2, 3, 4, 5]], dtype=torch.int32, device=DEV)
+    ctx_len = torch.tensor([4, 0], dtype=torch.int32, device=DEV)
+    pen = torch.tensor([1.3, 2.0], device=DEV)
+    K.repetition_penalty(logits, ctx, ctx_len, pen)
+    row = ph.apply_repetition_penalty(want[0].double().cpu().numpy(), 1.3, [5, 7, 5, 999])
+    assert rel_err(logits[0].cpu(), torch.from_numpy(row)) < 1e-6
+    assert torch.equal(logits[1], want[1])                # no context: untouched
+
+
+def _host_opts(temp, topk, topp, seed, counter):
+    t = lambda v, dt: torch.tensor(v, dtype=dt, device=DEV)
+    return dict(temperature=t(temp, torch.float32), top_k=t(topk, torch.int32),
+                top_p=t(topp, torch.float32), seed=t(seed, torch.int64), counter=t(counter, torch.int64))
+
+
+def test_temperature_sampling_matches_the_restated_generator(K):
+    vocab = 3001
+    logits = 3 * torch.randn(4, vocab, device=DEV)
+    out = torch.zeros(4, dtype=torch.int32, device=DEV)
+    temps, seeds, counters = [0.8, 1.0, 0.0, 2.5], [1024, 7, 7, 99], [0, 5, 5, 123456]
+    K.sample(logits, out, **_host_opts(temps, [0] * 4, [1.0] * 4, seeds, counters))
+    for r in range(4):
+        row = logits[r].double().cpu().numpy()
+        if temps[r] <= 0:
+            assert int(out[r]) == int(np.argmax(row))
+            continue
+        score = ph.gumbel_scores(row, temps[r], ph.uniform_noise(seeds[r], counters[r], vocab))
+        # float32 logs on the device: the chosen token's score must be the maximum up to rounding
+        assert score[int(out[r])] >= score.max() - 1e-4
+    again = torch.zeros_like(out)
+    K.sample(logits, again, **_host_opts(temps, [0] * 4, [1.0] * 4, seeds, counters))
+    assert torch.equal(out, again)
+    K.sample(logits, again, **_host_opts(temps, [0] * 4, [1.0] * 4, seeds, [c + 1 for c in counters]))
+    assert not torch.equal(out, again)
+
+
+def test_top_k_and_top_p(K):
+    vocab = 5003
+    logits = torch.randn(1, vocab, device=DEV)
+    best = [4000, 17, 2500, 901]
+    for i, b in enumerate(best):
+        logits[0, b] = 10.0 - i                     # probabilities ~ .64 .24 .09 .03 among the top 4
+    row = logits[0].double().cpu().numpy()
+    seen_k, seen_p = set(), set()
+    out = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for c in range(300):
+        K.sample(logits, out, **_host_opts([1.0], [3], [1.0], [5], [c]))
+        seen_k.add(int(out[0]))
+        K.sample(logits, out, **_host_opts([1.0], [0], [0.7], [5], [c]))
+        seen_p.add(int(out[0]))
+    assert seen_k == set(best[:3])                                   # never outside the top 3
+    keep = ph.top_k_top_p_keep(row, 1.0, 64, 0.7)
+    assert seen_p == set(int(i) for i in keep) == set(best[:2])      # .64 <= .7, plus the one after
+
+
+def test_sampling_frequencies_follow_the_softmax(K):
+    vocab = 7
+    logits = torch.tensor([[0.0, 1.0, 2.0, -1.0, 0.5, 1.5, -3.0]], device=DEV)
+    p = torch.softmax(logits[0] / 0.9, 0).cpu().numpy()
+    n = 4000
+    counts = np.zeros(vocab)
+    out = torch.zeros(1, dtype=torch.int32, device=DEV)
+    big = logits.repeat(n, 1)
+    outs = torch.zeros(n, dtype=torch.int32, device=DEV)
+    K.sample(big, outs, **_host_opts([0.9] * n, [0] * n, [1.0] * n, [11] * n, list(range(n))))
+    counts = np.bincount(outs.cpu().numpy(), minlength=vocab) / n
+    # u is drawn from [1e-7, 0.999), as in the reference, which trims the upper tail a little
+    assert np.abs(counts - p).max() < 0.03
