@@ -31,14 +31,15 @@ class LayerSpec:
 
 @dataclass
 class ScheduleStep:
-    """Run layer ``layer``; its mixer reads and writes the cache of layer
-    ``cache_of`` (its own unless stated).  A layer may appear more than once."""
+    """Run layer ``layer``.  Every step of the schedule has a cache of its own
+    (so a layer that is named twice keeps two), unless ``cache_of`` names the
+    step (by its place in the schedule) whose cache this one reads instead; a
+    step that reads another's cache writes none."""
     layer: int
     cache_of: Optional[int] = None
 
-    @property
-    def cache_layer(self) -> int:
-        return self.layer if self.cache_of is None else self.cache_of
+    def cache_step(self, own_place: int) -> int:
+        return own_place if self.cache_of is None else self.cache_of
 
 
 @dataclass

@@ -1,0 +1,386 @@
+// bf16 matrix product on the 5th-generation tensor cores of sm_100a:
+//   D[a, b] = sum_k A[a, k] * B[b, k]        A [rows_a, K], B [rows_b, K], both K-contiguous
+// Operands travel global -> shared memory by TMA (128-byte swizzle), the
+// product is issued by one thread as tcgen05.mma with the float accumulator in
+// tensor memory, and four warps read the accumulator back with tcgen05.ld for
+// the epilogue.  One CTA computes one 128 x BN tile over one slice of K.
+//
+// Two ways to use it for y = x W^T (crane-core/src/models/hunyuan_dense/
+// modeling.rs:273-330: weights are [out, in]):
+//   * many tokens:  A = x, B = W, BN = 128 or 256, output row-major [token, feature];
+//   * few tokens:   A = W, B = x ("swap-AB": the 128-wide side of the MMA is
+//     filled by weight rows, the narrow side holds 16..64 tokens), output
+//     written transposed so that it is again [token, feature].
+// With split_k > 1 every slice writes its float partial sums [slice][row][col]
+// and the consumer adds them (see GemmOut in elementwise.cu).
+//
+// Every wait on an mbarrier is bounded: when it runs out the kernel records
+// CRANE_ERR_WAIT_TIMEOUT, all roles leave their loops, tensor memory is freed
+// and the kernel returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;          // rows of A per tile = MMA M
+constexpr int BK = 64;           // bf16 elements per k-block = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192; // warp 0: TMA, warp 1: MMA + tensor memory, warps 2..5: epilogue
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (and raises the CTA's abort flag) when it gives up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+// K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle:
+// groups of 8 rows are 1024 bytes apart (stride byte offset), leading byte
+// offset 1 (unused for swizzled K-major), descriptor version 1, layout 2.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// kind::f16, bf16 x bf16 -> f32, both operands K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t instr_desc_bf16(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+struct GemmParams {
+    int rows_a, rows_b, k;          // extents
+    int kb_per_split;               // k-blocks per slice
+    void* out;                      // bf16 or float, see template flags
+    long long ld_out;               // elements between consecutive rows of the output
+    long long split_stride;         // elements between consecutive slices (split_k > 1)
+    const float* bias;              // over the feature dimension, or null
+    int* err;
+};
+
+// OUT_F32: float output (else bf16).  TRANSPOSED: element (a, b) goes to out[b * ld + a].
+template <int BN, int STAGES, bool OUT_F32, bool TRANSPOSED>
+__global__ void __launch_bounds__(NUM_THREADS)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const GemmParams p) {
+    constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // 1024-byte alignment is what the 128-byte swizzle pattern is anchored to
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + STAGES * A_BYTES;
+    uint64_t* bars = (uint64_t*)(smem + STAGES * (A_BYTES + B_BYTES));
+    uint64_t* full = bars;                    // [STAGES] operands of a stage have landed
+    uint64_t* empty = bars + STAGES;          // [STAGES] the MMAs that read a stage are done
+    uint64_t* acc_ready = bars + 2 * STAGES;  // the whole accumulator is done
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int a0 = blockIdx.x * BM, b0 = blockIdx.y * BN;
+    const int num_kb_total = (p.k + BK - 1) / BK;
+    const int kb_begin = blockIdx.z * p.kb_per_split;
+    const int kb_end = min(num_kb_total, kb_begin + p.kb_per_split);
+    const int num_kb = max(0, kb_end - kb_begin);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&full[s]), 1);
+            mbar_init(smem_u32(&empty[s]), 1);
+        }
+        mbar_init(smem_u32(acc_ready), 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(tmem_slot)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer ----------------
+        for (int i = 0; i < num_kb; ++i) {
+            const int s = i % STAGES;
+            const uint32_t parity = ((i / STAGES) & 1) ^ 1;
+            if (!mbar_wait(smem_u32(&empty[s]), parity, abort_flag)) break;
+            const uint32_t bar = smem_u32(&full[s]);
+            mbar_expect_tx(bar, A_BYTES + B_BYTES);
+            const int k0 = (kb_begin + i) * BK;
+            tma_load_2d(smem_u32(smem_a + s * A_BYTES), &map_a, bar, k0, a0);
+            tma_load_2d(smem_u32(smem_b + s * B_BYTES), &map_b, bar, k0, b0);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer ----------------
+        const uint32_t idesc = instr_desc_bf16(BN);
+        for (int i = 0; i < num_kb; ++i) {
+            const int s = i % STAGES;
+            if (!mbar_wait(smem_u32(&full[s]), (i / STAGES) & 1, abort_flag)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t da = smem_desc_sw128(smem_u32(smem_a + s * A_BYTES));
+            const uint64_t db = smem_desc_sw128(smem_u32(smem_b + s * B_BYTES));
+#pragma unroll
+            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                // 16 elements further along K: 32 bytes, 2 in descriptor units of 16 bytes
+                umma_bf16(tmem_base, da + 2 * kk, db + 2 * kk, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+            }
+            umma_commit(smem_u32(&empty[s]));
+        }
+        umma_commit(smem_u32(acc_ready));
+    } else if (warp >= 2) {
+        // ---------------- epilogue ----------------
+        // a warp may touch the 32 lanes of tensor memory given by its index modulo 4
+        const int quarter = warp & 3;
+        const bool ok = num_kb == 0 || mbar_wait(smem_u32(acc_ready), 0, abort_flag);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int a = a0 + quarter * 32 + lane;            // this thread's row of A
+        const bool split = gridDim.z > 1;
+        const bool with_bias = p.bias != nullptr && blockIdx.z == 0;
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                uint32_t r[16];
+                if (num_kb > 0) {
+                    tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[j] = 0u;
+                }
+                if (a >= p.rows_a) continue;
+                if (!TRANSPOSED && !split && b0 + c0 + 16 <= p.rows_b) {
+                    // 16 consecutive features of one token: whole 16-byte stores when aligned
+                    float v[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        v[j] = __uint_as_float(r[j]);
+                        if (with_bias) v[j] += p.bias[b0 + c0 + j];
+                    }
+                    const long long idx = (long long)a * p.ld_out + b0 + c0;
+                    if (OUT_F32) {
+                        float* dst = (float*)p.out + idx;
+                        if (((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 16; j += 4)
+                                *(float4*)(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) dst[j] = v[j];
+                        }
+                    } else {
+                        __nv_bfloat16* dst = (__nv_bfloat16*)p.out + idx;
+                        if (((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 16; j += 8) {
+                                uint4 w;
+                                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+                                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+                                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                                w.x = *(uint32_t*)&h0; w.y = *(uint32_t*)&h1;
+                                w.z = *(uint32_t*)&h2; w.w = *(uint32_t*)&h3;
+                                *(uint4*)(dst + j) = w;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) dst[j] = __float2bfloat16_rn(v[j]);
+                        }
+                    }
+                    continue;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int b = b0 + c0 + j;
+                    if (b >= p.rows_b) break;
+                    float v = __uint_as_float(r[j]);
+                    const int feature = TRANSPOSED ? a : b;
+                    if (with_bias) v += p.bias[feature];
+                    const long long idx = TRANSPOSED ? (long long)b * p.ld_out + a
+                                                     : (long long)a * p.ld_out + b;
+                    if (split)
+                        ((float*)p.out)[(long long)blockIdx.z * p.split_stride + idx] = v;
+                    else if (OUT_F32)
+                        ((float*)p.out)[idx] = v;
+                    else
+                        ((__nv_bfloat16*)p.out)[idx] = __float2bfloat16_rn(v);
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicOr(p.err, CRANE_ERR_WAIT_TIMEOUT);
+        // copies that were issued may still be landing: give them time before the CTA ends
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        fn = (EncodeTiledFn)sym;
+    }
+    return fn;
+}
+
+// [rows, k] bf16, k contiguous, `ld` elements between rows; box of 64 x box_rows.
+bool make_map(CUtensorMap* map, const void* ptr, int rows, int k, long long ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
+              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES, bool OUT_F32, bool TRANSPOSED>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid,
+           cudaStream_t st) {
+    constexpr size_t smem = STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
+    auto kern = gemm_bf16_kernel<BN, STAGES, OUT_F32, TRANSPOSED>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return (int)cudaGetLastError();
+        configured = true;
+    }
+    kern<<<grid, NUM_THREADS, smem, st>>>(ma, mb, p);
+    return crane_launch_status();
+}
+
+template <bool OUT_F32, bool TRANSPOSED>
+int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid,
+                cudaStream_t st) {
+    switch (bn) {
+        case 16: return launch<16, 8, OUT_F32, TRANSPOSED>(ma, mb, p, grid, st);
+        case 32: return launch<32, 8, OUT_F32, TRANSPOSED>(ma, mb, p, grid, st);
+        case 64: return launch<64, 8, OUT_F32, TRANSPOSED>(ma, mb, p, grid, st);
+        case 128: return launch<128, 6, OUT_F32, TRANSPOSED>(ma, mb, p, grid, st);
+        case 256: return launch<256, 4, OUT_F32, TRANSPOSED>(ma, mb, p, grid, st);
+    }
+    return (int)cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+// D[a, b] = sum_k A[a, k] B[b, k].  bn: columns (rows of B) per tile, 16..256.
+// out_f32 / transposed as in the kernel; split_k > 1 writes float partial sums
+// [split_k][...] into `out` (which must then be float) `split_stride` apart.
+// Requirements (checked, cudaErrorInvalidValue otherwise): k % 8 == 0, lda and
+// ldb multiples of 8 elements, A and B 16-byte aligned.
+CRANE_API int crane_gemm_bf16_tcgen05(const void* A, const void* B, const float* bias, void* out,
+                                      int rows_a, int rows_b, int k, long long lda, long long ldb,
+                                      long long ld_out, int bn, int out_f32, int transposed,
+                                      int split_k, long long split_stride, int* err,
+                                      cudaStream_t st) {
+    if (rows_a <= 0 || rows_b <= 0) return 0;
+    if (k <= 0 || (k & 7) || (lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15))
+        return (int)cudaErrorInvalidValue;
+    if (split_k < 1) split_k = 1;
+    if (split_k > 1 && !out_f32) return (int)cudaErrorInvalidValue;
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, A, rows_a, k, lda, BM) || !make_map(&mb, B, rows_b, k, ldb, bn))
+        return (int)cudaErrorInvalidValue;
+    const int num_kb = (k + BK - 1) / BK;
+    if (split_k > num_kb) split_k = num_kb;
+    GemmParams p;
+    p.rows_a = rows_a; p.rows_b = rows_b; p.k = k;
+    p.kb_per_split = (num_kb + split_k - 1) / split_k;
+    p.out = out; p.ld_out = ld_out; p.split_stride = split_stride; p.bias = bias; p.err = err;
+    dim3 grid((rows_a + BM - 1) / BM, (rows_b + bn - 1) / bn, (num_kb + p.kb_per_split - 1) / p.kb_per_split);
+    if (out_f32)
+        return transposed ? dispatch_bn<true, true>(bn, ma, mb, p, grid, st)
+                          : dispatch_bn<true, false>(bn, ma, mb, p, grid, st);
+    return transposed ? dispatch_bn<false, true>(bn, ma, mb, p, grid, st)
+                      : dispatch_bn<false, false>(bn, ma, mb, p, grid, st);
+}

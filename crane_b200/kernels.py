@@ -25,6 +25,7 @@ _SIGNATURES = {
     "crane_silu_mul": [I, P, P, I, L, P, I, I, P],
     "crane_to_float": [I, P, P, L, P],
     "crane_gemm_simt": [I, I, P, P, P, P, I, I, I, L, L, L, P],
+    "crane_gemm_bf16_tcgen05": [P, P, P, P, I, I, I, L, L, L, I, I, I, I, L, P, P],
     "crane_paged_attention_simt": [I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P],
     "crane_repetition_penalty": [P, L, I, I, P, I, P, P, P],
     "crane_sample": [P, L, I, I, P, P, P, P, P, P, P],
@@ -140,6 +141,42 @@ class Kernels:
                                              w.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K,
                                              a.stride(0), w.stride(0), out.stride(0),
                                              self._stream(a)), "gemm_simt")
+
+    # ---- matrix product on the tensor cores (bfloat16) -------------------
+    @staticmethod
+    def tcgen05_takes(x, w) -> bool:
+        """Whether the tensor-core kernel takes these operands: bfloat16, inner
+        dimension and row pitches multiples of 8 elements, 16-byte aligned."""
+        return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+                and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0
+                and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+    @staticmethod
+    def split_plan(k: int, want: int):
+        """(k-blocks per slice, slices) for a requested number of slices."""
+        num_kb = (k + 63) // 64
+        want = max(1, min(want, num_kb))
+        per = (num_kb + want - 1) // want
+        return per, (num_kb + per - 1) // per
+
+    def gemm_tcgen05(self, x, w, bias, out, err, split_k: int = 1, swap: bool = False,
+                     bn: int = 128) -> None:
+        """out[M,N] = x[M,K] @ w[N,K]^T (+ bias).  ``swap``: the weight fills the
+        128-row side of the MMA and ``bn`` (16..64) covers the tokens.  With
+        ``split_k`` > 1 ``out`` is float [slices, M, N] of partial sums."""
+        M, K = x.shape
+        N = w.shape[0]
+        if split_k > 1:
+            assert out.dtype == torch.float32 and out.dim() == 3 and out.shape[1:] == (M, N)
+            ld, stride = out.stride(1), out.stride(0)
+        else:
+            assert out.shape == (M, N) and out.stride(1) == 1
+            ld, stride = out.stride(0), 0
+        a, b = (w, x) if swap else (x, w)
+        self._check(self.lib.crane_gemm_bf16_tcgen05(
+            a.data_ptr(), b.data_ptr(), _ptr(bias), out.data_ptr(), a.shape[0], b.shape[0], K,
+            a.stride(0), b.stride(0), ld, bn, 1 if out.dtype == torch.float32 else 0,
+            1 if swap else 0, split_k, stride, err.data_ptr(), self._stream(x)), "gemm_tcgen05")
 
     # ---- attention ------------------------------------------------------
     def paged_attention_simt(self, q, out, k_pool, v_pool, positions, tok_entry, block_table,

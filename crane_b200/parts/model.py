@@ -51,24 +51,31 @@ class DecoderModel:
         for b in self.blocks:
             for part in b.parts():
                 part.load(weights, rt)
-        for step in spec.schedule:
-            if not 0 <= step.layer < len(self.blocks) or not 0 <= step.cache_layer < len(self.blocks):
-                raise ValueError(f"schedule step {step} names a layer that does not exist")
+        for place, step in enumerate(spec.schedule):
+            if not 0 <= step.layer < len(self.blocks):
+                raise ValueError(f"schedule step {place} names layer {step.layer}, which does not exist")
+            src = step.cache_step(place)
+            if not 0 <= src < len(spec.schedule) or spec.schedule[src].cache_of is not None and src != place:
+                raise ValueError(f"schedule step {place} reads the cache of step {src}, "
+                                 "which does not exist or has none of its own")
 
     def cache_needs(self) -> List[CacheNeed]:
-        """Per layer, what its mixer keeps between steps."""
-        return [b.mixer.cache_need() for b in self.blocks]
+        """Per step of the schedule, what its mixer keeps between engine steps
+        (nothing for a step that reads another step's cache)."""
+        return [self.blocks[s.layer].mixer.cache_need() if s.cache_of is None else CacheNeed("none")
+                for s in self.spec.schedule]
 
     def forward(self, ctx, caches: List[LayerCache]) -> torch.Tensor:
-        """Runs the step's tokens through the schedule and returns float logits
+        """Runs the step's tokens through the schedule (``caches``: one entry
+        per step of the schedule) and returns float logits
         [wanted rows, vocab] (an empty tensor if nothing is wanted)."""
         rt = self.rt
         n = ctx.n_tokens
         x = rt.ws.get("residual", n, self.spec.hidden_size, torch.float32)
         self.embed.forward(ctx.tokens, x, rt)
         pending = None
-        for step in self.spec.schedule:
-            pending = self.blocks[step.layer].forward(x, pending, ctx, caches[step.cache_layer], rt)
+        for place, step in enumerate(self.spec.schedule):
+            pending = self.blocks[step.layer].forward(x, pending, ctx, caches[step.cache_step(place)], rt)
         if ctx.n_want == 0:
             if pending is not None:
                 pass   # the last block's output only feeds the head

@@ -10,6 +10,7 @@ modeling.rs:517-522, 645, 716, 732).
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -40,6 +41,9 @@ class Runtime:
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.max_rows = max_rows
         self.launches = 0            # kernels of this package launched (a count for reports)
+        self.use_tcgen05 = os.environ.get("CRANE_BF16_GEMM", "tcgen05") != "library"
+        self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.split_rows = 64         # most tokens a product is computed for in slices
 
     # ---- device error word ---------------------------------------------
     def check_errors(self) -> None:
@@ -66,6 +70,31 @@ class Runtime:
         return self._linear_bf16(x, w, bias, out)
 
     def _linear_bf16(self, x, w, bias, out) -> Act:
+        k = self.kernels
+        M, K = x.shape
+        N = w.shape[0]
+        if self.use_tcgen05 and k.tcgen05_takes(x, w):
+            if M <= 64:
+                # few tokens: the weight rows fill the MMA's 128-wide side, and the inner
+                # dimension is cut into slices until every SM has a tile to stream
+                bn = 16 if M <= 16 else 32 if M <= 32 else 64
+                tiles = (N + 127) // 128
+                _, slices = k.split_plan(K, max(1, (self.num_sms + tiles - 1) // tiles))
+                if slices > 1:
+                    parts = self.ws.get("splitk:" + str(N), slices * self.split_rows, N,
+                                        torch.float32, cap=slices * self.split_rows)
+                    parts = parts[:slices * M].view(slices, M, N)
+                    k.gemm_tcgen05(x, w, bias, parts, self.err, split_k=slices, swap=True, bn=bn)
+                    self.launches += 1
+                    if out.dtype == torch.float32:
+                        torch.sum(parts, dim=0, out=out)
+                        return out
+                    return Partials(parts)
+                k.gemm_tcgen05(x, w, bias, out, self.err, swap=True, bn=bn)
+            else:
+                k.gemm_tcgen05(x, w, bias, out, self.err, bn=256 if N >= 2048 else 128)
+            self.launches += 1
+            return out
         if out.dtype == torch.bfloat16:
             torch.mm(x, w.t(), out=out)
             if bias is not None:
@@ -73,6 +102,6 @@ class Runtime:
             return out
         # float result from bfloat16 operands: the FP32-core kernel keeps the
         # float accumulator instead of rounding it to bfloat16 first
-        self.kernels.gemm_simt(x, w, bias, out)
+        k.gemm_simt(x, w, bias, out)
         self.launches += 1
         return out

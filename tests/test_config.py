@@ -89,7 +89,7 @@ def test_another_architecture_can_be_registered():
 def test_spec_is_data_layer_by_layer():
     spec = build_spec(HunyuanDenseConfig.from_dict(tiny_configs.B))
     assert len(spec.layers) == 3 and [s.layer for s in spec.schedule] == [0, 1, 2]
-    assert all(s.cache_layer == s.layer for s in spec.schedule)
+    assert all(s.cache_step(i) == i for i, s in enumerate(spec.schedule))
     m = spec.layers[1].parts["mixer"]
     assert m.name == "gqa_attention" and m.params["num_heads"] == 8 and m.params["qk_norm"] is False
     assert m.params["position"].params == {"head_dim": 32, "theta": 1e6, "alpha": 1000.0,
@@ -104,7 +104,7 @@ def test_spec_is_data_layer_by_layer():
 
 def test_cross_layer_sharing_is_a_schedule():
     spec = build_spec(HunyuanDenseConfig.from_dict(tiny_configs.C))
-    assert [(s.layer, s.cache_layer) for s in spec.schedule] == [(0, 0), (1, 0), (2, 2), (3, 2)]
+    assert [(s.layer, s.cache_step(i)) for i, s in enumerate(spec.schedule)] == [(0, 0), (1, 0), (2, 2), (3, 2)]
     assert spec.layers[1].parts["mixer"].params["own_kv"] is False
     assert "model.layers.1.self_attn.k_proj.weight" in spec.ignored_tensors
 

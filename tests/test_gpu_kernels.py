@@ -309,3 +309,58 @@ def test_sampling_frequencies_follow_the_softmax(K):
     counts = np.bincount(outs.cpu().numpy(), minlength=vocab) / n
     # u is drawn from [1e-7, 0.999), as in the reference, which trims the upper tail a little
     assert np.abs(counts - p).max() < 0.03
+
+
+@pytest.mark.parametrize("M,N,K_,bn", [(128, 128, 64, 128), (128, 256, 128, 256), (300, 520, 160, 128),
+                                       (2048, 3072, 2048, 256), (77, 1000, 352, 128)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tcgen05_many_tokens(K, err, M, N, K_, bn, out_dtype):
+    a = torch.randn(M, K_, device=DEV).bfloat16()
+    w = torch.randn(N, K_, device=DEV).bfloat16()
+    bias = torch.randn(N, device=DEV)
+    out = torch.full((M, N), 7.0, device=DEV, dtype=out_dtype)
+    K.gemm_tcgen05(a, w, bias, out, err, bn=bn)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    want = a.double() @ w.double().T + bias.double()
+    assert rel_err(out, want) < (2e-6 if out_dtype == torch.float32 else 5e-3)
+    K.gemm_tcgen05(a, w, None, out, err, bn=bn)
+    assert rel_err(out, a.double() @ w.double().T) < (2e-6 if out_dtype == torch.float32 else 5e-3)
+
+
+@pytest.mark.parametrize("M,bn", [(1, 16), (8, 16), (16, 16), (17, 32), (33, 64), (64, 64)])
+@pytest.mark.parametrize("N,K_,split", [(256, 128, 1), (3072, 2048, 6), (1000, 352, 3), (120818, 256, 1),
+                                        (2048, 6144, 9)])
+def test_gemm_tcgen05_few_tokens_swapped_and_split(K, err, M, bn, N, K_, split):
+    from crane_b200.kernels import Partials
+    a = torch.randn(M, K_, device=DEV).bfloat16()
+    w = torch.randn(N, K_, device=DEV).bfloat16()
+    bias = torch.randn(N, device=DEV)
+    want = a.double() @ w.double().T + bias.double()
+    out = torch.full((M, N), 7.0, device=DEV, dtype=torch.float32)
+    K.gemm_tcgen05(a, w, bias, out, err, swap=True, bn=bn)
+    assert rel_err(out, want) < 2e-6
+    outb = torch.full((M, N), 7.0, device=DEV, dtype=torch.bfloat16)
+    K.gemm_tcgen05(a, w, bias, outb, err, swap=True, bn=bn)
+    assert rel_err(outb, want) < 5e-3
+    _, slices = K.split_plan(K_, split)
+    if slices > 1:
+        parts = torch.full((slices, M, N), 7.0, device=DEV)
+        K.gemm_tcgen05(a, w, bias, parts, err, split_k=slices, swap=True, bn=bn)
+        assert rel_err(parts.sum(0), want) < 2e-6
+        # the consumers add the slices up themselves
+        x = torch.zeros(M, N, device=DEV)
+        normed = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+        K.add_rmsnorm(x, Partials(parts), torch.ones(N, device=DEV), 1e-6, normed)
+        assert rel_err(x, want.bfloat16().double()) < 1e-6
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+
+
+def test_gemm_tcgen05_refuses_what_it_cannot_take(K, err):
+    from crane_b200.kernels import KernelError
+    a = torch.randn(4, 100, device=DEV).bfloat16()        # inner dimension not a multiple of 8
+    w = torch.randn(16, 100, device=DEV).bfloat16()
+    assert not K.tcgen05_takes(a, w)
+    with pytest.raises(KernelError):
+        K.gemm_tcgen05(a, w, None, torch.empty(4, 16, device=DEV, dtype=torch.bfloat16), err)

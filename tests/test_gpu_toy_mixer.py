@@ -63,7 +63,7 @@ def register_toy():
                                                  "norm2": norm("l0.n2."), "ffn": ffn("l0.ffn.")}),
                   LayerSpec("prenorm_residual", {"norm1": norm("l1.n1."), "mixer": attn,
                                                  "norm2": norm("l1.n2."), "ffn": ffn("l1.ffn.")})]
-        # the toy layer runs twice: the schedule is data
+        # the toy layer runs twice (same weights, a state of its own each time): the schedule is data
         return ModelSpec("ToyStateForCausalLM", h, cfg["vocab"], cfg["max_pos"],
                          PartSpec("embed", "token_embedding", {"vocab_size": cfg["vocab"], "hidden_size": h}, "emb."),
                          layers, [ScheduleStep(0), ScheduleStep(1), ScheduleStep(0)],
@@ -93,7 +93,8 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
     a, b = rng.integers(0, 90, 40).tolist(), rng.integers(0, 90, 23).tolist()
     r = runner()
     kinds = [n.kind for n in r.model.cache_needs()]
-    assert kinds == ["state", "kv"] and r.pools.layers[0].state.shape == (2, 48)
+    assert kinds == ["state", "kv", "state"] and r.pools.layers[0].state.shape == (2, 48)
+    assert r.pools.layers[2].state.data_ptr() != r.pools.layers[0].state.data_ptr()
     whole_a = r.step([StepEntry(1, a, list(range(40)))]).cpu()
     whole_b = r.step([StepEntry(2, b, list(range(23)))]).cpu()
     r.end(1); r.end(2)
