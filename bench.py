@@ -1,0 +1,319 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200, Hunyuan-1.8B layer
+sizes with random weights (bfloat16), printed as ONE JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 8192]
+                    [--layers L] [--impl reference]
+
+A step is one decode step of the whole batch.  ``value`` is decoded tokens per
+second with the K steps timed on the device (CUDA events); ``e2e`` is the same
+through the Python entry point (``LLMEngine.step``: host token ids in, sampled
+token ids out, every step).  The cache of every request is first filled to the
+context length with random keys and values, so the step reads what a real
+request of that length would read; inputs (weights and cache, far more than the
+126 MB of L2) are larger than L2, so nothing is flushed between steps.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODEL = {
+    "architectures": ["HunYuanDenseV1ForCausalLM"], "model_type": "hunyuan_v1_dense",
+    "vocab_size": 120818, "hidden_size": 2048, "intermediate_size": 6144, "num_hidden_layers": 32,
+    "num_attention_heads": 16, "num_key_value_heads": 4, "head_dim": 128, "hidden_act": "silu",
+    "max_position_embeddings": 32768, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+    "rope_scaling": {"alpha": 1000.0, "type": "dynamic"}, "use_qk_norm": True,
+    "tie_word_embeddings": True, "attention_bias": False,
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            out = dict(FALLBACK_PEAKS)
+            out.update({k: float(v) for k, v in d.items() if k in out and v})
+            out["source"] = "measured"
+            return out
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while a region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(int(float(r[0]))); mx = max(mx, int(float(r[1])))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def param_bytes(cfg, layers):
+    h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    q = cfg["num_attention_heads"] * cfg["head_dim"]
+    kv = cfg["num_key_value_heads"] * cfg["head_dim"]
+    per_layer = h * (q + 2 * kv) + q * h + 3 * h * i + 2 * h + 2 * cfg["head_dim"]
+    head = v * h if cfg["tie_word_embeddings"] else 2 * v * h     # tied: the table is read once as the head
+    return 2 * (layers * per_layer + head), 2 * layers * per_layer
+
+
+def decode_bytes(cfg, layers, batch, context):
+    weights, _ = param_bytes(cfg, layers)
+    kv_per_token = 2 * layers * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
+    return weights + batch * context * kv_per_token
+
+
+def prefill_flops(cfg, layers, tokens):
+    h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    q = cfg["num_attention_heads"] * cfg["head_dim"]
+    kv = cfg["num_key_value_heads"] * cfg["head_dim"]
+    per_layer = h * (q + 2 * kv) + q * h + 3 * h * i
+    gemm = 2 * tokens * layers * per_layer + 2 * v * h            # the head runs on the last row only
+    attn = layers * 4 * q * tokens * tokens / 2                    # causal: half of QK^T and PV
+    return gemm + attn
+
+
+def build_model(cfg, engine_opts, seed=0):
+    import torch
+    from crane_b200.generation import ModelForCausalLM
+    from crane_b200.weights.random_init import model_manifest_for, random_tensors
+    tensors = random_tensors(model_manifest_for(cfg), seed, torch.bfloat16, "cuda:0")
+    return ModelForCausalLM.from_tensors(cfg, tensors, "bf16", **engine_opts)
+
+
+def fill_cache(model, batch, context, seed=1):
+    """Admits `batch` requests and gives each `context` cached positions of
+    random keys and values, without running a prefill."""
+    import torch
+    g = torch.Generator(device="cuda:0"); g.manual_seed(seed)
+    for lc in model.runner.pools.layers:
+        if lc.k is not None:
+            lc.k.normal_(0.0, 1.0, generator=g)
+            lc.v.normal_(0.0, 1.0, generator=g)
+    ids = list(range(1000, 1000 + batch))
+    for rid in ids:
+        model.runner.table.admit(rid)
+        model.runner.table.extend(rid, context)
+    return ids
+
+
+def time_decode(model, ids, steps, warmup, vocab):
+    """K decode steps of the whole batch, timed on the device."""
+    import torch
+    from crane_b200.engine import StepEntry
+    from crane_b200.sampling import SamplingParams
+    runner, sampler = model.runner, model.engine.sampler
+    greedy = [SamplingParams() for _ in ids]
+    toks = [(7 * i + 3) % vocab for i in range(len(ids))]
+
+    def one():
+        logits = runner.step([StepEntry(r, [t], [0]) for r, t in zip(ids, toks)])
+        return sampler.sample_device(logits, greedy)
+    for _ in range(warmup):
+        one()
+    torch.cuda.synchronize()
+    launches0 = runner.rt.launches
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        one()
+    stop.record()
+    torch.cuda.synchronize()
+    runner.rt.check_errors()
+    return start.elapsed_time(stop) / steps, (runner.rt.launches - launches0) // steps
+
+
+def time_decode_e2e(model, batch, context, steps, warmup, vocab):
+    """The same through the entry point: requests added with host token ids,
+    every step plans on the host, copies its inputs from pinned memory and
+    reads the sampled ids back."""
+    import torch
+    eng = model.engine
+    runner = model.runner
+    ids = []
+    for b in range(batch):
+        rid = eng.add_request([(11 * b + 5) % vocab], None, max_new_tokens=steps + warmup + 8,
+                              eos_token_ids=[])
+        ids.append(rid)
+    eng.step()                                    # the one-token prompts
+    for rid in ids:                               # then stretch every request to the context length
+        runner.table.extend(rid, context - runner.table.length(rid))
+    for _ in range(warmup):
+        eng.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    n = 0
+    for _ in range(steps):
+        n += len(eng.step())
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    for rid in ids:
+        eng.cancel(rid)
+    eng.finished.clear()
+    m = runner.meta
+    return n / dt, m.total * 4, batch * 4
+
+
+def time_prefill(model, tokens, vocab, reps=3):
+    import torch
+    from crane_b200.engine import StepEntry
+    runner = model.runner
+    prompt = [(13 * i + 1) % vocab for i in range(tokens)]
+    best = None
+    for r in range(reps + 1):
+        rid = 5000 + r
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        runner.step([StepEntry(rid, prompt, [tokens - 1])])
+        stop.record()
+        torch.cuda.synchronize()
+        runner.end(rid)
+        if r > 0:                                 # the first run warms up
+            ms = start.elapsed_time(stop)
+            best = ms if best is None else min(best, ms)
+    return best
+
+
+def reference_arm():
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "cryptomilk/Crane is a Rust workspace on Candle; there is no cargo or rustc "
+                      "in this image and no vendored crates, so it cannot be built or installed offline"}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (both numbers are reported)")
+    ap.add_argument("--impl", default="crane_b200")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print("bench.py: this engine runs on one GPU; --gpus must be 1")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    cfg = dict(MODEL)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    layers, vocab = cfg["num_hidden_layers"], cfg["vocab_size"]
+    pk = peaks()
+    page = 64
+    need_tokens = 64 * (args.context + args.steps + args.warmup + 64) if not args.no_points else \
+        args.batch * (args.context + args.steps + args.warmup + 64)
+    need_tokens = max(need_tokens, args.batch * (args.context + args.steps + args.warmup + 64))
+    opts = dict(page_size=page, num_pages=need_tokens // page + 64, max_concurrent=max(64, args.batch),
+                max_seq_len=args.context + 1024, max_batched_tokens=2048, chunk_size=2048)
+    model = build_model(cfg, opts)
+    runner = model.runner
+
+    def decode_point(batch):
+        ids = fill_cache(model, batch, args.context)
+        ms, launches = time_decode(model, ids, args.steps, args.warmup, vocab)
+        for rid in ids:
+            runner.end(rid)
+        return ms, launches
+
+    with ClockSampler() as clocks:
+        ms, launches = decode_point(args.batch)
+    clock = clocks.summary()
+    value = args.batch * 1000.0 / ms
+    bytes_step = decode_bytes(cfg, layers, args.batch, args.context + args.warmup + args.steps // 2)
+    achieved = bytes_step / (ms * 1e-3) / 1e9
+    e2e_value, h2d, d2h = time_decode_e2e(model, args.batch, args.context, args.steps, args.warmup, vocab)
+
+    out = {
+        "metric": "decode tokens/s (Hunyuan-1.8B sizes, batch %d, context %d)" % (args.batch, args.context),
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"model": "Hunyuan-1.8B-sized, random weights", "layers": layers,
+                   "layers_of_model": full_layers, "hidden": cfg["hidden_size"],
+                   "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
+                   "vocab": vocab, "global_batch": args.batch, "seq_len": args.context,
+                   "page_size": page, "parallelism": "none", "l2": "inputs larger than L2",
+                   "cuda_graphs": bool(runner.graph_replays)},
+        "clocks": clock,
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches * args.steps,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4),
+                     "peaks": pk["source"]},
+    }
+    if not args.no_points:
+        points = {}
+        for b in (1, 64):
+            pms, _ = decode_point(b)
+            points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
+        out["points"] = points
+        tokens = 2048
+        pms = time_prefill(model, tokens, vocab)
+        flops = prefill_flops(cfg, layers, tokens)
+        out["prefill"] = {"value": round(tokens * 1000.0 / pms, 1), "tokens": tokens,
+                          "ms": round(pms, 3),
+                          "frac": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -59,6 +59,8 @@ class StepContext:
     h_cu_q: np.ndarray
     h_kv_len: np.ndarray
     h_slots: np.ndarray
+    graph_bucket: int = 0       # > 0: a decode step padded to this many entries
+    real_entries: int = 0
 
 
 class _MetaBuffers:
@@ -120,6 +122,12 @@ class ModelRunner:
         self.model = DecoderModel(self.spec, source, self.rt, where)
         self._build_cache()
         self.steps = 0
+        # decode steps (one token per entry) of the bfloat16 path replay a captured graph
+        self._graphs: Dict[int, tuple] = {}
+        self._graph_generation = -1
+        self._graphs_ok = (self.cfg.use_cuda_graphs and not self.rt.exact
+                           and all(n.kind != "state" for n in self.model.cache_needs()))
+        self.graph_replays = 0
 
     # ---- cache geometry -------------------------------------------------
     def _build_cache(self) -> None:
@@ -212,8 +220,19 @@ class ModelRunner:
                 if not self.table.is_live(e.request_id):
                     self.table.admit(e.request_id)
                 self.table.extend(e.request_id, c)
+        # a pure decode step is padded to a fixed batch size (copies of entry 0, which
+        # recompute and rewrite exactly what entry 0 does) so that a captured graph fits it
+        pad_to = 0
+        if (self._graphs_ok and max(counts) == 1 and all(len(e.want) == 1 for e in entries)):
+            pad_to = self._bucket(n_entries)
         m = self.meta
         m.copied.synchronize()                      # the last step's copy has left the host block
+        real_entries, real_tokens = n_entries, n_tokens
+        if pad_to:
+            entries = list(entries) + [entries[0]] * (pad_to - n_entries)
+            arrays = arrays + [arrays[0]] * (pad_to - n_entries)
+            counts = counts + [1] * (pad_to - n_entries)
+            n_entries = n_tokens = pad_to
         tok = m.view("tokens", n_tokens, False)
         pos = m.view("positions", n_tokens, False)
         ent = m.view("tok_entry", n_tokens, False)
@@ -243,6 +262,7 @@ class ModelRunner:
         m.copied.record()
 
         ctx = StepContext()
+        ctx.graph_bucket, ctx.real_entries = pad_to, real_entries
         ctx.n_tokens, ctx.n_entries, ctx.n_want = n_tokens, n_entries, n_want
         ctx.max_q_len = max(counts)
         ctx.max_kv_len = int(kvl.max())
@@ -265,6 +285,39 @@ class ModelRunner:
         [number of wanted places, vocab] on the device, in the order of the
         entries and of their ``want``."""
         ctx = self.prepare(entries, reserved)
-        logits = self.model.forward(ctx, self.pools.layers)
         self.steps += 1
+        if ctx.graph_bucket:
+            return self._replay(ctx)[:ctx.real_entries]
+        return self.model.forward(ctx, self.pools.layers)
+
+    # ---- captured decode steps -----------------------------------------
+    def _bucket(self, n: int) -> int:
+        b = 1
+        while b < n:
+            b *= 2
+        return min(b, self.cap_entries) if b <= self.cap_entries else 0
+
+    def _replay(self, ctx: StepContext) -> torch.Tensor:
+        if self._graph_generation != self.rt.ws.generation:
+            self._graphs.clear()                    # a buffer moved: captured addresses are stale
+            self._graph_generation = self.rt.ws.generation
+        entry = self._graphs.get(ctx.graph_bucket)
+        if entry is None:
+            # once eagerly, so that every buffer exists; then the same step again under capture
+            # (it rewrites the same cache rows with the same values)
+            self.model.forward(ctx, self.pools.layers)
+            if self._graph_generation != self.rt.ws.generation:
+                self._graphs.clear()
+                self._graph_generation = self.rt.ws.generation
+            before = self.rt.launches
+            torch.cuda.synchronize(self.rt.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx, self.pools.layers)
+            entry = (graph, logits, self.rt.launches - before)
+            self._graphs[ctx.graph_bucket] = entry
+        graph, logits, launches = entry
+        graph.replay()
+        self.rt.launches += launches
+        self.graph_replays += 1
         return logits

@@ -120,6 +120,7 @@ class Workspace:
         self.device = device
         self.max_rows = max_rows
         self._bufs: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
+        self.generation = 0          # goes up whenever a buffer is replaced by a larger one
 
     def get(self, name: str, rows: int, cols: int, dtype: torch.dtype,
             cap: Optional[int] = None) -> torch.Tensor:
@@ -129,6 +130,8 @@ class Workspace:
         buf = self._bufs.get(key)
         if buf is None or buf.shape[0] < rows:
             cap = max(rows, self.max_rows if cap is None else cap)
+            if buf is not None:
+                self.generation += 1
             buf = torch.empty((cap, cols), dtype=dtype, device=self.device)
             self._bufs[key] = buf
         return buf[:rows]
