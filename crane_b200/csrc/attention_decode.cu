@@ -1,0 +1,299 @@
+// Attention of single decoded tokens over the paged cache (bf16), split along
+// the keys.  One CTA takes one (slice of the keys, kv head, request); its four
+// warps take 32-key tiles of the slice in turn, each keeping its own running
+// softmax, and merge at the end.  All query heads that share the kv head ride
+// in the rows of one MMA tile, so every key and value is read once per group
+// (the reference's decode path groups the same way:
+// crane-core/src/models/hunyuan_dense/modeling.rs:575-608).  With more than one
+// slice the CTAs leave (max, sum, unnormalised output) per slice in scratch
+// memory and a second kernel merges the slices.
+//
+// scores = q k^T / sqrt(d), softmax in float, keys lo..pos of the request with
+// lo = max(0, pos - window + 1) (modeling.rs:579-601).
+#include "attention_mma.cuh"
+
+namespace {
+using namespace attn;
+
+constexpr int TILE = 32;
+constexpr int WARPS = 4;
+
+template <int D>
+__global__ void __launch_bounds__(WARPS * 32)
+paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
+                         float* __restrict__ part_o, float* __restrict__ part_ml,
+                         const __nv_bfloat16* __restrict__ k_pool,
+                         const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ cu_q,
+                         const int* __restrict__ kv_len, const int* __restrict__ block_table,
+                         int max_blocks, int num_pages, int page_size, int nq, int nkv, int window,
+                         float scale_log2, int n_splits, int* err) {
+    constexpr int RB = Tile<D>::ROW_BYTES;
+    constexpr int TILE_BYTES = TILE * RB;
+    constexpr int KS = D / 16;                     // k-steps of q k^T
+    constexpr int DN = D / 8;                      // n-tiles of the output
+    extern __shared__ __align__(16) uint8_t smem[];
+
+    const int split = blockIdx.x, g = blockIdx.y, e = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_rep = nq / nkv;
+    const int t = cu_q[e];
+    const int pos = kv_len[e] - 1;
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int* table = block_table + (long long)e * max_blocks;
+
+    const int first_tile = lo / TILE;
+    const int n_tiles = pos / TILE - first_tile + 1;
+    const int per_split = (n_tiles + n_splits - 1) / n_splits;
+    const int tile_begin = first_tile + split * per_split;
+    const int tile_end = min(first_tile + n_tiles, tile_begin + per_split);
+
+    // this warp's two stages of (K tile, V tile)
+    const uint32_t wbase = smem_u32(smem) + warp * 4 * TILE_BYTES;
+
+    // query rows: row r of the MMA tile is query head g * n_rep + r
+    uint32_t qf[KS][4];
+    {
+        const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = r0 + (i & 1) * 8, c = ks * 16 + c0 + (i >> 1) * 8;
+                uint32_t v = 0;
+                if (r < n_rep)
+                    v = *(const uint32_t*)(q + ((long long)t * nq + g * n_rep + r) * D + c);
+                qf[ks][i] = v;
+            }
+        }
+    }
+    float o[DN][4];
+#pragma unroll
+    for (int i = 0; i < DN; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    bool bad_page = false;
+
+    int ti = tile_begin + warp;
+    if (ti < tile_end) {
+        load_tile_async<D, TILE>(wbase, k_pool, table, num_pages, page_size, nkv, g, ti * TILE, lo,
+                                 pos, lane, bad_page);
+        load_tile_async<D, TILE>(wbase + TILE_BYTES, v_pool, table, num_pages, page_size, nkv, g,
+                                 ti * TILE, lo, pos, lane, bad_page);
+    }
+    cp_async_commit();
+    for (int it = 0; ti < tile_end; ti += WARPS, ++it) {
+        const uint32_t kt = wbase + (it & 1) * 2 * TILE_BYTES, vt = kt + TILE_BYTES;
+        const int nxt = ti + WARPS;
+        if (nxt < tile_end) {
+            const uint32_t nk = wbase + ((it + 1) & 1) * 2 * TILE_BYTES;
+            load_tile_async<D, TILE>(nk, k_pool, table, num_pages, page_size, nkv, g, nxt * TILE, lo,
+                                     pos, lane, bad_page);
+            load_tile_async<D, TILE>(nk + TILE_BYTES, v_pool, table, num_pages, page_size, nkv, g,
+                                     nxt * TILE, lo, pos, lane, bad_page);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncwarp();
+
+        // ---- scores: 16 rows x 32 keys ----
+        float s[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+        const int mi = lane >> 3, mr = lane & 7;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                // matrices: (keys +0..7, d lo), (keys +0..7, d hi), (keys +8..15, d lo), (keys +8..15, d hi)
+                const int key = half * 16 + (mi >> 1) * 8 + mr;
+                const int chunk = ks * 2 + (mi & 1);
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(kt + key * RB + chunk * 16, b0, b1, b2, b3);
+                mma_bf16(s[half * 2], qf[ks], b0, b1);
+                mma_bf16(s[half * 2 + 1], qf[ks], b2, b3);
+            }
+        }
+        // ---- mask, running softmax ----
+        const int key0 = ti * TILE + (lane & 3) * 2;
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int j = key0 + nt * 8 + (c & 1);
+                const float v = (j >= lo && j <= pos) ? s[nt][c] * scale_log2 : -INFINITY;
+                s[nt][c] = v;
+                mx[c >> 1] = fmaxf(mx[c >> 1], v);
+            }
+        float corr[2], base[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float m_new = fmaxf(m[h], quad_max(mx[h]));
+            base[h] = (m_new == -INFINITY) ? 0.f : m_new;
+            corr[h] = exp2f(m[h] - base[h]);           // exp2(-inf) = 0 on the first tile
+            m[h] = m_new;
+        }
+        float rs[2] = {0.f, 0.f};
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float p = exp2f(s[nt][c] - base[c >> 1]);
+                s[nt][c] = p;
+                rs[c >> 1] += p;
+            }
+        l[0] = l[0] * corr[0] + rs[0];
+        l[1] = l[1] * corr[1] + rs[1];
+#pragma unroll
+        for (int i = 0; i < DN; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0];
+            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+        // ---- output += p v ----
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+            uint32_t pf[4];
+            pf[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+            pf[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+            pf[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            pf[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int dn = 0; dn < DN; dn += 2) {
+                // matrices: (keys +0..7, d dn), (keys +8..15, d dn), (keys +0..7, d dn+1), (keys +8..15, d dn+1)
+                const int key = kk * 16 + (mi & 1) * 8 + mr;
+                const int chunk = dn + (mi >> 1);
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(vt + key * RB + chunk * 16, b0, b1, b2, b3);
+                mma_bf16(o[dn], pf, b0, b1);
+                mma_bf16(o[dn + 1], pf, b2, b3);
+            }
+        }
+        __syncwarp();
+    }
+    cp_async_wait<0>();
+    if (__any_sync(0xffffffffu, bad_page) && lane == 0) atomicOr(err, CRANE_ERR_PAGE_RANGE);
+    l[0] = quad_sum(l[0]);
+    l[1] = quad_sum(l[1]);
+
+    // ---- merge the four warps ----
+    __syncthreads();                                 // every warp is done with its tiles
+    float* sm_o = (float*)smem;                      // [WARPS][16][D]
+    float* sm_ml = sm_o + WARPS * 16 * D;            // [WARPS][16][2]
+    {
+        const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+#pragma unroll
+        for (int dn = 0; dn < DN; ++dn) {
+            float* p0 = sm_o + ((warp * 16 + r0) * D) + dn * 8 + c0;
+            float* p1 = sm_o + ((warp * 16 + r0 + 8) * D) + dn * 8 + c0;
+            p0[0] = o[dn][0]; p0[1] = o[dn][1];
+            p1[0] = o[dn][2]; p1[1] = o[dn][3];
+        }
+        if ((lane & 3) == 0) {
+            sm_ml[(warp * 16 + r0) * 2] = m[0];      sm_ml[(warp * 16 + r0) * 2 + 1] = l[0];
+            sm_ml[(warp * 16 + r0 + 8) * 2] = m[1];  sm_ml[(warp * 16 + r0 + 8) * 2 + 1] = l[1];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n_rep * D; idx += WARPS * 32) {
+        const int r = idx / D, c = idx % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) M = fmaxf(M, sm_ml[(w * 16 + r) * 2]);
+        const float mb = (M == -INFINITY) ? 0.f : M;
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            const float f = exp2f(sm_ml[(w * 16 + r) * 2] - mb);
+            L += f * sm_ml[(w * 16 + r) * 2 + 1];
+            O += f * sm_o[(w * 16 + r) * D + c];
+        }
+        const int h = g * n_rep + r;
+        if (n_splits == 1) {
+            out[((long long)t * nq + h) * D + c] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        } else {
+            const long long pi = ((long long)e * nq + h) * n_splits + split;
+            part_o[pi * D + c] = O;
+            if (c == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
+        }
+    }
+}
+
+// out[t, h, :] = sum_s w_s o_s / sum_s w_s l_s with w_s = exp2(m_s - max m)
+__global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    __nv_bfloat16* __restrict__ out, const int* __restrict__ cu_q,
+                                    int nq, int d, int n_splits) {
+    const int e = blockIdx.x, h = blockIdx.y;
+    const long long base = ((long long)e * nq + h) * n_splits;
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+    const float mb = (M == -INFINITY) ? 0.f : M;
+    float L = 0.f;
+    for (int s = 0; s < n_splits; ++s) L += exp2f(part_ml[(base + s) * 2] - mb) * part_ml[(base + s) * 2 + 1];
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    const int t = cu_q[e];
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        float O = 0.f;
+        for (int s = 0; s < n_splits; ++s)
+            O += exp2f(part_ml[(base + s) * 2] - mb) * part_o[(base + s) * d + c];
+        out[((long long)t * nq + h) * d + c] = __float2bfloat16_rn(O * inv);
+    }
+}
+
+template <int D>
+int launch_decode(const void* q, void* out, float* part_o, float* part_ml, const void* k_pool,
+                  const void* v_pool, const int* cu_q, const int* kv_len, const int* block_table,
+                  int max_blocks, int num_pages, int page_size, int n_entries, int nq, int nkv,
+                  int window, float scale, int n_splits, int* err, cudaStream_t st) {
+    constexpr int tiles = WARPS * 4 * TILE * Tile<D>::ROW_BYTES;
+    constexpr int merge = WARPS * 16 * (D + 2) * 4;
+    constexpr int smem = tiles > merge ? tiles : merge;
+    auto kern = paged_decode_attn_kernel<D>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return (int)cudaGetLastError();
+        configured = true;
+    }
+    dim3 grid(n_splits, nkv, n_entries);
+    kern<<<grid, WARPS * 32, smem, st>>>(
+        (const __nv_bfloat16*)q, (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)k_pool,
+        (const __nv_bfloat16*)v_pool, cu_q, kv_len, block_table, max_blocks, num_pages, page_size, nq,
+        nkv, window, scale * 1.4426950408889634f, n_splits, err);
+    int rc = crane_launch_status();
+    if (rc == 0 && n_splits > 1) {
+        decode_merge_kernel<<<dim3(n_entries, nq), 64, 0, st>>>(part_o, part_ml, (__nv_bfloat16*)out,
+                                                               cu_q, nq, D, n_splits);
+        rc = crane_launch_status();
+    }
+    return rc;
+}
+}  // namespace
+
+// 1 if the kernel is built for this head size and group size, else 0.
+CRANE_API int crane_paged_decode_attention_supports(int d, int nq, int nkv) {
+    if (nkv <= 0 || nq % nkv != 0 || nq / nkv > 16) return 0;
+    return d == 16 || d == 32 || d == 48 || d == 64 || d == 128;
+}
+
+// One token per entry (row cu_q[e] of q and out).  part_o needs
+// n_entries * nq * n_splits * d floats and part_ml n_entries * nq * n_splits * 2
+// when n_splits > 1.
+CRANE_API int crane_paged_decode_attention(const void* q, void* out, float* part_o, float* part_ml,
+                                           const void* k_pool, const void* v_pool, const int* cu_q,
+                                           const int* kv_len, const int* block_table, int max_blocks,
+                                           int num_pages, int page_size, int n_entries, int nq, int nkv,
+                                           int d, int window, float scale, int n_splits, int* err,
+                                           cudaStream_t st) {
+    if (n_entries <= 0) return 0;
+    if (!crane_paged_decode_attention_supports(d, nq, nkv) || n_splits < 1)
+        return (int)cudaErrorInvalidValue;
+#define CASE(DD)                                                                                  \
+    case DD:                                                                                      \
+        return launch_decode<DD>(q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len, block_table, \
+                                 max_blocks, num_pages, page_size, n_entries, nq, nkv, window, scale, \
+                                 n_splits, err, st);
+    switch (d) {
+        CASE(16) CASE(32) CASE(48) CASE(64) CASE(128)
+    }
+#undef CASE
+    return (int)cudaErrorInvalidValue;
+}

@@ -27,6 +27,8 @@ _SIGNATURES = {
     "crane_gemm_simt": [I, I, P, P, P, P, I, I, I, L, L, L, P],
     "crane_gemm_bf16_tcgen05": [P, P, P, P, I, I, I, L, L, L, I, I, I, I, L, P, P],
     "crane_paged_attention_simt": [I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P],
+    "crane_paged_decode_attention_supports": [I, I, I],
+    "crane_paged_decode_attention": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P],
     "crane_repetition_penalty": [P, L, I, I, P, I, P, P, P],
     "crane_sample": [P, L, I, I, P, P, P, P, P, P, P],
 }
@@ -46,6 +48,11 @@ class Partials:
     @property
     def shape(self):
         return self.parts.shape[1:]
+
+    def sum(self, dtype=None):
+        """The product itself: the slices added up in order (rounded once to ``dtype``)."""
+        total = self.parts.sum(dim=0)
+        return total if dtype is None else total.to(dtype)
 
 
 Act = Union[torch.Tensor, Partials]
@@ -186,6 +193,20 @@ class Kernels:
             positions.data_ptr(), tok_entry.data_ptr(), block_table.data_ptr(),
             block_table.shape[1], k_pool.shape[0], page_size, q.shape[0], nq, nkv, d, int(window),
             float(scale), err.data_ptr(), self._stream(q)), "paged_attention_simt")
+
+    def decode_attention_supports(self, d: int, nq: int, nkv: int) -> bool:
+        return bool(self.lib.crane_paged_decode_attention_supports(d, nq, nkv))
+
+    def paged_decode_attention(self, q, out, k_pool, v_pool, cu_q, kv_len, block_table, page_size,
+                               nq, nkv, d, window, scale, n_splits, part_o, part_ml, err) -> None:
+        """One token per entry (bfloat16); ``part_o`` [entries * nq * n_splits * d]
+        and ``part_ml`` [entries * nq * n_splits * 2] floats are scratch for n_splits > 1."""
+        n_entries = kv_len.shape[0]
+        self._check(self.lib.crane_paged_decode_attention(
+            q.data_ptr(), out.data_ptr(), _ptr(part_o), _ptr(part_ml), k_pool.data_ptr(),
+            v_pool.data_ptr(), cu_q.data_ptr(), kv_len.data_ptr(), block_table.data_ptr(),
+            block_table.shape[1], k_pool.shape[0], page_size, n_entries, nq, nkv, d, int(window),
+            float(scale), int(n_splits), err.data_ptr(), self._stream(q)), "paged_decode_attention")
 
     # ---- sampling -------------------------------------------------------
     def repetition_penalty(self, logits, context, ctx_len, penalty) -> None:

@@ -95,8 +95,22 @@ class GqaAttention(Part):
                           cache.page_size, self.nq, self.nkv, self.d, self.own_kv,
                           self.position is not None, rt.err)
         o = rt.ws.get("attn_o", n, self.nq * self.d, rt.dtype)
-        k.paged_attention_simt(q, o, cache.k, cache.v, ctx.positions, ctx.tok_entry, table,
-                               cache.page_size, self.nq, self.nkv, self.d, self.window, self.scale,
-                               rt.err)
-        rt.launches += 2
+        if (not rt.exact and ctx.max_q_len == 1 and n == ctx.n_entries
+                and k.decode_attention_supports(self.d, self.nq, self.nkv)):
+            # single decoded tokens: keys split over enough CTAs to fill the device
+            splits = max(1, min(32, (2 * rt.num_sms) // max(1, ctx.n_entries * self.nkv)))
+            part_o = part_ml = None
+            if splits > 1:
+                rows = rt.max_decode_rows * self.nq * 32
+                part_o = rt.ws.get("attn_part_o", rows, self.d, torch.float32, cap=rows)
+                part_ml = rt.ws.get("attn_part_ml", rows, 2, torch.float32, cap=rows)
+            k.paged_decode_attention(q, o, cache.k, cache.v, ctx.cu_q, ctx.kv_len, table,
+                                     cache.page_size, self.nq, self.nkv, self.d, self.window,
+                                     self.scale, splits, part_o, part_ml, rt.err)
+            rt.launches += 3 if splits > 1 else 2
+        else:
+            k.paged_attention_simt(q, o, cache.k, cache.v, ctx.positions, ctx.tok_entry, table,
+                                   cache.page_size, self.nq, self.nkv, self.d, self.window,
+                                   self.scale, rt.err)
+            rt.launches += 2
         return rt.linear(o, self.o_w, self.o_b, "attn_out")

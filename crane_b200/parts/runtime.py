@@ -28,7 +28,7 @@ class DeviceFault(RuntimeError):
 
 
 class Runtime:
-    def __init__(self, device, dtype: torch.dtype, max_rows: int):
+    def __init__(self, device, dtype: torch.dtype, max_rows: int, max_decode_rows: int = 64):
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise KernelError("the engine runs on a CUDA device only; there is no CPU path")
@@ -40,6 +40,7 @@ class Runtime:
         self.ws = Workspace(self.device, max_rows)
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.max_rows = max_rows
+        self.max_decode_rows = max_decode_rows     # most single-token entries of a step
         self.launches = 0            # kernels of this package launched (a count for reports)
         self.use_tcgen05 = os.environ.get("CRANE_BF16_GEMM", "tcgen05") != "library"
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count

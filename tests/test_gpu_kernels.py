@@ -370,3 +370,40 @@ def test_gemm_tcgen05_refuses_what_it_cannot_take(K, err):
     assert not K.tcgen05_takes(a, w)
     with pytest.raises(KernelError):
         K.gemm_tcgen05(a, w, None, torch.empty(4, 16, device=DEV, dtype=torch.bfloat16), err)
+
+
+@pytest.mark.parametrize("d,nq,nkv,page_size,window,splits", [
+    (128, 16, 4, 64, 0, 1), (128, 16, 4, 64, 0, 7), (64, 8, 8, 16, 0, 3), (16, 4, 2, 8, 0, 2),
+    (32, 8, 2, 16, 50, 4), (48, 6, 3, 32, 0, 32), (128, 32, 2, 128, 300, 5)])
+def test_paged_decode_attention(K, err, d, nq, nkv, page_size, window, splits):
+    """Single tokens of requests of very different lengths, one of them with a
+    far key that must dominate; every slicing of the keys gives the same."""
+    assert K.decode_attention_supports(d, nq, nkv)
+    torch.manual_seed(d * 7 + splits)
+    lens = [1, 31, 32, 33, 700, 1025]
+    ks = [torch.randn(n, nkv, d).bfloat16().float() for n in lens]
+    vs = [torch.randn(n, nkv, d).bfloat16().float() for n in lens]
+    qs = [torch.randn(nq, d).bfloat16().float() for _ in lens]
+    far = 1025 - 40 if window else 11             # inside the window when there is one
+    ks[5][far] = 0.0; ks[5][far, :, 1] = 30.0; qs[5][:, 1] = 6.0 * d ** 0.5 / 30.0 * 4
+    ks[5] = ks[5].bfloat16().float(); qs[5] = qs[5].bfloat16().float()
+    k_pool, v_pool, table = paged_cache(ks, vs, page_size, torch.bfloat16, seed=splits)
+    n = len(lens)
+    q = torch.stack(qs).to(DEV).bfloat16().reshape(n, nq * d)
+    out = torch.full_like(q, 9.0)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    part_o = torch.empty(n * nq * splits * d, device=DEV)
+    part_ml = torch.empty(n * nq * splits * 2, device=DEV)
+    K.paged_decode_attention(q, out, k_pool, v_pool, i32(list(range(n + 1))), i32(lens), table, page_size,
+                             nq, nkv, d, window, d ** -0.5, splits, part_o, part_ml, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    for e in range(n):
+        want = attention_reference(qs[e], ks[e], vs[e], lens[e] - 1, window)
+        assert rel_err(out[e].cpu().view(nq, d), want) < 1.5e-2, (e, lens[e])
+    assert rel_err(out[5].cpu().view(nq, d)[0], vs[5][far, 0].double()) < 2e-2
+    # the plain kernel agrees
+    ref = torch.empty_like(q)
+    K.paged_attention_simt(q, ref, k_pool, v_pool, i32([l - 1 for l in lens]), i32(list(range(n))), table,
+                           page_size, nq, nkv, d, window, d ** -0.5, err)
+    assert rel_err(out, ref.double()) < 1.5e-2
