@@ -66,17 +66,19 @@ struct Tile {
 };
 
 // Copies rows [key0, key0 + ROWS) of one kv head from the paged pool into a
-// tile, one warp, asynchronously.  Rows outside [lo, hi] and rows whose page
+// tile, by THREADS threads together, asynchronously.  Rows outside [lo, hi] and rows whose page
 // number is out of range become zeros (the latter is also reported).
-template <int D, int ROWS>
+template <int D, int ROWS, int THREADS = 32>
 __device__ __forceinline__ void load_tile_async(uint32_t tile, const __nv_bfloat16* pool,
                                                 const int* table, int num_pages, int page_size,
                                                 int nkv, int g, int key0, int lo, int hi, int lane,
                                                 bool& bad_page) {
+    // `lane` is the thread's index among the THREADS that copy the tile together
     constexpr int CH = Tile<D>::CHUNKS;
+    static_assert(ROWS * CH % THREADS == 0, "the tile must divide among the copying threads");
 #pragma unroll
-    for (int i = 0; i < ROWS * CH / 32; ++i) {
-        const int c = i * 32 + lane;
+    for (int i = 0; i < ROWS * CH / THREADS; ++i) {
+        const int c = i * THREADS + lane;
         const int row = c / CH, col = c % CH;
         const int j = key0 + row;
         const __nv_bfloat16* src = pool;

@@ -29,6 +29,8 @@ _SIGNATURES = {
     "crane_paged_attention_simt": [I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P],
     "crane_paged_decode_attention_supports": [I, I, I],
     "crane_paged_decode_attention": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P],
+    "crane_paged_prefill_attention_supports": [I, I, I],
+    "crane_paged_prefill_attention": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P],
     "crane_repetition_penalty": [P, L, I, I, P, I, P, P, P],
     "crane_sample": [P, L, I, I, P, P, P, P, P, P, P],
 }
@@ -207,6 +209,19 @@ class Kernels:
             v_pool.data_ptr(), cu_q.data_ptr(), kv_len.data_ptr(), block_table.data_ptr(),
             block_table.shape[1], k_pool.shape[0], page_size, n_entries, nq, nkv, d, int(window),
             float(scale), int(n_splits), err.data_ptr(), self._stream(q)), "paged_decode_attention")
+
+    def prefill_attention_supports(self, d: int, nq: int, nkv: int) -> bool:
+        return bool(self.lib.crane_paged_prefill_attention_supports(d, nq, nkv))
+
+    def paged_prefill_attention(self, q, out, k_pool, v_pool, cu_q, kv_len, block_table, page_size,
+                                total_q_tiles, nq, nkv, d, window, scale, err) -> None:
+        """Any mix of portions and single tokens (bfloat16).  ``total_q_tiles``:
+        the sum over the entries of ceil(tokens / 64)."""
+        self._check(self.lib.crane_paged_prefill_attention(
+            q.data_ptr(), out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), cu_q.data_ptr(),
+            kv_len.data_ptr(), block_table.data_ptr(), block_table.shape[1], k_pool.shape[0],
+            page_size, kv_len.shape[0], int(total_q_tiles), nq, nkv, d, int(window), float(scale),
+            err.data_ptr(), self._stream(q)), "paged_prefill_attention")
 
     # ---- sampling -------------------------------------------------------
     def repetition_penalty(self, logits, context, ctx_len, penalty) -> None:

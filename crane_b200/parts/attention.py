@@ -108,6 +108,13 @@ class GqaAttention(Part):
                                      cache.page_size, self.nq, self.nkv, self.d, self.window,
                                      self.scale, splits, part_o, part_ml, rt.err)
             rt.launches += 3 if splits > 1 else 2
+        elif not rt.exact and k.prefill_attention_supports(self.d, self.nq, self.nkv):
+            q_lens = ctx.h_cu_q[1:ctx.n_entries + 1] - ctx.h_cu_q[:ctx.n_entries]
+            tiles = int(((q_lens + 63) // 64).sum())
+            k.paged_prefill_attention(q, o, cache.k, cache.v, ctx.cu_q, ctx.kv_len, table,
+                                      cache.page_size, tiles, self.nq, self.nkv, self.d, self.window,
+                                      self.scale, rt.err)
+            rt.launches += 2
         else:
             k.paged_attention_simt(q, o, cache.k, cache.v, ctx.positions, ctx.tok_entry, table,
                                    cache.page_size, self.nq, self.nkv, self.d, self.window,

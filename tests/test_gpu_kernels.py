@@ -407,3 +407,38 @@ def test_paged_decode_attention(K, err, d, nq, nkv, page_size, window, splits):
     K.paged_attention_simt(q, ref, k_pool, v_pool, i32([l - 1 for l in lens]), i32(list(range(n))), table,
                            page_size, nq, nkv, d, window, d ** -0.5, err)
     assert rel_err(out, ref.double()) < 1.5e-2
+
+
+@pytest.mark.parametrize("d,nq,nkv,page_size,window", [(128, 8, 2, 64, 0), (64, 4, 4, 16, 0),
+                                                        (16, 4, 2, 8, 0), (32, 4, 1, 16, 37),
+                                                        (48, 6, 3, 32, 0), (128, 4, 1, 128, 100)])
+def test_paged_prefill_attention_mixed_batch(K, err, d, nq, nkv, page_size, window):
+    """A portion that starts in the middle of a page after 105 cached positions, a
+    single decoded token far into a long context, a whole prompt of 200, a
+    2-token portion and a 1-token request, in one launch."""
+    torch.manual_seed(d + window)
+    lens = [150, 333, 200, 67, 1]
+    q_lens = [45, 1, 200, 2, 1]
+    ks = [torch.randn(n, nkv, d).bfloat16().float() for n in lens]
+    vs = [torch.randn(n, nkv, d).bfloat16().float() for n in lens]
+    qs = [torch.randn(ql, nq, d).bfloat16().float() for ql in q_lens]
+    far = 333 - 20 if window else 17
+    ks[1][far] = 0.0; ks[1][far, :, 0] = 40.0
+    qs[1][0, :, 0] = 1.0 * d ** 0.5                  # score 40 at the far key
+    k_pool, v_pool, table = paged_cache(ks, vs, page_size, torch.bfloat16, seed=d)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    cu = np.concatenate([[0], np.cumsum(q_lens)]).tolist()
+    tiles = sum((n + 63) // 64 for n in q_lens)
+    q = torch.cat(qs).to(DEV).bfloat16().reshape(-1, nq * d)
+    out = torch.full_like(q, 9.0)
+    K.paged_prefill_attention(q, out, k_pool, v_pool, i32(cu), i32(lens), table, page_size, tiles,
+                              nq, nkv, d, window, d ** -0.5, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    row = 0
+    for e, (n, ql) in enumerate(zip(lens, q_lens)):
+        for i in range(ql):
+            want = attention_reference(qs[e][i], ks[e], vs[e], n - ql + i, window)
+            assert rel_err(out[row].cpu().view(nq, d), want) < 1.5e-2, (e, i)
+            row += 1
+    assert rel_err(out[45].cpu().view(nq, d)[0], vs[1][far, 0].double()) < 2e-2
