@@ -11,6 +11,7 @@
 // scores = q k^T / sqrt(d), softmax in float, keys lo..pos of the request with
 // lo = max(0, pos - window + 1) (modeling.rs:579-601).
 #include "attention_mma.cuh"
+#include "no_alloc.h"
 
 namespace {
 using namespace attn;
@@ -296,4 +297,74 @@ CRANE_API int crane_paged_decode_attention(const void* q, void* out, float* part
     }
 #undef CASE
     return (int)cudaErrorInvalidValue;
+}
+
+// ------------------------------------------------------------------------
+// The entry point that allocates nothing (declared and described in
+// no_alloc.h).  The slices' partial results live in this array of the library
+// image: first the unnormalised outputs, then the (max, sum) pairs.
+static __device__ __align__(256) float g_noalloc_scratch[CRANE_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* g_scratch_addr[MAX_DEVICES];      // device address of the array, per device, once looked up
+
+// In host code the array's name is only a handle: the address a kernel can use
+// has to be asked for, with the device in question current.
+int scratch_address(float** out) {
+    int dev = -1;
+    cudaError_t rc = cudaGetDevice(&dev);
+    if (rc != cudaSuccess) return (int)rc;
+    if (dev < 0 || dev >= MAX_DEVICES) return CRANE_NOALLOC_BAD_ARGUMENT;
+    if (g_scratch_addr[dev] == nullptr) {
+        float* p = nullptr;
+        rc = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+        if (rc != cudaSuccess || p == nullptr) return rc != cudaSuccess ? (int)rc : CRANE_NOALLOC_NO_SYMBOL;
+        g_scratch_addr[dev] = p;
+    }
+    *out = g_scratch_addr[dev];
+    return 0;
+}
+}  // namespace
+
+CRANE_API const char* crane_noalloc_strerror(int code) {
+    switch (code) {
+        case 0: return "ok";
+        case CRANE_NOALLOC_TOO_LARGE:
+            return "n_entries * nq * n_splits * (d + 2) floats exceed the library's built-in scratch "
+                   "array (CRANE_NOALLOC_SCRATCH_FLOATS = 1048576 floats): use fewer slices, fewer "
+                   "entries per call, or the entry point that takes the caller's scratch buffers";
+        case CRANE_NOALLOC_BAD_ARGUMENT:
+            return "an argument is out of range (head size or head grouping without a kernel, "
+                   "n_splits < 1, or a device ordinal beyond 63)";
+        case CRANE_NOALLOC_NO_SYMBOL:
+            return "the device address of the built-in scratch array could not be found";
+    }
+    return "a CUDA error (positive codes are cudaError_t values)";
+}
+
+CRANE_API int crane_paged_decode_attention_noalloc(const void* q, void* out, const void* k_pool,
+                                                   const void* v_pool, const int* cu_q,
+                                                   const int* kv_len, const int* block_table,
+                                                   int max_blocks, int num_pages, int page_size,
+                                                   int n_entries, int nq, int nkv, int d, int window,
+                                                   float scale, int n_splits, int* err,
+                                                   cudaStream_t stream) {
+    if (n_entries <= 0) return 0;
+    if (!crane_paged_decode_attention_supports(d, nq, nkv) || n_splits < 1)
+        return CRANE_NOALLOC_BAD_ARGUMENT;
+    float* part_o = nullptr;
+    float* part_ml = nullptr;
+    if (n_splits > 1) {
+        const long long slots = (long long)n_entries * nq * n_splits;
+        if (slots * (d + 2) > (long long)CRANE_NOALLOC_SCRATCH_FLOATS) return CRANE_NOALLOC_TOO_LARGE;
+        float* base = nullptr;
+        const int rc = scratch_address(&base);
+        if (rc != 0) return rc;
+        part_o = base;                   // [slots][d]
+        part_ml = base + slots * d;      // [slots][2]
+    }
+    return crane_paged_decode_attention(q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len,
+                                        block_table, max_blocks, num_pages, page_size, n_entries, nq,
+                                        nkv, d, window, scale, n_splits, err, stream);
 }
