@@ -52,6 +52,7 @@ def _host():
             "crane_cache_length": ([P, L], I),
             "crane_cache_slot": ([P, L], I),
             "crane_cache_block_table": ([P, L, I, P, I], I),
+            "crane_cache_fill_step": ([P, I, P, P, P, I, I, I, I, I, P, P], I),
             "crane_cache_free_pages": ([P, I], I),
             "crane_cache_total_pages": ([P, I], I),
             "crane_cache_free_slots": ([P], I),
@@ -143,6 +144,20 @@ class PageTable:
         out = np.empty(capacity, dtype=np.int32)
         self.block_table_into(rid, group, out)
         return out
+
+    def fill_step(self, ids: np.ndarray, counts: np.ndarray, meta: np.ndarray, off_positions: int,
+                  off_tok_entry: int, off_cu_q: int, off_kv_len: int, off_slots: int,
+                  off_tables: np.ndarray, max_blocks: np.ndarray) -> int:
+        """One native call that writes positions, entry of each token, cu_q,
+        kv_len, slots and every group's block-table rows of a step into the
+        int32 block ``meta``.  Returns the number of tokens."""
+        n = self._lib.crane_cache_fill_step(
+            self._h, len(ids), ids.ctypes.data, counts.ctypes.data, meta.ctypes.data, off_positions,
+            off_tok_entry, off_cu_q, off_kv_len, off_slots, off_tables.ctypes.data,
+            max_blocks.ctypes.data)
+        if n < 0:
+            raise CacheError("a request of the step is not live")
+        return n
 
     def free_pages(self, group: int = 0) -> int:
         return self._lib.crane_cache_free_pages(self._h, group)

@@ -1,7 +1,8 @@
 // Attention of single decoded tokens over the paged cache (bf16), split along
 // the keys.  One CTA takes one (slice of the keys, kv head, request); its four
-// warps take 32-key tiles of the slice in turn, each keeping its own running
-// softmax, and merge at the end.  All query heads that share the kv head ride
+// warps take 32-key tiles of the slice in turn (each warp with its own ring of
+// three tile stages fed by cp.async), each keeping its own running softmax, and
+// merge at the end.  All query heads that share the kv head ride
 // in the rows of one MMA tile, so every key and value is read once per group
 // (the reference's decode path groups the same way:
 // crane-core/src/models/hunyuan_dense/modeling.rs:575-608).  With more than one
@@ -18,6 +19,7 @@ using namespace attn;
 
 constexpr int TILE = 32;
 constexpr int WARPS = 4;
+constexpr int NSTAGE = 3;        // tiles of K and V per warp in shared memory: one in use, two on the way
 
 template <int D>
 __global__ void __launch_bounds__(WARPS * 32)
@@ -34,6 +36,8 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     constexpr int DN = D / 8;                      // n-tiles of the output
     extern __shared__ __align__(16) uint8_t smem[];
 
+    pdl_launch_dependents();
+    pdl_wait();                                    // q and this step's keys come from the kernel before
     const int split = blockIdx.x, g = blockIdx.y, e = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_rep = nq / nkv;
@@ -48,8 +52,8 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     const int tile_begin = first_tile + split * per_split;
     const int tile_end = min(first_tile + n_tiles, tile_begin + per_split);
 
-    // this warp's two stages of (K tile, V tile)
-    const uint32_t wbase = smem_u32(smem) + warp * 4 * TILE_BYTES;
+    // this warp's ring of (K tile, V tile) stages
+    const uint32_t wbase = smem_u32(smem) + warp * NSTAGE * 2 * TILE_BYTES;
 
     // query rows: row r of the MMA tile is query head g * n_rep + r
     uint32_t qf[KS][4];
@@ -74,25 +78,31 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     bool bad_page = false;
 
     int ti = tile_begin + warp;
-    if (ti < tile_end) {
-        load_tile_async<D, TILE>(wbase, k_pool, table, num_pages, page_size, nkv, g, ti * TILE, lo,
-                                 pos, lane, bad_page);
-        load_tile_async<D, TILE>(wbase + TILE_BYTES, v_pool, table, num_pages, page_size, nkv, g,
-                                 ti * TILE, lo, pos, lane, bad_page);
+#pragma unroll
+    for (int s = 0; s < NSTAGE - 1; ++s) {
+        const int tj = ti + s * WARPS;
+        if (tj < tile_end) {
+            const uint32_t st = wbase + s * 2 * TILE_BYTES;
+            load_tile_async<D, TILE>(st, k_pool, table, num_pages, page_size, nkv, g, tj * TILE, lo,
+                                     pos, lane, bad_page);
+            load_tile_async<D, TILE>(st + TILE_BYTES, v_pool, table, num_pages, page_size, nkv, g,
+                                     tj * TILE, lo, pos, lane, bad_page);
+        }
+        cp_async_commit();
     }
-    cp_async_commit();
     for (int it = 0; ti < tile_end; ti += WARPS, ++it) {
-        const uint32_t kt = wbase + (it & 1) * 2 * TILE_BYTES, vt = kt + TILE_BYTES;
-        const int nxt = ti + WARPS;
+        const uint32_t kt = wbase + (it % NSTAGE) * 2 * TILE_BYTES, vt = kt + TILE_BYTES;
+        const int nxt = ti + (NSTAGE - 1) * WARPS;
         if (nxt < tile_end) {
-            const uint32_t nk = wbase + ((it + 1) & 1) * 2 * TILE_BYTES;
+            // the stage that the previous iteration finished with
+            const uint32_t nk = wbase + ((it + NSTAGE - 1) % NSTAGE) * 2 * TILE_BYTES;
             load_tile_async<D, TILE>(nk, k_pool, table, num_pages, page_size, nkv, g, nxt * TILE, lo,
                                      pos, lane, bad_page);
             load_tile_async<D, TILE>(nk + TILE_BYTES, v_pool, table, num_pages, page_size, nkv, g,
                                      nxt * TILE, lo, pos, lane, bad_page);
         }
         cp_async_commit();
-        cp_async_wait<1>();
+        cp_async_wait<NSTAGE - 1>();
         __syncwarp();
 
         // ---- scores: 16 rows x 32 keys ----
@@ -222,6 +232,8 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     __nv_bfloat16* __restrict__ out, const int* __restrict__ cu_q,
                                     int nq, int d, int n_splits) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int e = blockIdx.x, h = blockIdx.y;
     const long long base = ((long long)e * nq + h) * n_splits;
     float M = -INFINITY;
@@ -244,7 +256,7 @@ int launch_decode(const void* q, void* out, float* part_o, float* part_ml, const
                   const void* v_pool, const int* cu_q, const int* kv_len, const int* block_table,
                   int max_blocks, int num_pages, int page_size, int n_entries, int nq, int nkv,
                   int window, float scale, int n_splits, int* err, cudaStream_t st) {
-    constexpr int tiles = WARPS * 4 * TILE * Tile<D>::ROW_BYTES;
+    constexpr int tiles = WARPS * NSTAGE * 2 * TILE * Tile<D>::ROW_BYTES;
     constexpr int merge = WARPS * 16 * (D + 2) * 4;
     constexpr int smem = tiles > merge ? tiles : merge;
     auto kern = paged_decode_attn_kernel<D>;
@@ -255,16 +267,14 @@ int launch_decode(const void* q, void* out, float* part_o, float* part_ml, const
         configured = true;
     }
     dim3 grid(n_splits, nkv, n_entries);
-    kern<<<grid, WARPS * 32, smem, st>>>(
-        (const __nv_bfloat16*)q, (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)k_pool,
-        (const __nv_bfloat16*)v_pool, cu_q, kv_len, block_table, max_blocks, num_pages, page_size, nq,
-        nkv, window, scale * 1.4426950408889634f, n_splits, err);
-    int rc = crane_launch_status();
-    if (rc == 0 && n_splits > 1) {
-        decode_merge_kernel<<<dim3(n_entries, nq), 64, 0, st>>>(part_o, part_ml, (__nv_bfloat16*)out,
-                                                               cu_q, nq, D, n_splits);
-        rc = crane_launch_status();
-    }
+    int rc = crane_launch(kern, grid, dim3(WARPS * 32), smem, st, (const __nv_bfloat16*)q,
+                          (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)k_pool,
+                          (const __nv_bfloat16*)v_pool, cu_q, kv_len, block_table, max_blocks, num_pages,
+                          page_size, nq, nkv, window, scale * 1.4426950408889634f, n_splits, err);
+    if (rc == 0 && n_splits > 1)
+        rc = crane_launch(decode_merge_kernel, dim3(n_entries, nq), dim3(64), 0, st,
+                          (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, cu_q, nq, D,
+                          n_splits);
     return rc;
 }
 }  // namespace

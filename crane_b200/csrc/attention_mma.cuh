@@ -76,6 +76,28 @@ __device__ __forceinline__ void load_tile_async(uint32_t tile, const __nv_bfloat
     // `lane` is the thread's index among the THREADS that copy the tile together
     constexpr int CH = Tile<D>::CHUNKS;
     static_assert(ROWS * CH % THREADS == 0, "the tile must divide among the copying threads");
+    if (page_size % ROWS == 0) {
+        // tiles start at multiples of ROWS, so the whole tile lies in one page: one look-up
+        const bool wanted = key0 <= hi && key0 + ROWS - 1 >= lo;
+        const __nv_bfloat16* base = pool;
+        bool ok = false;
+        if (wanted) {
+            const int page = table[key0 / page_size];
+            ok = page >= 0 && page < num_pages;
+            if (!ok) bad_page = true;
+            else base = pool + (((long long)page * nkv + g) * page_size + key0 % page_size) * D;
+        }
+#pragma unroll
+        for (int i = 0; i < ROWS * CH / THREADS; ++i) {
+            const int c = i * THREADS + lane;
+            const int row = c / CH, col = c % CH;
+            const int j = key0 + row;
+            const bool in = ok && j >= lo && j <= hi;
+            cp_async16(tile + row * Tile<D>::ROW_BYTES + col * 16,
+                       in ? base + row * D + col * 8 : pool, in ? 16 : 0);
+        }
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < ROWS * CH / THREADS; ++i) {
         const int c = i * THREADS + lane;

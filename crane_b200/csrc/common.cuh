@@ -48,4 +48,35 @@ __device__ __forceinline__ float block_sum(float v, float* scratch32) {
     return warp_sum(t);
 }
 
+// Programmatic dependent launch: a kernel launched with the attribute may start
+// while the kernel before it in the stream is still running.  It must not touch
+// anything that kernel (or one before it) writes or reads-then-overwrites until
+// it has called pdl_wait(), which returns once all earlier kernels are complete
+// and their writes visible.  pdl_launch_dependents() lets the NEXT kernel start
+// early in the same way.  Without the attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 static inline int crane_launch_status() { return (int)cudaGetLastError(); }
+
+// 1: kernels of a decoder step are launched with programmatic dependent launch.
+extern int g_crane_pdl;
+
+template <typename... KArgs, typename... Args>
+static inline int crane_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                               cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_crane_pdl ? 1 : 0;
+    const cudaError_t rc = cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+    return rc != cudaSuccess ? (int)rc : (int)cudaGetLastError();
+}

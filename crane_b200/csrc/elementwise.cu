@@ -11,6 +11,10 @@
 // (crane-core/src/models/hunyuan_dense/modeling.rs:541-555).
 #include "common.cuh"
 
+int g_crane_pdl = 1;
+
+CRANE_API void crane_set_pdl(int on) { g_crane_pdl = on ? 1 : 0; }
+
 // A GEMM result is either one tensor of T or `n_parts` float partial sums
 // (split-K), laid out [part][row][col]; readers add the partials in a fixed
 // order and round once to T, so that both forms give the same value.
@@ -32,6 +36,8 @@ struct GemmOut {
 template <typename T>
 __global__ void embed_gather_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                                     float* __restrict__ x, int hidden, int vocab, int* err) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     int tok = tokens[t];
     if (tok < 0 || tok >= vocab) {
@@ -48,30 +54,52 @@ __global__ void embed_gather_kernel(const int* __restrict__ tokens, const T* __r
 // rows == nullptr: row = r = blockIdx.x, x is updated in place.
 // rows != nullptr: row = rows[r]; x is left untouched (used for the final norm
 // over the wanted positions only).
-template <typename T>
+// A thread keeps its up to PER elements of the row in registers between the
+// sum of squares and the scaling, so the row is read once.
+template <typename T, int PER>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, GemmOut<T> delta, int has_delta,
                                    const float* __restrict__ w, const int* __restrict__ rows,
                                    T* __restrict__ out, int hidden, float eps) {
     __shared__ float scratch[32];
     const int r = blockIdx.x;
-    const int row = rows ? rows[r] : r;
+    const int row = rows ? rows[r] : r;          // written by the host's copy, long before
     float* xr = x + (long long)row * hidden;
     const long long dbase = (long long)row * hidden;
     const bool write_x = (rows == nullptr) && has_delta;
+    float v[PER], wv[PER];
     float ss = 0.f;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        float v = xr[c];
-        if (has_delta) v += delta.load(dbase + c);
-        if (write_x) xr[c] = v;
-        ss += v * v;
+    pdl_launch_dependents();
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {                 // the norm's weight depends on no earlier kernel
+        const int c = threadIdx.x + k * blockDim.x;
+        wv[k] = c < hidden ? w[c] : 0.f;
+    }
+    pdl_wait();
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        v[k] = c < hidden ? xr[c] : 0.f;
+    }
+    if (has_delta) {
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const int c = threadIdx.x + k * blockDim.x;
+            if (c < hidden) v[k] += delta.load(dbase + c);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (write_x && c < hidden) xr[c] = v[k];
+        ss += v[k] * v[k];
     }
     const float total = block_sum(ss, scratch);
     const float rstd = rsqrtf(total / (float)hidden + eps);
     T* o = out + (long long)r * hidden;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        float v = xr[c];
-        if (has_delta && !write_x) v += delta.load(dbase + c);
-        o[c] = from_f32<T>(v * rstd * w[c]);
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < hidden) o[c] = from_f32<T>(v[k] * rstd * wv[k]);
     }
 }
 
@@ -92,6 +120,8 @@ __global__ void rope_norm_cache_kernel(GemmOut<T> qkv, int qkv_stride,
                                        T* __restrict__ v_pool, int num_pages, int page_size,
                                        int n_tokens, int nq, int nkv, int d, int has_kv,
                                        int rotary, int* err) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int heads = nq + (has_kv ? 2 * nkv : 0);
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -174,6 +204,8 @@ __global__ void rope_norm_cache_kernel(GemmOut<T> qkv, int qkv_stride,
 // gu rows hold [gate (inter) | up (inter)].
 template <typename T>
 __global__ void silu_mul_kernel(GemmOut<T> gu, T* __restrict__ out, long long n_rows, int inter) {
+    pdl_launch_dependents();
+    pdl_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_rows * inter) return;
     const long long r = i / inter;
@@ -199,9 +231,8 @@ __global__ void to_float_kernel(const T* __restrict__ in, float* __restrict__ ou
 CRANE_API int crane_embed_gather(int dtype, const int* tokens, const void* table, float* x,
                                  int n_tokens, int hidden, int vocab, int* err, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
-    DISPATCH_T(dtype, (embed_gather_kernel<T><<<n_tokens, 256, 0, st>>>(
-        tokens, (const T*)table, x, hidden, vocab, err)));
-    return crane_launch_status();
+    DISPATCH_T(dtype, return crane_launch(embed_gather_kernel<T>, dim3(n_tokens), dim3(256), 0, st, tokens,
+                                          (const T*)table, x, hidden, vocab, err));
 }
 
 CRANE_API int crane_add_rmsnorm(int dtype, float* x, const void* delta, const float* delta_parts,
@@ -210,13 +241,22 @@ CRANE_API int crane_add_rmsnorm(int dtype, float* x, const void* delta, const fl
                                 cudaStream_t st) {
     if (n_rows <= 0) return 0;
     const int has_delta = (delta != nullptr || delta_parts != nullptr) ? 1 : 0;
-    const int threads = hidden >= 2048 ? 512 : 256;
+    // 4 elements per thread up to 4096 wide, then more per thread at 1024 threads
+    int per = 4;
+    while (per < 32 && (hidden + per - 1) / per > 1024) per *= 2;
+    if ((hidden + per - 1) / per > 1024) return (int)cudaErrorInvalidValue;    // wider than 32768
+    int threads = ((hidden + per - 1) / per + 31) / 32 * 32;
     DISPATCH_T(dtype, {
         GemmOut<T> d{(const T*)delta, delta_parts, n_parts, part_stride};
-        add_rmsnorm_kernel<T><<<n_rows, threads, 0, st>>>(x, d, has_delta, w, rows, (T*)out,
-                                                          hidden, eps);
+        const dim3 g(n_rows), b(threads);
+        if (per == 4)
+            return crane_launch(add_rmsnorm_kernel<T, 4>, g, b, 0, st, x, d, has_delta, w, rows, (T*)out, hidden, eps);
+        if (per == 8)
+            return crane_launch(add_rmsnorm_kernel<T, 8>, g, b, 0, st, x, d, has_delta, w, rows, (T*)out, hidden, eps);
+        if (per == 16)
+            return crane_launch(add_rmsnorm_kernel<T, 16>, g, b, 0, st, x, d, has_delta, w, rows, (T*)out, hidden, eps);
+        return crane_launch(add_rmsnorm_kernel<T, 32>, g, b, 0, st, x, d, has_delta, w, rows, (T*)out, hidden, eps);
     });
-    return crane_launch_status();
 }
 
 CRANE_API int crane_rope_norm_cache(int dtype, const void* qkv, const float* qkv_parts, int n_parts,
@@ -235,12 +275,11 @@ CRANE_API int crane_rope_norm_cache(int dtype, const void* qkv, const float* qkv
     const int blocks = (int)((warps * 32 + threads - 1) / threads);
     DISPATCH_T(dtype, {
         GemmOut<T> src{(const T*)qkv, qkv_parts, n_parts, part_stride};
-        rope_norm_cache_kernel<T><<<blocks, threads, 0, st>>>(
-            src, qkv_stride, positions, tok_entry, block_table, max_blocks, cos_tab, sin_tab,
-            table_len, q_norm_w, k_norm_w, eps, (T*)q_out, (T*)k_pool, (T*)v_pool, num_pages,
-            page_size, n_tokens, nq, nkv, d, has_kv, rotary, err);
+        return crane_launch(rope_norm_cache_kernel<T>, dim3(blocks), dim3(threads), 0, st, src, qkv_stride,
+                            positions, tok_entry, block_table, max_blocks, cos_tab, sin_tab, table_len,
+                            q_norm_w, k_norm_w, eps, (T*)q_out, (T*)k_pool, (T*)v_pool, num_pages,
+                            page_size, n_tokens, nq, nkv, d, has_kv, rotary, err);
     });
-    return crane_launch_status();
 }
 
 CRANE_API int crane_silu_mul(int dtype, const void* gu, const float* gu_parts, int n_parts,
@@ -251,9 +290,9 @@ CRANE_API int crane_silu_mul(int dtype, const void* gu, const float* gu_parts, i
     const int blocks = (int)((n + 255) / 256);
     DISPATCH_T(dtype, {
         GemmOut<T> src{(const T*)gu, gu_parts, n_parts, part_stride};
-        silu_mul_kernel<T><<<blocks, 256, 0, st>>>(src, (T*)out, n_rows, inter);
+        return crane_launch(silu_mul_kernel<T>, dim3(blocks), dim3(256), 0, st, src, (T*)out,
+                            (long long)n_rows, inter);
     });
-    return crane_launch_status();
 }
 
 CRANE_API int crane_to_float(int dtype, const void* in, float* out, long long n, cudaStream_t st) {

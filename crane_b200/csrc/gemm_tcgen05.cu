@@ -14,6 +14,9 @@
 // With split_k > 1 every slice writes its float partial sums [slice][row][col]
 // and the consumer adds them (see GemmOut in elementwise.cu).
 //
+// Launched with programmatic dependent launch: the first tiles of the weights
+// are requested before the kernel waits for its predecessor (see the producer).
+//
 // Every wait on an mbarrier is bounded: when it runs out the kernel records
 // CRANE_ERR_WAIT_TIMEOUT, all roles leave their loops, tensor memory is freed
 // and the kernel returns.
@@ -167,9 +170,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
+    pdl_launch_dependents();
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer ----------------
-        for (int i = 0; i < num_kb; ++i) {
+        // The weights (A when transposed, else B) depend on no earlier kernel: their
+        // first tiles are requested before waiting for the kernel that produces the
+        // activations, so the stream of weights starts while that kernel still runs.
+        const int pre = min(num_kb, STAGES);
+        for (int i = 0; i < pre; ++i) {
+            const uint32_t bar = smem_u32(&full[i]);
+            mbar_expect_tx(bar, A_BYTES + B_BYTES);
+            const int k0 = (kb_begin + i) * BK;
+            if (TRANSPOSED) tma_load_2d(smem_u32(smem_a + i * A_BYTES), &map_a, bar, k0, a0);
+            else tma_load_2d(smem_u32(smem_b + i * B_BYTES), &map_b, bar, k0, b0);
+        }
+        pdl_wait();
+        for (int i = 0; i < pre; ++i) {
+            const uint32_t bar = smem_u32(&full[i]);
+            const int k0 = (kb_begin + i) * BK;
+            if (TRANSPOSED) tma_load_2d(smem_u32(smem_b + i * B_BYTES), &map_b, bar, k0, b0);
+            else tma_load_2d(smem_u32(smem_a + i * A_BYTES), &map_a, bar, k0, a0);
+        }
+        for (int i = pre; i < num_kb; ++i) {
             const int s = i % STAGES;
             const uint32_t parity = ((i / STAGES) & 1) ^ 1;
             if (!mbar_wait(smem_u32(&empty[s]), parity, abort_flag)) break;
@@ -334,8 +356,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
             return (int)cudaGetLastError();
         configured = true;
     }
-    kern<<<grid, NUM_THREADS, smem, st>>>(ma, mb, p);
-    return crane_launch_status();
+    return crane_launch(kern, grid, dim3(NUM_THREADS), smem, st, ma, mb, p);
 }
 
 template <bool OUT_F32, bool TRANSPOSED>

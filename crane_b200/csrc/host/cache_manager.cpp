@@ -126,6 +126,35 @@ int CacheManager::block_table(int64_t id, int g, int32_t* out, int capacity) con
     return (int)b.size();
 }
 
+int CacheManager::fill_step(int n, const int64_t* ids, const int32_t* counts, int32_t* meta,
+                            int off_positions, int off_tok_entry, int off_cu_q, int off_kv_len,
+                            int off_slots, const int32_t* off_tables, const int32_t* max_blocks) const {
+    int row = 0;
+    meta[off_cu_q] = 0;
+    for (int i = 0; i < n; ++i) {
+        auto it = reqs_.find(ids[i]);
+        if (it == reqs_.end()) return -2;
+        const Request& r = it->second;
+        const int c = counts[i], start = r.len - c;
+        for (int t = 0; t < c; ++t) {
+            meta[off_positions + row + t] = start + t;
+            meta[off_tok_entry + row + t] = i;
+        }
+        row += c;
+        meta[off_cu_q + i + 1] = row;
+        meta[off_kv_len + i] = r.len;
+        meta[off_slots + i] = r.slot;
+        for (size_t g = 0; g < groups_.size(); ++g) {
+            int32_t* out = meta + off_tables[g] + (long long)i * max_blocks[g];
+            const auto& b = r.blocks[g];
+            const int m = std::min((int)b.size(), (int)max_blocks[g]);
+            for (int k = 0; k < m; ++k) out[k] = b[k];
+            for (int k = m; k < max_blocks[g]; ++k) out[k] = -1;
+        }
+    }
+    return row;
+}
+
 int CacheManager::check() const {
     std::vector<int> slot_seen(max_requests_, 0);
     for (int s : free_slots_) {
@@ -182,6 +211,13 @@ CRANE_HOST_API int crane_cache_length(void* c, int64_t id) { return ((CacheManag
 CRANE_HOST_API int crane_cache_slot(void* c, int64_t id) { return ((CacheManager*)c)->slot(id); }
 CRANE_HOST_API int crane_cache_block_table(void* c, int64_t id, int g, int32_t* out, int cap) {
     return ((CacheManager*)c)->block_table(id, g, out, cap);
+}
+CRANE_HOST_API int crane_cache_fill_step(void* c, int n, const int64_t* ids, const int32_t* counts,
+                                         int32_t* meta, int off_positions, int off_tok_entry,
+                                         int off_cu_q, int off_kv_len, int off_slots,
+                                         const int32_t* off_tables, const int32_t* max_blocks) {
+    return ((CacheManager*)c)->fill_step(n, ids, counts, meta, off_positions, off_tok_entry, off_cu_q,
+                                         off_kv_len, off_slots, off_tables, max_blocks);
 }
 CRANE_HOST_API int crane_cache_free_pages(void* c, int g) {
     return ((CacheManager*)c)->free_pages(g);

@@ -46,6 +46,16 @@ public:
     // blocks are -1.  Returns the number of logical blocks in use, -2 unknown.
     int block_table(int64_t id, int g, int32_t* out, int capacity) const;
 
+    // Lays out the metadata of one step for `n` live requests whose pages are
+    // already taken: entry i has `counts[i]` new tokens, the last of which sits
+    // at position length(ids[i]) - 1.  Writes into `meta` at the given offsets
+    // (in int32 units): positions and tok_entry per token, cu_q [n + 1], kv_len
+    // and slots per entry, and per group the block-table rows [n][max_blocks[g]].
+    // Returns the number of tokens, or -2 for an unknown id.
+    int fill_step(int n, const int64_t* ids, const int32_t* counts, int32_t* meta, int off_positions,
+                  int off_tok_entry, int off_cu_q, int off_kv_len, int off_slots,
+                  const int32_t* off_tables, const int32_t* max_blocks) const;
+
     int num_groups() const { return (int)groups_.size(); }
     int free_pages(int g) const { return (int)free_[g].size(); }
     int total_pages(int g) const { return groups_[g].num_pages; }

@@ -232,6 +232,11 @@ CRANE_HOST_API int crane_sched_schedule(void* s, int64_t* ids, int32_t* start, i
 CRANE_HOST_API int crane_sched_on_token(void* s, int64_t id, int32_t tok) {
     return (int)((Scheduler*)s)->on_token(id, tok);
 }
+// The tokens sampled for several entries at once; reasons[i] gets the finish reason.
+CRANE_HOST_API void crane_sched_on_tokens(void* s, int n, const int64_t* ids, const int32_t* toks,
+                                          int32_t* reasons) {
+    for (int i = 0; i < n; ++i) reasons[i] = (int)((Scheduler*)s)->on_token(ids[i], toks[i]);
+}
 CRANE_HOST_API int crane_sched_cancel(void* s, int64_t id) { return ((Scheduler*)s)->cancel(id); }
 CRANE_HOST_API int crane_sched_drop(void* s, int64_t id) { return ((Scheduler*)s)->drop(id); }
 CRANE_HOST_API int crane_sched_has_work(void* s) { return ((Scheduler*)s)->has_work() ? 1 : 0; }

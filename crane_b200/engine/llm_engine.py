@@ -106,10 +106,10 @@ class LLMEngine:
             hist = [self.scheduler.tokens(p.request_id) for p in sampled] if need_hist else None
             counters = [self._live[p.request_id].sampled for p in sampled]
             toks = self.sampler.sample(logits, params, hist, counters)
-            for p, tok in zip(sampled, toks):
+            reasons = self.scheduler.on_tokens([p.request_id for p in sampled], toks)
+            for p, tok, reason in zip(sampled, toks, reasons):
                 live = self._live[p.request_id]
                 live.sampled += 1
-                reason = self.scheduler.on_token(p.request_id, tok)
                 out.append((p.request_id, tok, reason))
                 if live.on_token is not None:
                     live.on_token(p.request_id, tok, reason)

@@ -27,6 +27,7 @@ def _host():
             "crane_sched_add": ([P, L, P, I, I, P, I], I),
             "crane_sched_schedule": ([P, P, P, P, P, I, P, I, P], I),
             "crane_sched_on_token": ([P, L, c_int32], I),
+            "crane_sched_on_tokens": ([P, I, P, P, P], None),
             "crane_sched_cancel": ([P, L], I),
             "crane_sched_drop": ([P, L], I),
             "crane_sched_has_work": ([P], I),
@@ -122,6 +123,14 @@ class Scheduler:
 
     def on_token(self, rid: int, token: int) -> Optional[str]:
         return FINISH_REASONS[self._lib.crane_sched_on_token(self._h, rid, int(token))]
+
+    def on_tokens(self, ids: Sequence[int], tokens: Sequence[int]) -> List[Optional[str]]:
+        """``on_token`` for several requests in one native call."""
+        a = np.asarray(ids, dtype=np.int64)
+        t = np.asarray(tokens, dtype=np.int32)
+        r = np.zeros(len(a), dtype=np.int32)
+        self._lib.crane_sched_on_tokens(self._h, len(a), a.ctypes.data, t.ctypes.data, r.ctypes.data)
+        return [FINISH_REASONS[int(v)] for v in r]
 
     def cancel(self, rid: int) -> None:
         self._lib.crane_sched_cancel(self._h, rid)

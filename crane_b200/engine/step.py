@@ -81,6 +81,8 @@ class _MetaBuffers:
             self.bt_off.append(off)
             off += (cap_entries * mb + 3) // 4 * 4
         self.total = off
+        self.bt_off_arr = np.asarray(self.bt_off or [0], dtype=np.int32)
+        self.max_blocks_arr = np.asarray(max_blocks or [0], dtype=np.int32)
         self.host = torch.empty(off, dtype=torch.int32).pin_memory()
         self.np = self.host.numpy()
         self.dev = torch.zeros(off, dtype=torch.int32, device=device)
@@ -228,44 +230,38 @@ class ModelRunner:
             pad_to = self._bucket(n_entries)
         m = self.meta
         m.copied.synchronize()                      # the last step's copy has left the host block
-        real_entries, real_tokens = n_entries, n_tokens
+        real_entries = n_entries
+        ids = np.fromiter((e.request_id for e in entries), dtype=np.int64, count=n_entries)
+        cnt = np.asarray(counts, dtype=np.int32)
         if pad_to:
-            entries = list(entries) + [entries[0]] * (pad_to - n_entries)
-            arrays = arrays + [arrays[0]] * (pad_to - n_entries)
-            counts = counts + [1] * (pad_to - n_entries)
-            n_entries = n_tokens = pad_to
-        tok = m.view("tokens", n_tokens, False)
-        pos = m.view("positions", n_tokens, False)
-        ent = m.view("tok_entry", n_tokens, False)
+            extra = pad_to - n_entries
+            ids = np.concatenate([ids, np.full(extra, ids[0], dtype=np.int64)])
+            cnt = np.concatenate([cnt, np.ones(extra, dtype=np.int32)])
+            arrays = arrays + [arrays[0]] * extra
+            n_entries = pad_to
+        # one native call lays out positions, entry of each token, cu_q, kv_len, slots, block tables
+        n_tokens = self.table.fill_step(ids, cnt, m.np, m.off["positions"], m.off["tok_entry"],
+                                        m.off["cu_q"], m.off["kv_len"], m.off["slots"], m.bt_off_arr,
+                                        m.max_blocks_arr)
+        m.view("tokens", n_tokens, False)[:] = arrays[0] if len(arrays) == 1 else np.concatenate(arrays)
         cu = m.view("cu_q", n_entries + 1, False)
         kvl = m.view("kv_len", n_entries, False)
         slots = m.view("slots", n_entries, False)
-        want_rows: List[int] = []
-        row = 0
-        cu[0] = 0
-        for i, (e, c) in enumerate(zip(entries, counts)):
-            after = self.table.length(e.request_id)
-            start = after - c
-            tok[row:row + c] = arrays[i]
-            pos[row:row + c] = np.arange(start, after, dtype=np.int32)
-            ent[row:row + c] = i
-            want_rows.extend(row + w for w in e.want)
-            row += c
-            cu[i + 1] = row
-            kvl[i] = after
-            slots[i] = self.table.slot(e.request_id)
-            for g in range(self.num_groups):
-                self.table.block_table_into(e.request_id, g, m.table(g, n_entries, False)[i])
-        n_want = len(want_rows)
-        if n_want:
-            m.view("want_rows", n_want, False)[:] = np.asarray(want_rows, dtype=np.int32)
+        if pad_to:
+            n_want = pad_to
+            m.view("want_rows", n_want, False)[:] = np.arange(n_want, dtype=np.int32)
+        else:
+            want_rows = [int(cu[i]) + w for i, e in enumerate(entries) for w in e.want]
+            n_want = len(want_rows)
+            if n_want:
+                m.view("want_rows", n_want, False)[:] = np.asarray(want_rows, dtype=np.int32)
         m.dev.copy_(m.host, non_blocking=True)
         m.copied.record()
 
         ctx = StepContext()
         ctx.graph_bucket, ctx.real_entries = pad_to, real_entries
         ctx.n_tokens, ctx.n_entries, ctx.n_want = n_tokens, n_entries, n_want
-        ctx.max_q_len = max(counts)
+        ctx.max_q_len = int(cnt.max())
         ctx.max_kv_len = int(kvl.max())
         ctx.max_positions = self.max_seq_len
         ctx.tokens = m.view("tokens", n_tokens, True)

@@ -8,6 +8,7 @@ raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional, Union
 
@@ -87,6 +88,10 @@ class Kernels:
             fn = getattr(self.lib, name)
             fn.argtypes = sig
             fn.restype = c_int
+        # kernels of a step overlap their start with the end of the kernel before them
+        self.lib.crane_set_pdl.argtypes = [c_int]
+        self.lib.crane_set_pdl.restype = None
+        self.lib.crane_set_pdl(0 if os.environ.get("CRANE_PDL", "1") == "0" else 1)
 
     @staticmethod
     def _stream(t: torch.Tensor) -> int:
