@@ -240,6 +240,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (both numbers are reported)")
     ap.add_argument("--impl", default="crane_b200")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
+    ap.add_argument("--only-prefill", action="store_true",
+                    help="measure the 2,048-token prefill alone (for profiling); prints its record only")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -261,8 +263,17 @@ def main():
     need_tokens = max(need_tokens, args.batch * (args.context + args.steps + args.warmup + 64))
     opts = dict(page_size=page, num_pages=need_tokens // page + 64, max_concurrent=max(64, args.batch),
                 max_seq_len=args.context + 1024, max_batched_tokens=2048, chunk_size=2048)
+    if args.only_prefill:
+        opts.update(num_pages=2048 // page + 8, max_concurrent=4)
     model = build_model(cfg, opts)
     runner = model.runner
+    if args.only_prefill:
+        pms = time_prefill(model, 2048, vocab, reps=max(1, args.steps))
+        flops = prefill_flops(cfg, layers, 2048)
+        print(json.dumps({"prefill": {"value": round(2048 * 1000.0 / pms, 1), "tokens": 2048,
+                                      "ms": round(pms, 3), "layers": layers,
+                                      "frac": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}}))
+        return 0
 
     def decode_point(batch):
         ids = fill_cache(model, batch, args.context)

@@ -15,6 +15,15 @@ int g_crane_pdl = 1;
 
 CRANE_API void crane_set_pdl(int on) { g_crane_pdl = on ? 1 : 0; }
 
+__device__ __forceinline__ float2 ld2(const float* p) { return *(const float2*)p; }
+__device__ __forceinline__ float2 ld2(const __nv_bfloat16* p) {
+    return __bfloat1622float2(*(const __nv_bfloat162*)p);
+}
+__device__ __forceinline__ void st2(float* p, float a, float b) { *(float2*)p = make_float2(a, b); }
+__device__ __forceinline__ void st2(__nv_bfloat16* p, float a, float b) {
+    *(__nv_bfloat162*)p = __floats2bfloat162_rn(a, b);
+}
+
 // A GEMM result is either one tensor of T or `n_parts` float partial sums
 // (split-K), laid out [part][row][col]; readers add the partials in a fixed
 // order and round once to T, so that both forms give the same value.
@@ -29,6 +38,17 @@ struct GemmOut {
         float s = 0.f;
         for (int i = 0; i < n_parts; ++i) s += parts[(long long)i * part_stride + idx];
         return to_f32(from_f32<T>(s));
+    }
+    // two neighbours at once; idx even and the tensors' rows evenly long
+    __device__ __forceinline__ float2 load2(long long idx) const {
+        if (parts == nullptr) return ld2(whole + idx);
+        float2 s = make_float2(0.f, 0.f);
+        for (int i = 0; i < n_parts; ++i) {
+            const float2 p = *(const float2*)(parts + (long long)i * part_stride + idx);
+            s.x += p.x;
+            s.y += p.y;
+        }
+        return make_float2(to_f32(from_f32<T>(s.x)), to_f32(from_f32<T>(s.y)));
     }
 };
 
@@ -103,11 +123,63 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, GemmOut<T> delta, int 
     }
 }
 
+// The same, two neighbouring elements per step (rows of even length).
+template <typename T, int PER>
+__global__ void add_rmsnorm2_kernel(float* __restrict__ x, GemmOut<T> delta, int has_delta,
+                                    const float* __restrict__ w, const int* __restrict__ rows,
+                                    T* __restrict__ out, int hidden, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int row = rows ? rows[r] : r;
+    float* xr = x + (long long)row * hidden;
+    const long long dbase = (long long)row * hidden;
+    const bool write_x = (rows == nullptr) && has_delta;
+    float2 v[PER], wv[PER];
+    float ss = 0.f;
+    pdl_launch_dependents();
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+        const int c = 2 * (threadIdx.x + k * blockDim.x);
+        wv[k] = c < hidden ? ld2(w + c) : make_float2(0.f, 0.f);
+    }
+    pdl_wait();
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+        const int c = 2 * (threadIdx.x + k * blockDim.x);
+        v[k] = c < hidden ? ld2(xr + c) : make_float2(0.f, 0.f);
+    }
+    if (has_delta) {
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const int c = 2 * (threadIdx.x + k * blockDim.x);
+            if (c < hidden) {
+                const float2 d = delta.load2(dbase + c);
+                v[k].x += d.x;
+                v[k].y += d.y;
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+        const int c = 2 * (threadIdx.x + k * blockDim.x);
+        if (write_x && c < hidden) st2(xr + c, v[k].x, v[k].y);
+        ss += v[k].x * v[k].x + v[k].y * v[k].y;
+    }
+    const float total = block_sum(ss, scratch);
+    const float rstd = rsqrtf(total / (float)hidden + eps);
+    T* o = out + (long long)r * hidden;
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+        const int c = 2 * (threadIdx.x + k * blockDim.x);
+        if (c < hidden) st2(o + c, v[k].x * rstd * wv[k].x, v[k].y * rstd * wv[k].y);
+    }
+}
+
 // ------------------------------------- rotary + per-head norm + cache write
 // One warp per (token, head).  Heads 0..nq-1 are queries, then nkv keys, then
 // nkv values (values are only copied).  `qkv` rows hold [q | k | v]; with
 // has_kv == 0 they hold q alone (a layer that reads another layer's cache).
-template <typename T>
+template <typename T, bool PAIRS>
 __global__ void rope_norm_cache_kernel(GemmOut<T> qkv, int qkv_stride,
                                        const int* __restrict__ positions,
                                        const int* __restrict__ tok_entry,
@@ -149,7 +221,14 @@ __global__ void rope_norm_cache_kernel(GemmOut<T> qkv, int qkv_stride,
         T* pool = is_v ? v_pool : k_pool;
         dst = pool + (((long long)page * nkv + g) * page_size + pos % page_size) * d;
         if (is_v) {
-            for (int c = lane; c < d; c += 32) dst[c] = from_f32<T>(qkv.load(src + c));
+            if (PAIRS) {
+                for (int c = 2 * lane; c < d; c += 64) {
+                    const float2 x = qkv.load2(src + c);
+                    st2(dst + c, x.x, x.y);
+                }
+            } else {
+                for (int c = lane; c < d; c += 32) dst[c] = from_f32<T>(qkv.load(src + c));
+            }
             return;
         }
         nw = k_norm_w;
@@ -157,6 +236,47 @@ __global__ void rope_norm_cache_kernel(GemmOut<T> qkv, int qkv_stride,
     if (rotate && (pos < 0 || pos >= table_len)) {
         if (lane == 0) atomicOr(err, CRANE_ERR_POSITION_RANGE);
         rotate = false;
+    }
+    if (PAIRS) {
+        // each lane owns j, j + 1 and their partners j + d/2, j + 1 + d/2 for j = 2 lane, 2 lane + 64, ...
+        constexpr int MAXP2 = 4;                  // d <= 512
+        float2 a2[MAXP2], b2[MAXP2];
+        float ss2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < MAXP2; ++i) {
+            const int j = 2 * lane + 64 * i;
+            a2[i] = b2[i] = make_float2(0.f, 0.f);
+            if (j < half) {
+                const float2 x1 = qkv.load2(src + j), x2 = qkv.load2(src + j + half);
+                if (rotate) {
+                    const float2 c = ld2(cos_tab + (long long)pos * half + j);
+                    const float2 sn = ld2(sin_tab + (long long)pos * half + j);
+                    a2[i] = make_float2(x1.x * c.x - x2.x * sn.x, x1.y * c.y - x2.y * sn.y);
+                    b2[i] = make_float2(x2.x * c.x + x1.x * sn.x, x2.y * c.y + x1.y * sn.y);
+                } else {
+                    a2[i] = x1;
+                    b2[i] = x2;
+                }
+                ss2 += a2[i].x * a2[i].x + a2[i].y * a2[i].y + b2[i].x * b2[i].x + b2[i].y * b2[i].y;
+            }
+        }
+        float rstd2 = 1.f;
+        if (nw != nullptr) rstd2 = rsqrtf(warp_sum(ss2) / (float)d + eps);
+#pragma unroll
+        for (int i = 0; i < MAXP2; ++i) {
+            const int j = 2 * lane + 64 * i;
+            if (j < half) {
+                float2 y1 = a2[i], y2 = b2[i];
+                if (nw != nullptr) {
+                    const float2 w1 = ld2(nw + j), w2 = ld2(nw + j + half);
+                    y1 = make_float2(y1.x * rstd2 * w1.x, y1.y * rstd2 * w1.y);
+                    y2 = make_float2(y2.x * rstd2 * w2.x, y2.y * rstd2 * w2.y);
+                }
+                st2(dst + j, y1.x, y1.y);
+                st2(dst + j + half, y2.x, y2.y);
+            }
+        }
+        return;
     }
     // each lane owns the pairs (j, j + d/2) for j = lane, lane + 32, ...
     constexpr int MAXP = 8;                       // d <= 512
@@ -215,6 +335,28 @@ __global__ void silu_mul_kernel(GemmOut<T> gu, T* __restrict__ out, long long n_
     out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
 }
 
+// The same for whole bf16 rows, eight neighbours per thread (inter % 8 == 0).
+__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu,
+                                       __nv_bfloat16* __restrict__ out, int inter) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c >= inter) return;
+    const long long r = blockIdx.y;
+    const uint4 g4 = *(const uint4*)(gu + r * 2 * inter + c);
+    const uint4 u4 = *(const uint4*)(gu + r * 2 * inter + inter + c);
+    const __nv_bfloat162* g2 = (const __nv_bfloat162*)&g4;
+    const __nv_bfloat162* u2 = (const __nv_bfloat162*)&u4;
+    uint4 o4;
+    __nv_bfloat162* o2 = (__nv_bfloat162*)&o4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 g = __bfloat1622float2(g2[i]), u = __bfloat1622float2(u2[i]);
+        o2[i] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+    }
+    *(uint4*)(out + r * inter + c) = o4;
+}
+
 // a T tensor to float (logits of a bf16 head, test helpers)
 template <typename T>
 __global__ void to_float_kernel(const T* __restrict__ in, float* __restrict__ out, long long n) {
@@ -246,6 +388,21 @@ CRANE_API int crane_add_rmsnorm(int dtype, float* x, const void* delta, const fl
     while (per < 32 && (hidden + per - 1) / per > 1024) per *= 2;
     if ((hidden + per - 1) / per > 1024) return (int)cudaErrorInvalidValue;    // wider than 32768
     int threads = ((hidden + per - 1) / per + 31) / 32 * 32;
+    const bool aligned = ((uintptr_t)x | (uintptr_t)delta | (uintptr_t)delta_parts | (uintptr_t)w |
+                          (uintptr_t)out) % 8 == 0 && part_stride % 2 == 0;
+    if (hidden % 2 == 0 && hidden <= 8192 && aligned) {
+        // pairs of neighbours: 2 or 4 pairs per thread
+        const int pp = hidden <= 4096 ? 2 : 4;
+        const int th = ((hidden / 2 + pp - 1) / pp + 31) / 32 * 32;
+        DISPATCH_T(dtype, {
+            GemmOut<T> d{(const T*)delta, delta_parts, n_parts, part_stride};
+            if (pp == 2)
+                return crane_launch(add_rmsnorm2_kernel<T, 2>, dim3(n_rows), dim3(th), 0, st, x, d, has_delta, w,
+                                    rows, (T*)out, hidden, eps);
+            return crane_launch(add_rmsnorm2_kernel<T, 4>, dim3(n_rows), dim3(th), 0, st, x, d, has_delta, w,
+                                rows, (T*)out, hidden, eps);
+        });
+    }
     DISPATCH_T(dtype, {
         GemmOut<T> d{(const T*)delta, delta_parts, n_parts, part_stride};
         const dim3 g(n_rows), b(threads);
@@ -275,10 +432,20 @@ CRANE_API int crane_rope_norm_cache(int dtype, const void* qkv, const float* qkv
     const int blocks = (int)((warps * 32 + threads - 1) / threads);
     DISPATCH_T(dtype, {
         GemmOut<T> src{(const T*)qkv, qkv_parts, n_parts, part_stride};
-        return crane_launch(rope_norm_cache_kernel<T>, dim3(blocks), dim3(threads), 0, st, src, qkv_stride,
-                            positions, tok_entry, block_table, max_blocks, cos_tab, sin_tab, table_len,
-                            q_norm_w, k_norm_w, eps, (T*)q_out, (T*)k_pool, (T*)v_pool, num_pages,
-                            page_size, n_tokens, nq, nkv, d, has_kv, rotary, err);
+        // two neighbours per load when every row starts on an even element and 8-byte boundary
+        const bool pairs = d % 4 == 0 && qkv_stride % 2 == 0 && part_stride % 2 == 0 &&
+                           ((uintptr_t)qkv | (uintptr_t)qkv_parts | (uintptr_t)q_out | (uintptr_t)k_pool |
+                            (uintptr_t)v_pool | (uintptr_t)cos_tab | (uintptr_t)sin_tab |
+                            (uintptr_t)q_norm_w | (uintptr_t)k_norm_w) % 8 == 0;
+        if (pairs)
+            return crane_launch(rope_norm_cache_kernel<T, true>, dim3(blocks), dim3(threads), 0, st, src,
+                                qkv_stride, positions, tok_entry, block_table, max_blocks, cos_tab, sin_tab,
+                                table_len, q_norm_w, k_norm_w, eps, (T*)q_out, (T*)k_pool, (T*)v_pool,
+                                num_pages, page_size, n_tokens, nq, nkv, d, has_kv, rotary, err);
+        return crane_launch(rope_norm_cache_kernel<T, false>, dim3(blocks), dim3(threads), 0, st, src,
+                            qkv_stride, positions, tok_entry, block_table, max_blocks, cos_tab, sin_tab,
+                            table_len, q_norm_w, k_norm_w, eps, (T*)q_out, (T*)k_pool, (T*)v_pool,
+                            num_pages, page_size, n_tokens, nq, nkv, d, has_kv, rotary, err);
     });
 }
 
@@ -288,6 +455,10 @@ CRANE_API int crane_silu_mul(int dtype, const void* gu, const float* gu_parts, i
     if (n_rows <= 0) return 0;
     const long long n = (long long)n_rows * inter;
     const int blocks = (int)((n + 255) / 256);
+    if (dtype == 1 && gu != nullptr && inter % 8 == 0 && n_rows <= 65535 &&
+        ((uintptr_t)gu | (uintptr_t)out) % 16 == 0)
+        return crane_launch(silu_mul_bf16x8_kernel, dim3((inter / 8 + 127) / 128, n_rows), dim3(128), 0, st,
+                            (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter);
     DISPATCH_T(dtype, {
         GemmOut<T> src{(const T*)gu, gu_parts, n_parts, part_stride};
         return crane_launch(silu_mul_kernel<T>, dim3(blocks), dim3(256), 0, st, src, (T*)out,

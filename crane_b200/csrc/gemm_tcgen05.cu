@@ -114,7 +114,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
 
 struct GemmParams {
     int rows_a, rows_b, k;          // extents
-    int kb_per_split;               // k-blocks per slice
     void* out;                      // bf16 or float, see template flags
     long long ld_out;               // elements between consecutive rows of the output
     long long split_stride;         // elements between consecutive slices (split_k > 1)
@@ -143,10 +142,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int a0 = blockIdx.x * BM, b0 = blockIdx.y * BN;
+    // the k-blocks are dealt out to the slices as evenly as they go
     const int num_kb_total = (p.k + BK - 1) / BK;
-    const int kb_begin = blockIdx.z * p.kb_per_split;
-    const int kb_end = min(num_kb_total, kb_begin + p.kb_per_split);
-    const int num_kb = max(0, kb_end - kb_begin);
+    const int kb_begin = (int)(((long long)blockIdx.z * num_kb_total) / gridDim.z);
+    const int kb_end = (int)(((long long)(blockIdx.z + 1) * num_kb_total) / gridDim.z);
+    const int num_kb = kb_end - kb_begin;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -396,9 +396,8 @@ CRANE_API int crane_gemm_bf16_tcgen05(const void* A, const void* B, const float*
     if (split_k > num_kb) split_k = num_kb;
     GemmParams p;
     p.rows_a = rows_a; p.rows_b = rows_b; p.k = k;
-    p.kb_per_split = (num_kb + split_k - 1) / split_k;
     p.out = out; p.ld_out = ld_out; p.split_stride = split_stride; p.bias = bias; p.err = err;
-    dim3 grid((rows_a + BM - 1) / BM, (rows_b + bn - 1) / bn, (num_kb + p.kb_per_split - 1) / p.kb_per_split);
+    dim3 grid((rows_a + BM - 1) / BM, (rows_b + bn - 1) / bn, split_k);
     if (out_f32)
         return transposed ? dispatch_bn<true, true>(bn, ma, mb, p, grid, st)
                           : dispatch_bn<true, false>(bn, ma, mb, p, grid, st);

@@ -167,11 +167,25 @@ class Kernels:
 
     @staticmethod
     def split_plan(k: int, want: int):
-        """(k-blocks per slice, slices) for a requested number of slices."""
+        """(k-blocks of the shortest slice, slices) for a requested number of
+        slices: at most one slice per 64-wide k-block."""
         num_kb = (k + 63) // 64
-        want = max(1, min(want, num_kb))
-        per = (num_kb + want - 1) // want
-        return per, (num_kb + per - 1) // per
+        slices = max(1, min(want, num_kb))
+        return num_kb // slices, slices
+
+    @staticmethod
+    def slices_for(tiles: int, k: int, sms: int, max_waves: int = 3) -> int:
+        """How many slices of the inner dimension make ``tiles`` output tiles fill
+        the device's SMs best: the fewest slices among those whose last wave of
+        CTAs is (nearly) as full as it gets."""
+        num_kb = (k + 63) // 64
+        best, best_eff = 1, 0.0
+        for s in range(1, min(num_kb, max(1, (max_waves * sms) // max(1, tiles))) + 1):
+            ctas = tiles * s
+            eff = ctas / (-(-ctas // sms) * sms)
+            if eff > best_eff + 0.02:
+                best, best_eff = s, eff
+        return best
 
     def gemm_tcgen05(self, x, w, bias, out, err, split_k: int = 1, swap: bool = False,
                      bn: int = 128) -> None:

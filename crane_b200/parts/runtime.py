@@ -80,7 +80,7 @@ class Runtime:
                 # dimension is cut into slices until every SM has a tile to stream
                 bn = 16 if M <= 16 else 32 if M <= 32 else 64
                 tiles = (N + 127) // 128
-                _, slices = k.split_plan(K, max(1, (self.num_sms + tiles - 1) // tiles))
+                slices = k.slices_for(tiles, K, self.num_sms)
                 if slices > 1:
                     parts = self.ws.get("splitk:" + str(N), slices * self.split_rows, N,
                                         torch.float32, cap=slices * self.split_rows)
