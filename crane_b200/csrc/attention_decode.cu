@@ -1,5 +1,5 @@
 // Attention of single decoded tokens over the paged cache (bf16), split along
-// the keys.  One CTA takes one (slice of the keys, kv head, request); its four
+// the keys.  One CTA takes one (slice of the keys, kv head, request); its
 // warps take 32-key tiles of the slice in turn (each warp with its own ring of
 // three tile stages fed by cp.async), each keeping its own running softmax, and
 // merge at the end.  All query heads that share the kv head ride
@@ -18,7 +18,7 @@ namespace {
 using namespace attn;
 
 constexpr int TILE = 32;
-constexpr int WARPS = 4;
+constexpr int WARPS = 2;         // 2 warps x 3 stages: 104 KB at head size 128, two CTAs (or a product's CTA) per SM
 constexpr int NSTAGE = 3;        // tiles of K and V per warp in shared memory: one in use, two on the way
 
 template <int D>
@@ -185,7 +185,7 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     l[0] = quad_sum(l[0]);
     l[1] = quad_sum(l[1]);
 
-    // ---- merge the four warps ----
+    // ---- merge the warps ----
     __syncthreads();                                 // every warp is done with its tiles
     float* sm_o = (float*)smem;                      // [WARPS][16][D]
     float* sm_ml = sm_o + WARPS * 16 * D;            // [WARPS][16][2]

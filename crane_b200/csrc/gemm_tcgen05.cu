@@ -363,9 +363,11 @@ template <bool OUT_F32, bool TRANSPOSED>
 int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid,
                 cudaStream_t st) {
     switch (bn) {
-        case 16: return launch<16, 8, OUT_F32, TRANSPOSED>(ma, mb, p, grid, st);
-        case 32: return launch<32, 8, OUT_F32, TRANSPOSED>(ma, mb, p, grid, st);
-        case 64: return launch<64, 8, OUT_F32, TRANSPOSED>(ma, mb, p, grid, st);
+        // the narrow tiles keep their shared memory under half an SM's, so that the CTAs of
+        // the next product can move in beside them and request their weights early
+        case 16: return launch<16, 6, OUT_F32, TRANSPOSED>(ma, mb, p, grid, st);
+        case 32: return launch<32, 5, OUT_F32, TRANSPOSED>(ma, mb, p, grid, st);
+        case 64: return launch<64, 4, OUT_F32, TRANSPOSED>(ma, mb, p, grid, st);
         case 128: return launch<128, 6, OUT_F32, TRANSPOSED>(ma, mb, p, grid, st);
         case 256: return launch<256, 4, OUT_F32, TRANSPOSED>(ma, mb, p, grid, st);
     }
