@@ -21,7 +21,98 @@ constexpr int TILE = 32;
 constexpr int WARPS = 2;         // 2 warps x 3 stages: 104 KB at head size 128, two CTAs (or a product's CTA) per SM
 constexpr int NSTAGE = 3;        // tiles of K and V per warp in shared memory: one in use, two on the way
 
+// The fused form takes the step's q, k and v raw from the product that made
+// them and does, inside the attention kernel, what rope_norm_cache_kernel does
+// for a decode step: rotary encoding, per-head RMSNorm, and the write of the new
+// key and value into their page (crane-core/src/models/hunyuan_dense/
+// modeling.rs:541-557).  Every CTA prepares the query rows of its group itself;
+// the warp whose tile holds the new position prepares the new key and value,
+// puts them into its tile in shared memory and into the page.
+struct FusedArgs {
+    const __nv_bfloat16* qkv;       // rows [q | k | v] of the step's tokens, or null when they
+    const float* qkv_parts;         // come as float partial sums [part][row][col]
+    int n_parts;
+    long long part_stride;
+    int qkv_stride;
+    int has_kv;                     // 0: the layer reads another layer's cache and writes nothing
+    int rotary;
+    const float* cos_tab;
+    const float* sin_tab;
+    int table_len;
+    const float* q_norm_w;          // [D] or null
+    const float* k_norm_w;
+    float eps;
+    __nv_bfloat16* k_pool_w;        // the pools again, writable
+    __nv_bfloat16* v_pool_w;
+    int* counters;                  // [entries * kv heads], zero between launches: slices done per group
+};
+
+__device__ __forceinline__ float2 raw2(const FusedArgs& a, long long idx) {
+    if (a.qkv_parts == nullptr) return __bfloat1622float2(*(const __nv_bfloat162*)(a.qkv + idx));
+    float2 s = make_float2(0.f, 0.f);
+    for (int i = 0; i < a.n_parts; ++i) {
+        const float2 p = *(const float2*)(a.qkv_parts + (long long)i * a.part_stride + idx);
+        s.x += p.x;
+        s.y += p.y;
+    }
+    // rounded once to bf16, like a product that was written out whole
+    return __bfloat1622float2(__floats2bfloat162_rn(s.x, s.y));
+}
+
+// One head row of D elements at `src`: rotary encoding at position pos, then
+// RMSNorm with weight nw (if any); lane owns the neighbours j, j + 1 and their
+// partners in the second half.  Results (rounded to bf16) go to dst0 and, if
+// given, dst1.
 template <int D>
+__device__ __forceinline__ void rope_norm_row(const FusedArgs& a, long long src, int pos, bool rotate,
+                                              const float* nw, int lane, __nv_bfloat16* dst0,
+                                              __nv_bfloat16* dst1) {
+    constexpr int HALF = D / 2;
+    constexpr int IT = (HALF + 63) / 64;
+    float2 x1[IT], x2[IT];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < IT; ++i) {
+        const int j = 2 * lane + 64 * i;
+        x1[i] = x2[i] = make_float2(0.f, 0.f);
+        if (j < HALF) {
+            const float2 u = raw2(a, src + j), v = raw2(a, src + j + HALF);
+            if (rotate) {
+                const float2 c = *(const float2*)(a.cos_tab + (long long)pos * HALF + j);
+                const float2 sn = *(const float2*)(a.sin_tab + (long long)pos * HALF + j);
+                x1[i] = make_float2(u.x * c.x - v.x * sn.x, u.y * c.y - v.y * sn.y);
+                x2[i] = make_float2(v.x * c.x + u.x * sn.x, v.y * c.y + u.y * sn.y);
+            } else {
+                x1[i] = u;
+                x2[i] = v;
+            }
+            ss += x1[i].x * x1[i].x + x1[i].y * x1[i].y + x2[i].x * x2[i].x + x2[i].y * x2[i].y;
+        }
+    }
+    float rstd = 1.f;
+    if (nw != nullptr) rstd = rsqrtf(warp_sum(ss) / (float)D + a.eps);
+#pragma unroll
+    for (int i = 0; i < IT; ++i) {
+        const int j = 2 * lane + 64 * i;
+        if (j < HALF) {
+            float2 y1 = x1[i], y2 = x2[i];
+            if (nw != nullptr) {
+                const float2 w1 = *(const float2*)(nw + j), w2 = *(const float2*)(nw + j + HALF);
+                y1 = make_float2(y1.x * rstd * w1.x, y1.y * rstd * w1.y);
+                y2 = make_float2(y2.x * rstd * w2.x, y2.y * rstd * w2.y);
+            }
+            const __nv_bfloat162 b1 = __floats2bfloat162_rn(y1.x, y1.y), b2 = __floats2bfloat162_rn(y2.x, y2.y);
+            *(__nv_bfloat162*)(dst0 + j) = b1;
+            *(__nv_bfloat162*)(dst0 + j + HALF) = b2;
+            if (dst1 != nullptr) {
+                *(__nv_bfloat162*)(dst1 + j) = b1;
+                *(__nv_bfloat162*)(dst1 + j + HALF) = b2;
+            }
+        }
+    }
+}
+
+template <int D, bool FUSED>
 __global__ void __launch_bounds__(WARPS * 32)
 paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                          float* __restrict__ part_o, float* __restrict__ part_ml,
@@ -29,7 +120,7 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
                          const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ cu_q,
                          const int* __restrict__ kv_len, const int* __restrict__ block_table,
                          int max_blocks, int num_pages, int page_size, int nq, int nkv, int window,
-                         float scale_log2, int n_splits, int* err) {
+                         float scale_log2, int n_splits, int* err, const FusedArgs fa) {
     constexpr int RB = Tile<D>::ROW_BYTES;
     constexpr int TILE_BYTES = TILE * RB;
     constexpr int KS = D / 16;                     // k-steps of q k^T
@@ -57,7 +148,28 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
 
     // query rows: row r of the MMA tile is query head g * n_rep + r
     uint32_t qf[KS][4];
-    {
+    bool bad_page = false;
+    bool rotate = FUSED && fa.rotary != 0;
+    if (FUSED) {
+        if (rotate && (pos < 0 || pos >= fa.table_len)) {
+            if (threadIdx.x == 0) atomicOr(err, CRANE_ERR_POSITION_RANGE);
+            rotate = false;
+        }
+        // the group's query rows, encoded and normalised here, staged in shared memory
+        __nv_bfloat16* q_s = (__nv_bfloat16*)(smem + WARPS * NSTAGE * 2 * TILE_BYTES);   // [16][D]
+        for (int i = threadIdx.x; i < 16 * D / 2; i += WARPS * 32) ((uint32_t*)q_s)[i] = 0u;
+        __syncthreads();
+        for (int r = warp; r < n_rep; r += WARPS)
+            rope_norm_row<D>(fa, (long long)t * fa.qkv_stride + (long long)(g * n_rep + r) * D, pos, rotate,
+                             fa.q_norm_w, lane, q_s + r * D, nullptr);
+        __syncthreads();
+        const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                qf[ks][i] = *(const uint32_t*)(q_s + (r0 + (i & 1) * 8) * D + ks * 16 + c0 + (i >> 1) * 8);
+    } else {
         const int r0 = lane >> 2, c0 = (lane & 3) * 2;
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
@@ -71,11 +183,13 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
             }
         }
     }
+    // keys that are read from the pages: the new position's row is made here when fused
+    const bool makes_kv = FUSED && fa.has_kv != 0;
+    const int hi = makes_kv ? pos - 1 : pos;
     float o[DN][4];
 #pragma unroll
     for (int i = 0; i < DN; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    bool bad_page = false;
 
     int ti = tile_begin + warp;
 #pragma unroll
@@ -84,9 +198,9 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
         if (tj < tile_end) {
             const uint32_t st = wbase + s * 2 * TILE_BYTES;
             load_tile_async<D, TILE>(st, k_pool, table, num_pages, page_size, nkv, g, tj * TILE, lo,
-                                     pos, lane, bad_page);
+                                     hi, lane, bad_page);
             load_tile_async<D, TILE>(st + TILE_BYTES, v_pool, table, num_pages, page_size, nkv, g,
-                                     tj * TILE, lo, pos, lane, bad_page);
+                                     tj * TILE, lo, hi, lane, bad_page);
         }
         cp_async_commit();
     }
@@ -97,13 +211,36 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
             // the stage that the previous iteration finished with
             const uint32_t nk = wbase + ((it + NSTAGE - 1) % NSTAGE) * 2 * TILE_BYTES;
             load_tile_async<D, TILE>(nk, k_pool, table, num_pages, page_size, nkv, g, nxt * TILE, lo,
-                                     pos, lane, bad_page);
+                                     hi, lane, bad_page);
             load_tile_async<D, TILE>(nk + TILE_BYTES, v_pool, table, num_pages, page_size, nkv, g,
-                                     nxt * TILE, lo, pos, lane, bad_page);
+                                     nxt * TILE, lo, hi, lane, bad_page);
         }
         cp_async_commit();
         cp_async_wait<NSTAGE - 1>();
         __syncwarp();
+        if (makes_kv && ti == pos / TILE) {
+            // this tile holds the new position: its key (encoded, normalised) and value are
+            // made here, for the tile in shared memory and for the page
+            const int page = table[pos / page_size];
+            if (page < 0 || page >= num_pages) {
+                bad_page = true;
+            } else {
+                const long long prow = (((long long)page * nkv + g) * page_size + pos % page_size) * D;
+                uint8_t* stage = smem + (size_t)(warp * NSTAGE + it % NSTAGE) * 2 * TILE_BYTES;
+                __nv_bfloat16* k_row = (__nv_bfloat16*)(stage + (pos % TILE) * RB);
+                __nv_bfloat16* v_row = (__nv_bfloat16*)(stage + TILE_BYTES + (pos % TILE) * RB);
+                const long long row_src = (long long)t * fa.qkv_stride;
+                rope_norm_row<D>(fa, row_src + (long long)(nq + g) * D, pos, rotate, fa.k_norm_w, lane, k_row,
+                                 fa.k_pool_w + prow);
+                for (int c = 2 * lane; c < D; c += 64) {
+                    const float2 x = raw2(fa, row_src + (long long)(nq + nkv + g) * D + c);
+                    const __nv_bfloat162 b = __floats2bfloat162_rn(x.x, x.y);
+                    *(__nv_bfloat162*)(v_row + c) = b;
+                    *(__nv_bfloat162*)(fa.v_pool_w + prow + c) = b;
+                }
+            }
+            __syncwarp();
+        }
 
         // ---- scores: 16 rows x 32 keys ----
         float s[4][4];
@@ -226,6 +363,35 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
             if (c == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
         }
     }
+    if (FUSED && n_splits > 1 && fa.counters != nullptr) {
+        // the CTA that finishes its group's last slice merges all of them, in slice order
+        __shared__ int ticket;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) ticket = atomicAdd(fa.counters + e * nkv + g, 1);
+        __syncthreads();
+        if (ticket == n_splits - 1) {
+            __threadfence();
+            for (int r = 0; r < n_rep; ++r) {
+                const int h = g * n_rep + r;
+                const long long base = ((long long)e * nq + h) * n_splits;
+                float M = -INFINITY;
+                for (int sp = 0; sp < n_splits; ++sp) M = fmaxf(M, __ldcg(part_ml + (base + sp) * 2));
+                const float mb = (M == -INFINITY) ? 0.f : M;
+                float L = 0.f;
+                for (int sp = 0; sp < n_splits; ++sp)
+                    L += exp2f(__ldcg(part_ml + (base + sp) * 2) - mb) * __ldcg(part_ml + (base + sp) * 2 + 1);
+                const float inv = L > 0.f ? 1.f / L : 0.f;
+                for (int c = threadIdx.x; c < D; c += WARPS * 32) {
+                    float O = 0.f;
+                    for (int sp = 0; sp < n_splits; ++sp)
+                        O += exp2f(__ldcg(part_ml + (base + sp) * 2) - mb) * __ldcg(part_o + (base + sp) * D + c);
+                    out[((long long)t * nq + h) * D + c] = __float2bfloat16_rn(O * inv);
+                }
+            }
+            if (threadIdx.x == 0) fa.counters[e * nkv + g] = 0;      // ready for the next launch
+        }
+    }
 }
 
 // out[t, h, :] = sum_s w_s o_s / sum_s w_s l_s with w_s = exp2(m_s - max m)
@@ -251,15 +417,15 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
     }
 }
 
-template <int D>
+template <int D, bool FUSED>
 int launch_decode(const void* q, void* out, float* part_o, float* part_ml, const void* k_pool,
                   const void* v_pool, const int* cu_q, const int* kv_len, const int* block_table,
                   int max_blocks, int num_pages, int page_size, int n_entries, int nq, int nkv,
-                  int window, float scale, int n_splits, int* err, cudaStream_t st) {
-    constexpr int tiles = WARPS * NSTAGE * 2 * TILE * Tile<D>::ROW_BYTES;
+                  int window, float scale, int n_splits, int* err, const FusedArgs& fa, cudaStream_t st) {
+    constexpr int tiles = WARPS * NSTAGE * 2 * TILE * Tile<D>::ROW_BYTES + (FUSED ? 16 * D * 2 : 0);
     constexpr int merge = WARPS * 16 * (D + 2) * 4;
     constexpr int smem = tiles > merge ? tiles : merge;
-    auto kern = paged_decode_attn_kernel<D>;
+    auto kern = paged_decode_attn_kernel<D, FUSED>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
@@ -270,8 +436,9 @@ int launch_decode(const void* q, void* out, float* part_o, float* part_ml, const
     int rc = crane_launch(kern, grid, dim3(WARPS * 32), smem, st, (const __nv_bfloat16*)q,
                           (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)k_pool,
                           (const __nv_bfloat16*)v_pool, cu_q, kv_len, block_table, max_blocks, num_pages,
-                          page_size, nq, nkv, window, scale * 1.4426950408889634f, n_splits, err);
-    if (rc == 0 && n_splits > 1)
+                          page_size, nq, nkv, window, scale * 1.4426950408889634f, n_splits, err, fa);
+    const bool merged_inside = FUSED && fa.counters != nullptr;
+    if (rc == 0 && n_splits > 1 && !merged_inside)
         rc = crane_launch(decode_merge_kernel, dim3(n_entries, nq), dim3(64), 0, st,
                           (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, cu_q, nq, D,
                           n_splits);
@@ -297,11 +464,47 @@ CRANE_API int crane_paged_decode_attention(const void* q, void* out, float* part
     if (n_entries <= 0) return 0;
     if (!crane_paged_decode_attention_supports(d, nq, nkv) || n_splits < 1)
         return (int)cudaErrorInvalidValue;
+    const FusedArgs none = {};
 #define CASE(DD)                                                                                  \
     case DD:                                                                                      \
-        return launch_decode<DD>(q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len, block_table, \
-                                 max_blocks, num_pages, page_size, n_entries, nq, nkv, window, scale, \
-                                 n_splits, err, st);
+        return launch_decode<DD, false>(q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len,       \
+                                        block_table, max_blocks, num_pages, page_size, n_entries, nq, \
+                                        nkv, window, scale, n_splits, err, none, st);
+    switch (d) {
+        CASE(16) CASE(32) CASE(48) CASE(64) CASE(128)
+    }
+#undef CASE
+    return (int)cudaErrorInvalidValue;
+}
+
+// The fused form: q, k and v of the step's tokens come raw from the product
+// (`qkv` whole, or `qkv_parts` as n_parts float partial sums), one row of
+// [q | k | v] (q alone when has_kv == 0) per token.  The kernel encodes and
+// normalises them, writes the new key and value into their pages, attends, and
+// merges the slices itself (`counters`: entries * kv heads ints, zero before the
+// first launch; the kernel leaves them zero).  Head sizes must be multiples of 4.
+CRANE_API int crane_paged_decode_attention_fused(
+    const void* qkv, const float* qkv_parts, int n_parts, long long part_stride, int qkv_stride,
+    int has_kv, int rotary, const float* cos_tab, const float* sin_tab, int table_len,
+    const float* q_norm_w, const float* k_norm_w, float eps, void* out, float* part_o, float* part_ml,
+    int* counters, void* k_pool, void* v_pool, const int* cu_q, const int* kv_len,
+    const int* block_table, int max_blocks, int num_pages, int page_size, int n_entries, int nq, int nkv,
+    int d, int window, float scale, int n_splits, int* err, cudaStream_t st) {
+    if (n_entries <= 0) return 0;
+    if (!crane_paged_decode_attention_supports(d, nq, nkv) || n_splits < 1 || (d & 3) ||
+        (qkv_stride & 1) || (part_stride & 1) || (n_splits > 1 && counters == nullptr))
+        return (int)cudaErrorInvalidValue;
+    FusedArgs fa;
+    fa.qkv = (const __nv_bfloat16*)qkv; fa.qkv_parts = qkv_parts; fa.n_parts = n_parts;
+    fa.part_stride = part_stride; fa.qkv_stride = qkv_stride; fa.has_kv = has_kv; fa.rotary = rotary;
+    fa.cos_tab = cos_tab; fa.sin_tab = sin_tab; fa.table_len = table_len; fa.q_norm_w = q_norm_w;
+    fa.k_norm_w = k_norm_w; fa.eps = eps; fa.k_pool_w = (__nv_bfloat16*)k_pool;
+    fa.v_pool_w = (__nv_bfloat16*)v_pool; fa.counters = counters;
+#define CASE(DD)                                                                                  \
+    case DD:                                                                                      \
+        return launch_decode<DD, true>(nullptr, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len,  \
+                                       block_table, max_blocks, num_pages, page_size, n_entries, nq,  \
+                                       nkv, window, scale, n_splits, err, fa, st);
     switch (d) {
         CASE(16) CASE(32) CASE(48) CASE(64) CASE(128)
     }

@@ -85,19 +85,34 @@ class GqaAttention(Part):
         n = h.shape[0]
         k = rt.kernels
         qkv = rt.linear(h, self.qkv_w, self.qkv_b, "attn_qkv")
-        q = rt.ws.get("attn_q", n, self.nq * self.d, rt.dtype)
         cos = sin = None
         if self.position is not None:
             cos, sin = self.position.tables(rt, ctx.max_positions)
         table = ctx.block_tables[cache.group]
+        o = rt.ws.get("attn_o", n, self.nq * self.d, rt.dtype)
+        decode = (not rt.exact and ctx.max_q_len == 1 and n == ctx.n_entries
+                  and k.decode_attention_supports(self.d, self.nq, self.nkv))
+        if decode and self.d % 4 == 0:
+            # single decoded tokens: rotary encoding, head norms, the cache write, attention over
+            # key slices (enough of them to fill the device) and their merge, all in one kernel
+            splits = max(1, min(32, (2 * rt.num_sms) // max(1, ctx.n_entries * self.nkv)))
+            rows = rt.max_decode_rows * self.nq * 32
+            part_o = rt.ws.get("attn_part_o", rows, self.d, torch.float32, cap=rows)
+            part_ml = rt.ws.get("attn_part_ml", rows, 2, torch.float32, cap=rows)
+            counters = rt.ws.zeros("attn_counters", rt.max_decode_rows * self.nkv, 1, torch.int32)
+            k.paged_decode_attention_fused(qkv, self.qkv_cols, self.own_kv, cos, sin, self.q_norm,
+                                           self.k_norm, self.eps, o, cache.k, cache.v, ctx.cu_q,
+                                           ctx.kv_len, table, cache.page_size, self.nq, self.nkv,
+                                           self.d, self.window, self.scale, splits, part_o, part_ml,
+                                           counters, rt.err)
+            rt.launches += 1
+            return rt.linear(o, self.o_w, self.o_b, "attn_out")
+        q = rt.ws.get("attn_q", n, self.nq * self.d, rt.dtype)
         k.rope_norm_cache(qkv, self.qkv_cols, rt.dtype, ctx.positions, ctx.tok_entry, table, cos,
                           sin, self.q_norm, self.k_norm, self.eps, q, cache.k, cache.v,
                           cache.page_size, self.nq, self.nkv, self.d, self.own_kv,
                           self.position is not None, rt.err)
-        o = rt.ws.get("attn_o", n, self.nq * self.d, rt.dtype)
-        if (not rt.exact and ctx.max_q_len == 1 and n == ctx.n_entries
-                and k.decode_attention_supports(self.d, self.nq, self.nkv)):
-            # single decoded tokens: keys split over enough CTAs to fill the device
+        if decode:
             splits = max(1, min(32, (2 * rt.num_sms) // max(1, ctx.n_entries * self.nkv)))
             part_o = part_ml = None
             if splits > 1:

@@ -136,5 +136,17 @@ class Workspace:
             self._bufs[key] = buf
         return buf[:rows]
 
+    def zeros(self, name: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
+        """A buffer that starts as zeros and is never replaced (counters that
+        kernels leave at zero)."""
+        key = (name, cols, dtype)
+        buf = self._bufs.get(key)
+        if buf is None or buf.shape[0] < rows:
+            if buf is not None:
+                self.generation += 1
+            buf = torch.zeros((rows, cols), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[:rows]
+
     def nbytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._bufs.values())

@@ -442,3 +442,59 @@ def test_paged_prefill_attention_mixed_batch(K, err, d, nq, nkv, page_size, wind
             assert rel_err(out[row].cpu().view(nq, d), want) < 1.5e-2, (e, i)
             row += 1
     assert rel_err(out[45].cpu().view(nq, d)[0], vs[1][far, 0].double()) < 2e-2
+
+
+@pytest.mark.parametrize("d,nq,nkv,page_size,window,splits,qk_norm,parts", [
+    (128, 16, 4, 64, 0, 9, True, 0), (128, 16, 4, 64, 0, 1, True, 3), (64, 8, 8, 16, 0, 3, False, 0),
+    (16, 4, 2, 8, 0, 2, True, 2), (32, 8, 2, 16, 50, 4, True, 0), (48, 6, 3, 32, 0, 32, False, 5)])
+def test_fused_decode_attention_equals_the_separate_kernels(K, err, d, nq, nkv, page_size, window,
+                                                            splits, qk_norm, parts):
+    """Rotary encoding, head norms, cache write, attention and merge in one
+    kernel against rope_norm_cache + paged_decode_attention: same outputs, same
+    keys and values in the pages.  Requests end at the first, a middle and the
+    last row of a tile and of a page."""
+    from crane_b200.kernels import Partials
+    torch.manual_seed(d + splits)
+    lens = [1, 32, 33, 64, 65, 700, 1024]           # cached length after the step
+    n = len(lens)
+    ks = [torch.randn(m, nkv, d).bfloat16().float() for m in lens]
+    vs = [torch.randn(m, nkv, d).bfloat16().float() for m in lens]
+    k_pool, v_pool, table = paged_cache(ks, vs, page_size, torch.bfloat16, seed=splits)
+    cols = (nq + 2 * nkv) * d
+    qkv = torch.randn(n, cols, device=DEV)
+    if parts:
+        p = torch.randn(parts, n, cols, device=DEV)
+        p[0] += qkv - p.sum(0)
+        src, whole = Partials(p), p.sum(0).bfloat16()
+    else:
+        src = whole = qkv.bfloat16()
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    pos, ent, cu, kvl = i32([m - 1 for m in lens]), i32(list(range(n))), i32(list(range(n + 1))), i32(lens)
+    inv = ph.rope_inv_freq(d, 10000.0, 3.0)
+    ang = ph.rope_angles(np.arange(1100), inv).astype(np.float64)
+    cos = torch.from_numpy(np.cos(ang).astype(np.float32)).to(DEV)
+    sin = torch.from_numpy(np.sin(ang).astype(np.float32)).to(DEV)
+    qw = (1 + 0.1 * torch.randn(d)).to(DEV) if qk_norm else None
+    kw = (1 + 0.1 * torch.randn(d)).to(DEV) if qk_norm else None
+    # separate kernels
+    k1, v1 = k_pool.clone(), v_pool.clone()
+    q = torch.empty(n, nq * d, device=DEV, dtype=torch.bfloat16)
+    K.rope_norm_cache(whole, cols, torch.bfloat16, pos, ent, table, cos, sin, qw, kw, 1e-5, q, k1, v1,
+                      page_size, nq, nkv, d, True, True, err)
+    want = torch.empty_like(q)
+    part_o = torch.empty(n * nq * splits * d, device=DEV)
+    part_ml = torch.empty(n * nq * splits * 2, device=DEV)
+    K.paged_decode_attention(q, want, k1, v1, cu, kvl, table, page_size, nq, nkv, d, window, d ** -0.5,
+                             splits, part_o, part_ml, err)
+    # one kernel, twice (the counters must be back at zero after the first call)
+    counters = torch.zeros(n * nkv, dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        k2, v2 = k_pool.clone(), v_pool.clone()
+        got = torch.full_like(q, 9.0)
+        K.paged_decode_attention_fused(src, cols, True, cos, sin, qw, kw, 1e-5, got, k2, v2, cu, kvl, table,
+                                       page_size, nq, nkv, d, window, d ** -0.5, splits, part_o, part_ml,
+                                       counters, err)
+        torch.cuda.synchronize()
+        assert int(err.item()) == 0 and int(counters.abs().sum()) == 0
+        assert torch.equal(k2, k1) and torch.equal(v2, v1)
+        assert rel_err(got, want.double()) < 4e-3
