@@ -128,7 +128,11 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     extern __shared__ __align__(16) uint8_t smem[];
 
     pdl_launch_dependents();
-    pdl_wait();                                    // q and this step's keys come from the kernel before
+    // Keys and values of earlier positions were written by earlier steps; when this kernel makes
+    // the new position's row itself (fused, own cache) it can request its first tiles before the
+    // kernel that produces q, k and v has finished.  Otherwise everything waits for that kernel.
+    const bool early = FUSED && fa.has_kv != 0;
+    if (!early) pdl_wait();
     const int split = blockIdx.x, g = blockIdx.y, e = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_rep = nq / nkv;
@@ -146,9 +150,31 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     // this warp's ring of (K tile, V tile) stages
     const uint32_t wbase = smem_u32(smem) + warp * NSTAGE * 2 * TILE_BYTES;
 
+    bool bad_page = false;
+    // keys that are read from the pages: the new position's row is made here when fused
+    const bool makes_kv = FUSED && fa.has_kv != 0;
+    const int hi = makes_kv ? pos - 1 : pos;
+    float o[DN][4];
+#pragma unroll
+    for (int i = 0; i < DN; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    int ti = tile_begin + warp;
+#pragma unroll
+    for (int s = 0; s < NSTAGE - 1; ++s) {
+        const int tj = ti + s * WARPS;
+        if (tj < tile_end) {
+            const uint32_t st = wbase + s * 2 * TILE_BYTES;
+            load_tile_async<D, TILE>(st, k_pool, table, num_pages, page_size, nkv, g, tj * TILE, lo,
+                                     hi, lane, bad_page);
+            load_tile_async<D, TILE>(st + TILE_BYTES, v_pool, table, num_pages, page_size, nkv, g,
+                                     tj * TILE, lo, hi, lane, bad_page);
+        }
+        cp_async_commit();
+    }
+    if (early) pdl_wait();                         // from here on q, k and v of this step are read
     // query rows: row r of the MMA tile is query head g * n_rep + r
     uint32_t qf[KS][4];
-    bool bad_page = false;
     bool rotate = FUSED && fa.rotary != 0;
     if (FUSED) {
         if (rotate && (pos < 0 || pos >= fa.table_len)) {
@@ -182,27 +208,6 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
                 qf[ks][i] = v;
             }
         }
-    }
-    // keys that are read from the pages: the new position's row is made here when fused
-    const bool makes_kv = FUSED && fa.has_kv != 0;
-    const int hi = makes_kv ? pos - 1 : pos;
-    float o[DN][4];
-#pragma unroll
-    for (int i = 0; i < DN; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-
-    int ti = tile_begin + warp;
-#pragma unroll
-    for (int s = 0; s < NSTAGE - 1; ++s) {
-        const int tj = ti + s * WARPS;
-        if (tj < tile_end) {
-            const uint32_t st = wbase + s * 2 * TILE_BYTES;
-            load_tile_async<D, TILE>(st, k_pool, table, num_pages, page_size, nkv, g, tj * TILE, lo,
-                                     hi, lane, bad_page);
-            load_tile_async<D, TILE>(st + TILE_BYTES, v_pool, table, num_pages, page_size, nkv, g,
-                                     tj * TILE, lo, hi, lane, bad_page);
-        }
-        cp_async_commit();
     }
     for (int it = 0; ti < tile_end; ti += WARPS, ++it) {
         const uint32_t kt = wbase + (it % NSTAGE) * 2 * TILE_BYTES, vt = kt + TILE_BYTES;
@@ -372,22 +377,47 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
         __syncthreads();
         if (ticket == n_splits - 1) {
             __threadfence();
-            for (int r = 0; r < n_rep; ++r) {
-                const int h = g * n_rep + r;
-                const long long base = ((long long)e * nq + h) * n_splits;
+            // weights of the slices, per head: exp2(m_s - max m) / sum, in shared memory
+            float* wgt = (float*)smem;                           // [n_rep][n_splits], tiles are done with
+            const int pairs = n_rep * n_splits;
+            for (int i = threadIdx.x; i < pairs; i += WARPS * 32) {
+                const int r = i / n_splits, sp = i % n_splits;
+                const long long pi = ((long long)e * nq + g * n_rep + r) * n_splits + sp;
+                wgt[i] = __ldcg(part_ml + pi * 2);               // m for now
+                wgt[pairs + i] = __ldcg(part_ml + pi * 2 + 1);   // l
+            }
+            __syncthreads();
+            if (threadIdx.x < n_rep) {
+                const int r = threadIdx.x;
                 float M = -INFINITY;
-                for (int sp = 0; sp < n_splits; ++sp) M = fmaxf(M, __ldcg(part_ml + (base + sp) * 2));
+                for (int sp = 0; sp < n_splits; ++sp) M = fmaxf(M, wgt[r * n_splits + sp]);
                 const float mb = (M == -INFINITY) ? 0.f : M;
                 float L = 0.f;
-                for (int sp = 0; sp < n_splits; ++sp)
-                    L += exp2f(__ldcg(part_ml + (base + sp) * 2) - mb) * __ldcg(part_ml + (base + sp) * 2 + 1);
-                const float inv = L > 0.f ? 1.f / L : 0.f;
-                for (int c = threadIdx.x; c < D; c += WARPS * 32) {
-                    float O = 0.f;
-                    for (int sp = 0; sp < n_splits; ++sp)
-                        O += exp2f(__ldcg(part_ml + (base + sp) * 2) - mb) * __ldcg(part_o + (base + sp) * D + c);
-                    out[((long long)t * nq + h) * D + c] = __float2bfloat16_rn(O * inv);
+                for (int sp = 0; sp < n_splits; ++sp) {
+                    const float f = exp2f(wgt[r * n_splits + sp] - mb);
+                    L += f * wgt[pairs + r * n_splits + sp];
+                    wgt[r * n_splits + sp] = f;
                 }
+                const float inv = L > 0.f ? 1.f / L : 0.f;
+                for (int sp = 0; sp < n_splits; ++sp) wgt[r * n_splits + sp] *= inv;
+            }
+            __syncthreads();
+            for (int idx = threadIdx.x; idx < n_rep * D; idx += WARPS * 32) {
+                const int r = idx / D, c = idx % D;
+                const int h = g * n_rep + r;
+                const float* po = part_o + ((long long)e * nq + h) * n_splits * D + c;
+                float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+                int sp = 0;
+                for (; sp + 4 <= n_splits; sp += 4) {            // four loads in flight at a time
+                    const float v0 = __ldcg(po + (long long)sp * D), v1 = __ldcg(po + (long long)(sp + 1) * D);
+                    const float v2 = __ldcg(po + (long long)(sp + 2) * D), v3 = __ldcg(po + (long long)(sp + 3) * D);
+                    acc0 += wgt[r * n_splits + sp] * v0;
+                    acc1 += wgt[r * n_splits + sp + 1] * v1;
+                    acc2 += wgt[r * n_splits + sp + 2] * v2;
+                    acc3 += wgt[r * n_splits + sp + 3] * v3;
+                }
+                for (; sp < n_splits; ++sp) acc0 += wgt[r * n_splits + sp] * __ldcg(po + (long long)sp * D);
+                out[((long long)t * nq + h) * D + c] = __float2bfloat16_rn((acc0 + acc1) + (acc2 + acc3));
             }
             if (threadIdx.x == 0) fa.counters[e * nkv + g] = 0;      // ready for the next launch
         }
@@ -481,8 +511,8 @@ CRANE_API int crane_paged_decode_attention(const void* q, void* out, float* part
 // (`qkv` whole, or `qkv_parts` as n_parts float partial sums), one row of
 // [q | k | v] (q alone when has_kv == 0) per token.  The kernel encodes and
 // normalises them, writes the new key and value into their pages, attends, and
-// merges the slices itself (`counters`: entries * kv heads ints, zero before the
-// first launch; the kernel leaves them zero).  Head sizes must be multiples of 4.
+// merges the slices itself if `counters` is given (entries * kv heads ints, zero
+// before the first launch; the kernel leaves them zero), else in a second kernel.  Head sizes must be multiples of 4.
 CRANE_API int crane_paged_decode_attention_fused(
     const void* qkv, const float* qkv_parts, int n_parts, long long part_stride, int qkv_stride,
     int has_kv, int rotary, const float* cos_tab, const float* sin_tab, int table_len,
@@ -492,7 +522,7 @@ CRANE_API int crane_paged_decode_attention_fused(
     int d, int window, float scale, int n_splits, int* err, cudaStream_t st) {
     if (n_entries <= 0) return 0;
     if (!crane_paged_decode_attention_supports(d, nq, nkv) || n_splits < 1 || (d & 3) ||
-        (qkv_stride & 1) || (part_stride & 1) || (n_splits > 1 && counters == nullptr))
+        (qkv_stride & 1) || (part_stride & 1))
         return (int)cudaErrorInvalidValue;
     FusedArgs fa;
     fa.qkv = (const __nv_bfloat16*)qkv; fa.qkv_parts = qkv_parts; fa.n_parts = n_parts;

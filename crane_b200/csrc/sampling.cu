@@ -14,7 +14,7 @@
 #include "common.cuh"
 
 namespace {
-constexpr int THREADS = 512;
+constexpr int THREADS = 1024;
 constexpr int MAXK = 64;
 
 __device__ __forceinline__ unsigned long long splitmix64(unsigned long long x) {
@@ -96,9 +96,37 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
     Best b{-INFINITY, 0x7fffffff};
 
     if (!(temp > 0.f)) {                                        // greedy
-        for (int i = threadIdx.x; i < vocab; i += THREADS) {
-            const float v = row[i];
-            if (better(v, i, b)) { b.v = v; b.i = i; }
+        if ((((uintptr_t)row) & 7) == 0) {
+            // pairs of neighbours, four pairs in flight per thread
+            const int pairs = vocab >> 1;
+            const float2* row2 = (const float2*)row;
+            int i = threadIdx.x;
+            for (; i + 3 * THREADS < pairs; i += 4 * THREADS) {
+                const float2 a = row2[i], c = row2[i + THREADS], d = row2[i + 2 * THREADS],
+                             f = row2[i + 3 * THREADS];
+                if (better(a.x, 2 * i, b)) { b.v = a.x; b.i = 2 * i; }
+                if (better(a.y, 2 * i + 1, b)) { b.v = a.y; b.i = 2 * i + 1; }
+                if (better(c.x, 2 * (i + THREADS), b)) { b.v = c.x; b.i = 2 * (i + THREADS); }
+                if (better(c.y, 2 * (i + THREADS) + 1, b)) { b.v = c.y; b.i = 2 * (i + THREADS) + 1; }
+                if (better(d.x, 2 * (i + 2 * THREADS), b)) { b.v = d.x; b.i = 2 * (i + 2 * THREADS); }
+                if (better(d.y, 2 * (i + 2 * THREADS) + 1, b)) { b.v = d.y; b.i = 2 * (i + 2 * THREADS) + 1; }
+                if (better(f.x, 2 * (i + 3 * THREADS), b)) { b.v = f.x; b.i = 2 * (i + 3 * THREADS); }
+                if (better(f.y, 2 * (i + 3 * THREADS) + 1, b)) { b.v = f.y; b.i = 2 * (i + 3 * THREADS) + 1; }
+            }
+            for (; i < pairs; i += THREADS) {
+                const float2 a = row2[i];
+                if (better(a.x, 2 * i, b)) { b.v = a.x; b.i = 2 * i; }
+                if (better(a.y, 2 * i + 1, b)) { b.v = a.y; b.i = 2 * i + 1; }
+            }
+            if ((vocab & 1) && threadIdx.x == 0) {
+                const float v = row[vocab - 1];
+                if (better(v, vocab - 1, b)) { b.v = v; b.i = vocab - 1; }
+            }
+        } else {
+            for (int i = threadIdx.x; i < vocab; i += THREADS) {
+                const float v = row[i];
+                if (better(v, i, b)) { b.v = v; b.i = i; }
+            }
         }
         b = block_best(b, scratch);
         if (threadIdx.x == 0) out[r] = b.i < vocab ? b.i : 0;

@@ -12,6 +12,7 @@ computes q only and reads the cache it is given (modeling.rs:501-514).
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -99,13 +100,15 @@ class GqaAttention(Part):
             rows = rt.max_decode_rows * self.nq * 32
             part_o = rt.ws.get("attn_part_o", rows, self.d, torch.float32, cap=rows)
             part_ml = rt.ws.get("attn_part_ml", rows, 2, torch.float32, cap=rows)
-            counters = rt.ws.zeros("attn_counters", rt.max_decode_rows * self.nkv, 1, torch.int32)
+            counters = None
+            if os.environ.get("CRANE_MERGE_IN_ATTENTION", "0") == "1":
+                counters = rt.ws.zeros("attn_counters", rt.max_decode_rows * self.nkv, 1, torch.int32)
             k.paged_decode_attention_fused(qkv, self.qkv_cols, self.own_kv, cos, sin, self.q_norm,
                                            self.k_norm, self.eps, o, cache.k, cache.v, ctx.cu_q,
                                            ctx.kv_len, table, cache.page_size, self.nq, self.nkv,
                                            self.d, self.window, self.scale, splits, part_o, part_ml,
                                            counters, rt.err)
-            rt.launches += 1
+            rt.launches += 1 if (counters is not None or splits == 1) else 2
             return rt.linear(o, self.o_w, self.o_b, "attn_out")
         q = rt.ws.get("attn_q", n, self.nq * self.d, rt.dtype)
         k.rope_norm_cache(qkv, self.qkv_cols, rt.dtype, ctx.positions, ctx.tok_entry, table, cos,
