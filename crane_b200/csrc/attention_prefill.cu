@@ -22,7 +22,7 @@ constexpr int WARPS = 4;
 constexpr int THREADS = WARPS * 32;
 
 template <int D>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 3)
 paged_prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                           const __nv_bfloat16* __restrict__ k_pool,
                           const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ cu_q,
@@ -34,11 +34,15 @@ paged_prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __
     constexpr int KS = D / 16, DN = D / 8;
     extern __shared__ __align__(16) uint8_t smem[];
 
-    // which request and which of its query tiles this CTA has
+    // which request and which of its query tiles this CTA has; a request's last tiles (which
+    // read the most keys) come first, so that the long CTAs start early
     int e = 0, tile = blockIdx.x;
     for (; e < n_entries; ++e) {
         const int tiles = (cu_q[e + 1] - cu_q[e] + BQ - 1) / BQ;
-        if (tile < tiles) break;
+        if (tile < tiles) {
+            tile = tiles - 1 - tile;
+            break;
+        }
         tile -= tiles;
     }
     if (e >= n_entries) return;

@@ -321,30 +321,36 @@ __global__ void rope_norm_cache_kernel(GemmOut<T> qkv, int qkv_stride,
 }
 
 // ------------------------------------------------------------ SiLU(g) * u
-// gu rows hold [gate (inter) | up (inter)].
+// gu rows hold [gate (inter) | up (inter)], or, `blocked`, blocks of 16 gate
+// columns followed by the 16 up columns of the same features.
 template <typename T>
-__global__ void silu_mul_kernel(GemmOut<T> gu, T* __restrict__ out, long long n_rows, int inter) {
+__global__ void silu_mul_kernel(GemmOut<T> gu, T* __restrict__ out, long long n_rows, int inter,
+                                int blocked) {
     pdl_launch_dependents();
     pdl_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_rows * inter) return;
     const long long r = i / inter;
     const int c = (int)(i % inter);
-    const float g = gu.load(r * 2 * inter + c);
-    const float u = gu.load(r * 2 * inter + inter + c);
+    const int gc = blocked ? (c >> 4) * 32 + (c & 15) : c;
+    const int uc = blocked ? gc + 16 : inter + c;
+    const float g = gu.load(r * 2 * inter + gc);
+    const float u = gu.load(r * 2 * inter + uc);
     out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
 }
 
 // The same for whole bf16 rows, eight neighbours per thread (inter % 8 == 0).
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu,
-                                       __nv_bfloat16* __restrict__ out, int inter) {
+                                       __nv_bfloat16* __restrict__ out, int inter, int blocked) {
     pdl_launch_dependents();
     pdl_wait();
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (c >= inter) return;
     const long long r = blockIdx.y;
-    const uint4 g4 = *(const uint4*)(gu + r * 2 * inter + c);
-    const uint4 u4 = *(const uint4*)(gu + r * 2 * inter + inter + c);
+    const int gc = blocked ? (c >> 4) * 32 + (c & 15) : c;
+    const int uc = blocked ? gc + 16 : inter + c;
+    const uint4 g4 = *(const uint4*)(gu + r * 2 * inter + gc);
+    const uint4 u4 = *(const uint4*)(gu + r * 2 * inter + uc);
     const __nv_bfloat162* g2 = (const __nv_bfloat162*)&g4;
     const __nv_bfloat162* u2 = (const __nv_bfloat162*)&u4;
     uint4 o4;
@@ -450,19 +456,20 @@ CRANE_API int crane_rope_norm_cache(int dtype, const void* qkv, const float* qkv
 }
 
 CRANE_API int crane_silu_mul(int dtype, const void* gu, const float* gu_parts, int n_parts,
-                             long long part_stride, void* out, int n_rows, int inter,
+                             long long part_stride, void* out, int n_rows, int inter, int blocked,
                              cudaStream_t st) {
+    if (blocked && (inter & 15)) return (int)cudaErrorInvalidValue;
     if (n_rows <= 0) return 0;
     const long long n = (long long)n_rows * inter;
     const int blocks = (int)((n + 255) / 256);
     if (dtype == 1 && gu != nullptr && inter % 8 == 0 && n_rows <= 65535 &&
         ((uintptr_t)gu | (uintptr_t)out) % 16 == 0)
         return crane_launch(silu_mul_bf16x8_kernel, dim3((inter / 8 + 127) / 128, n_rows), dim3(128), 0, st,
-                            (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter);
+                            (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, blocked);
     DISPATCH_T(dtype, {
         GemmOut<T> src{(const T*)gu, gu_parts, n_parts, part_stride};
         return crane_launch(silu_mul_kernel<T>, dim3(blocks), dim3(256), 0, st, src, (T*)out,
-                            (long long)n_rows, inter);
+                            (long long)n_rows, inter, blocked);
     });
 }
 

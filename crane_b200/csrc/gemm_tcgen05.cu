@@ -313,6 +313,229 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
 }
 
+// ---------------------------------------------------------------------------
+// Many tokens: a persistent kernel.  One CTA per SM walks over output tiles
+// (A rows fastest, so CTAs that run together share a tile of weights in L2).
+// The accumulator is double-buffered in tensor memory: while the four epilogue
+// warps drain tile i, the MMA warp already fills the other buffer with tile
+// i + 1, and the TMA warp runs ahead of both across tile borders.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// SILU: the B rows (weights) come in blocks of 32 = 16 gate rows then the 16 up
+// rows of the same features; the epilogue writes silu(gate) * up, half as many
+// columns as the product has (silu(x) = x / (1 + exp(-x)) in float:
+// crane-core/kernels/fused_ops.cu:39-42, 112-130).
+template <int BN, int STAGES, bool OUT_F32, bool SILU>
+__global__ void __launch_bounds__(NUM_THREADS)
+gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+                            const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+    constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    constexpr uint32_t TMEM_COLS = 2 * BN;                  // two accumulators
+    static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "tensor memory comes in powers of two");
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + STAGES * A_BYTES;
+    uint64_t* bars = (uint64_t*)(smem + STAGES * (A_BYTES + B_BYTES));
+    uint64_t* full = bars;                       // [STAGES]
+    uint64_t* empty = bars + STAGES;             // [STAGES]
+    uint64_t* acc_full = bars + 2 * STAGES;      // [2] an accumulator is complete
+    uint64_t* acc_empty = bars + 2 * STAGES + 2; // [2] the epilogue has read it out
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_a = (p.rows_a + BM - 1) / BM, tiles_b = (p.rows_b + BN - 1) / BN;
+    const int num_tiles = tiles_a * tiles_b;
+    const int num_kb = (p.k + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&full[s]), 1);
+            mbar_init(smem_u32(&empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&acc_full[b]), 1);
+            mbar_init(smem_u32(&acc_empty[b]), 4);           // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(tmem_slot)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer ----------------
+        pdl_wait();                                          // the activations come from the kernel before
+        int it = 0;                                          // k-blocks issued so far, over all tiles
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            const int a0 = (tile % tiles_a) * BM, b0 = (tile / tiles_a) * BN;
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int s = it % STAGES;
+                if (!mbar_wait(smem_u32(&empty[s]), ((it / STAGES) & 1) ^ 1, abort_flag)) goto done;
+                const uint32_t bar = smem_u32(&full[s]);
+                mbar_expect_tx(bar, A_BYTES + B_BYTES);
+                tma_load_2d(smem_u32(smem_a + s * A_BYTES), &map_a, bar, kb * BK, a0);
+                tma_load_2d(smem_u32(smem_b + s * B_BYTES), &map_b, bar, kb * BK, b0);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer ----------------
+        const uint32_t idesc = instr_desc_bf16(BN);
+        int it = 0, local = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+            const int acc = local & 1;
+            // the epilogue must have emptied this accumulator (two tiles ago)
+            if (!mbar_wait(smem_u32(&acc_empty[acc]), ((local >> 1) & 1) ^ 1, abort_flag)) goto done;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int s = it % STAGES;
+                if (!mbar_wait(smem_u32(&full[s]), (it / STAGES) & 1, abort_flag)) goto done;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t da = smem_desc_sw128(smem_u32(smem_a + s * A_BYTES));
+                const uint64_t db = smem_desc_sw128(smem_u32(smem_b + s * B_BYTES));
+#pragma unroll
+                for (int kk = 0; kk < BK / UMMA_K; ++kk)
+                    umma_bf16(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(smem_u32(&empty[s]));
+            }
+            umma_commit(smem_u32(&acc_full[acc]));
+        }
+    } else if (warp >= 2) {
+        // ---------------- epilogue ----------------
+        const int quarter = warp & 3;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+            const int acc = local & 1;
+            const int a0 = (tile % tiles_a) * BM, b0 = (tile / tiles_a) * BN;
+            if (!mbar_wait(smem_u32(&acc_full[acc]), (local >> 1) & 1, abort_flag)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int a = a0 + quarter * 32 + lane;
+            const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(trow + (uint32_t)c0, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (a >= p.rows_a) continue;
+                const int b_first = b0 + c0;
+                if (b_first >= p.rows_b) continue;
+                if (SILU) {
+                    // columns 0..15 of the chunk: gate, 16..31: up, of features b_first / 2 + 0..15
+                    __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (long long)a * p.ld_out + (b_first >> 1);
+                    float v[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float g = __uint_as_float(r[j]), u = __uint_as_float(r[16 + j]);
+                        v[j] = g / (1.f + expf(-g)) * u;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; j += 8) {
+                        uint4 w;
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+                        __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+                        __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                        w.x = *(uint32_t*)&h0; w.y = *(uint32_t*)&h1;
+                        w.z = *(uint32_t*)&h2; w.w = *(uint32_t*)&h3;
+                        *(uint4*)(dst + j) = w;
+                    }
+                    continue;
+                }
+                const long long idx = (long long)a * p.ld_out + b_first;
+                const bool whole = b_first + 32 <= p.rows_b;
+                if (OUT_F32) {
+                    float* dst = (float*)p.out + idx;
+                    if (whole && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                   __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                            if (p.bias) { v.x += p.bias[b_first + j]; v.y += p.bias[b_first + j + 1];
+                                          v.z += p.bias[b_first + j + 2]; v.w += p.bias[b_first + j + 3]; }
+                            *(float4*)(dst + j) = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (b_first + j < p.rows_b)
+                                dst[j] = __uint_as_float(r[j]) + (p.bias ? p.bias[b_first + j] : 0.f);
+                    }
+                } else {
+                    __nv_bfloat16* dst = (__nv_bfloat16*)p.out + idx;
+                    if (whole && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            float v[8];
+#pragma unroll
+                            for (int q = 0; q < 8; ++q)
+                                v[q] = __uint_as_float(r[j + q]) + (p.bias ? p.bias[b_first + j + q] : 0.f);
+                            uint4 w;
+                            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]);
+                            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[2], v[3]);
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]);
+                            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[6], v[7]);
+                            w.x = *(uint32_t*)&h0; w.y = *(uint32_t*)&h1;
+                            w.z = *(uint32_t*)&h2; w.w = *(uint32_t*)&h3;
+                            *(uint4*)(dst + j) = w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (b_first + j < p.rows_b)
+                                dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]) +
+                                                             (p.bias ? p.bias[b_first + j] : 0.f));
+                    }
+                }
+            }
+            // this warp is done with the accumulator: let the MMA warp reuse it
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
+        }
+    }
+done:
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicOr(p.err, CRANE_ERR_WAIT_TIMEOUT);
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(TMEM_COLS)
+                     : "memory");
+    }
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -359,6 +582,25 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
     return crane_launch(kern, grid, dim3(NUM_THREADS), smem, st, ma, mb, p);
 }
 
+template <int BN, int STAGES, bool OUT_F32, bool SILU = false>
+int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int num_tiles,
+                      cudaStream_t st) {
+    constexpr size_t smem = STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
+    auto kern = gemm_bf16_persistent_kernel<BN, STAGES, OUT_F32, SILU>;
+    static bool configured = false;
+    static int sms = 0;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return (int)cudaGetLastError();
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        configured = true;
+    }
+    const int ctas = num_tiles < sms ? num_tiles : sms;
+    return crane_launch(kern, dim3(ctas), dim3(NUM_THREADS), smem, st, ma, mb, p);
+}
+
 template <bool OUT_F32, bool TRANSPOSED>
 int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid,
                 cudaStream_t st) {
@@ -377,6 +619,7 @@ int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const Gemm
 }  // namespace
 
 // D[a, b] = sum_k A[a, k] B[b, k].  bn: columns (rows of B) per tile, 16..256.
+// epilogue: 0 none, 1 silu(gate) * up (see the persistent kernel).
 // out_f32 / transposed as in the kernel; split_k > 1 writes float partial sums
 // [split_k][...] into `out` (which must then be float) `split_stride` apart.
 // Requirements (checked, cudaErrorInvalidValue otherwise): k % 8 == 0, lda and
@@ -384,7 +627,7 @@ int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const Gemm
 CRANE_API int crane_gemm_bf16_tcgen05(const void* A, const void* B, const float* bias, void* out,
                                       int rows_a, int rows_b, int k, long long lda, long long ldb,
                                       long long ld_out, int bn, int out_f32, int transposed,
-                                      int split_k, long long split_stride, int* err,
+                                      int split_k, long long split_stride, int epilogue, int* err,
                                       cudaStream_t st) {
     if (rows_a <= 0 || rows_b <= 0) return 0;
     if (k <= 0 || (k & 7) || (lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15))
@@ -400,6 +643,24 @@ CRANE_API int crane_gemm_bf16_tcgen05(const void* A, const void* B, const float*
     p.rows_a = rows_a; p.rows_b = rows_b; p.k = k;
     p.out = out; p.ld_out = ld_out; p.split_stride = split_stride; p.bias = bias; p.err = err;
     dim3 grid((rows_a + BM - 1) / BM, (rows_b + bn - 1) / bn, split_k);
+    if (epilogue == 1) {
+        // silu(gate) * up: bf16 output of rows_b / 2 columns; the weights' rows in blocks of 16 + 16
+        if (transposed || split_k != 1 || out_f32 || bias != nullptr || (rows_b & 31) || (ld_out & 7) ||
+            ((uintptr_t)out & 15) || (bn != 128 && bn != 256))
+            return (int)cudaErrorInvalidValue;
+        const int tiles = (int)(grid.x * grid.y);
+        return bn == 256 ? launch_persistent<256, 4, false, true>(ma, mb, p, tiles, st)
+                         : launch_persistent<128, 6, false, true>(ma, mb, p, tiles, st);
+    }
+    if (epilogue != 0) return (int)cudaErrorInvalidValue;
+    if (!transposed && split_k == 1 && (bn == 128 || bn == 256)) {
+        const int tiles = (int)(grid.x * grid.y);
+        if (bn == 256)
+            return out_f32 ? launch_persistent<256, 4, true>(ma, mb, p, tiles, st)
+                           : launch_persistent<256, 4, false>(ma, mb, p, tiles, st);
+        return out_f32 ? launch_persistent<128, 6, true>(ma, mb, p, tiles, st)
+                       : launch_persistent<128, 6, false>(ma, mb, p, tiles, st);
+    }
     if (out_f32)
         return transposed ? dispatch_bn<true, true>(bn, ma, mb, p, grid, st)
                           : dispatch_bn<true, false>(bn, ma, mb, p, grid, st);

@@ -23,10 +23,10 @@ _SIGNATURES = {
     "crane_add_rmsnorm": [I, P, P, P, I, L, P, P, P, I, I, F, P],
     "crane_rope_norm_cache": [I, P, P, I, L, I, P, P, P, I, P, P, I, P, P, F, P, P, P, I, I, I, I,
                               I, I, I, I, P, P],
-    "crane_silu_mul": [I, P, P, I, L, P, I, I, P],
+    "crane_silu_mul": [I, P, P, I, L, P, I, I, I, P],
     "crane_to_float": [I, P, P, L, P],
     "crane_gemm_simt": [I, I, P, P, P, P, I, I, I, L, L, L, P],
-    "crane_gemm_bf16_tcgen05": [P, P, P, P, I, I, I, L, L, L, I, I, I, I, L, P, P],
+    "crane_gemm_bf16_tcgen05": [P, P, P, P, I, I, I, L, L, L, I, I, I, I, L, I, P, P],
     "crane_paged_attention_simt": [I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P],
     "crane_paged_decode_attention_supports": [I, I, I],
     "crane_paged_decode_attention": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P],
@@ -136,11 +136,13 @@ class Kernels:
             d, 1 if has_kv else 0, 1 if rotary else 0, err.data_ptr(), self._stream(q_out)),
             "rope_norm_cache")
 
-    def silu_mul(self, gu: Act, out) -> None:
+    def silu_mul(self, gu: Act, out, blocked: bool = False) -> None:
+        """out = silu(gate) * up.  ``gu`` rows are [gate | up], or, ``blocked``,
+        16 gate columns then the 16 up columns of the same features, and so on."""
         whole, parts, n_parts, stride = _split(gu)
         self._check(self.lib.crane_silu_mul(_dt(out.dtype), whole, parts, n_parts, stride,
                                             out.data_ptr(), out.shape[0], out.shape[1],
-                                            self._stream(out)), "silu_mul")
+                                            1 if blocked else 0, self._stream(out)), "silu_mul")
 
     def to_float(self, t, out) -> None:
         self._check(self.lib.crane_to_float(_dt(t.dtype), t.data_ptr(), out.data_ptr(), t.numel(),
@@ -190,13 +192,18 @@ class Kernels:
         return best
 
     def gemm_tcgen05(self, x, w, bias, out, err, split_k: int = 1, swap: bool = False,
-                     bn: int = 128) -> None:
+                     bn: int = 128, silu_mul: bool = False) -> None:
         """out[M,N] = x[M,K] @ w[N,K]^T (+ bias).  ``swap``: the weight fills the
         128-row side of the MMA and ``bn`` (16..64) covers the tokens.  With
-        ``split_k`` > 1 ``out`` is float [slices, M, N] of partial sums."""
+        ``split_k`` > 1 ``out`` is float [slices, M, N] of partial sums.
+        ``silu_mul``: w's rows come as 16 gate rows then the 16 up rows of the same
+        features, and out[M, N/2] = silu(gate) * up."""
         M, K = x.shape
         N = w.shape[0]
-        if split_k > 1:
+        if silu_mul:
+            assert out.shape == (M, N // 2) and out.stride(1) == 1 and split_k == 1 and not swap
+            ld, stride = out.stride(0), 0
+        elif split_k > 1:
             assert out.dtype == torch.float32 and out.dim() == 3 and out.shape[1:] == (M, N)
             ld, stride = out.stride(1), out.stride(0)
         else:
@@ -206,7 +213,8 @@ class Kernels:
         self._check(self.lib.crane_gemm_bf16_tcgen05(
             a.data_ptr(), b.data_ptr(), _ptr(bias), out.data_ptr(), a.shape[0], b.shape[0], K,
             a.stride(0), b.stride(0), ld, bn, 1 if out.dtype == torch.float32 else 0,
-            1 if swap else 0, split_k, stride, err.data_ptr(), self._stream(x)), "gemm_tcgen05")
+            1 if swap else 0, split_k, stride, 1 if silu_mul else 0, err.data_ptr(), self._stream(x)),
+            "gemm_tcgen05")
 
     # ---- attention ------------------------------------------------------
     def paged_attention_simt(self, q, out, k_pool, v_pool, positions, tok_entry, block_table,

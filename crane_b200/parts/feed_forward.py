@@ -29,13 +29,24 @@ class SwiGLU(Part):
     def load(self, weights, rt):
         p = self.prefix
         self.inter = int(self.params["intermediate_size"])
-        self.gate_up = torch.cat([weights.pop(p + "gate_proj.weight"),
-                                  weights.pop(p + "up_proj.weight")], dim=0).contiguous()
+        gate, up = weights.pop(p + "gate_proj.weight"), weights.pop(p + "up_proj.weight")
+        # On the tensor-core path the merged matrix holds 16 gate rows, then the 16 up rows of
+        # the same features, and so on: a tile of the product then has both halves of a
+        # feature side by side and its epilogue can apply silu(gate) * up itself.
+        self.blocked = (not rt.exact) and self.inter % 16 == 0
+        if self.blocked:
+            h = gate.shape[1]
+            self.gate_up = torch.stack([gate.view(-1, 16, h), up.view(-1, 16, h)], dim=1).reshape(
+                2 * self.inter, h).contiguous()
+        else:
+            self.gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.down = weights[p + "down_proj.weight"]
 
     def forward(self, h, ctx, rt):
-        gu = rt.linear(h, self.gate_up, None, "ffn_gate_up")
         act = rt.ws.get("ffn_act", h.shape[0], self.inter, rt.dtype)
-        rt.kernels.silu_mul(gu, act)
+        if self.blocked and rt.linear_silu_mul(h, self.gate_up, act):
+            return rt.linear(act, self.down, None, "ffn_down")
+        gu = rt.linear(h, self.gate_up, None, "ffn_gate_up")
+        rt.kernels.silu_mul(gu, act, self.blocked)
         rt.launches += 1
         return rt.linear(act, self.down, None, "ffn_down")

@@ -70,6 +70,20 @@ class Runtime:
             return out
         return self._linear_bf16(x, w, bias, out)
 
+    def linear_silu_mul(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+        """out[M, N/2] = silu(gate) * up of x @ w^T in one kernel, for w whose rows
+        alternate 16 gate / 16 up.  False if this step's shape has no such kernel
+        (few tokens, where the product is computed in slices)."""
+        M = x.shape[0]
+        if self.exact or not self.use_tcgen05 or M <= 64 or not self.kernels.tcgen05_takes(x, w):
+            return False
+        if w.shape[0] % 32 or out.stride(0) % 8 or out.data_ptr() % 16:
+            return False
+        self.kernels.gemm_tcgen05(x, w, None, out, self.err, bn=256 if w.shape[0] >= 2048 else 128,
+                                  silu_mul=True)
+        self.launches += 1
+        return True
+
     def _linear_bf16(self, x, w, bias, out) -> Act:
         k = self.kernels
         M, K = x.shape

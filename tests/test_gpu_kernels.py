@@ -94,6 +94,14 @@ def test_silu_mul(K, dtype):
     K.silu_mul(gu, out)
     g, u = gu[:, :inter].double().cpu().numpy(), gu[:, inter:].double().cpu().numpy()
     assert rel_err(out.cpu(), torch.from_numpy(ph.silu(g) * u)) < TOL[dtype]
+    # the same with gate and up columns in alternating blocks of 16
+    n2, i2 = 5, 352
+    gate, up = (2 * torch.randn(n2, i2, device=DEV)).to(dtype), (2 * torch.randn(n2, i2, device=DEV)).to(dtype)
+    blocked = torch.stack([gate.view(n2, -1, 16), up.view(n2, -1, 16)], dim=2).reshape(n2, 2 * i2).contiguous()
+    out2 = torch.empty(n2, i2, device=DEV, dtype=dtype)
+    K.silu_mul(blocked, out2, blocked=True)
+    want2 = ph.silu(gate.double().cpu().numpy()) * up.double().cpu().numpy()
+    assert rel_err(out2.cpu(), torch.from_numpy(want2)) < TOL[dtype]
 
 
 @pytest.mark.parametrize("in_dtype,out_dtype", [(torch.float32, torch.float32),
@@ -498,3 +506,18 @@ def test_fused_decode_attention_equals_the_separate_kernels(K, err, d, nq, nkv, 
         assert int(err.item()) == 0 and int(counters.abs().sum()) == 0
         assert torch.equal(k2, k1) and torch.equal(v2, v1)
         assert rel_err(got, want.double()) < 4e-3
+
+
+@pytest.mark.parametrize("M,I,K_,bn", [(128, 128, 64, 128), (300, 352, 160, 128), (2048, 6144, 2048, 256)])
+def test_gemm_tcgen05_with_silu_mul_epilogue(K, err, M, I, K_, bn):
+    a = torch.randn(M, K_, device=DEV).bfloat16()
+    gate = (torch.randn(I, K_, device=DEV) / K_ ** 0.5).bfloat16()
+    up = (torch.randn(I, K_, device=DEV) / K_ ** 0.5).bfloat16()
+    w = torch.stack([gate.view(-1, 16, K_), up.view(-1, 16, K_)], dim=1).reshape(2 * I, K_).contiguous()
+    out = torch.full((M, I), 7.0, device=DEV, dtype=torch.bfloat16)
+    K.gemm_tcgen05(a, w, None, out, err, bn=bn, silu_mul=True)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    g, u = a.double() @ gate.double().T, a.double() @ up.double().T
+    want = g / (1 + torch.exp(-g)) * u
+    assert rel_err(out, want) < 5e-3
