@@ -57,8 +57,9 @@ class CachePools:
         for need, g in zip(needs, self.group_of_layer):
             if need.kind == "kv":
                 shape = (pages_per_group[g], need.kv_heads, page_size, need.head_dim)
-                self.layers.append(LayerCache(need, g, torch.empty(shape, dtype=dtype, device=device),
-                                              torch.empty(shape, dtype=dtype, device=device), page_size))
+                # zeros, not uninitialised memory: rows that a tile loads but masks must be finite
+                self.layers.append(LayerCache(need, g, torch.zeros(shape, dtype=dtype, device=device),
+                                              torch.zeros(shape, dtype=dtype, device=device), page_size))
             elif need.kind == "state":
                 st = torch.zeros((max_requests, *need.state_shape), dtype=need.state_dtype,
                                  device=device)

@@ -1,0 +1,497 @@
+// Flash attention for prompt portions on the 5th-generation tensor cores
+// (head size 128, bf16, pages of 16..128 tokens).  One CTA owns 128 query rows
+// of one request and one query head and walks over the keys in tiles of 128:
+//
+//   warp 0 (one thread)   TMA: the Q tile once, then K and V tiles from the
+//                         paged pool, page by page through the block table,
+//                         into 128-byte-swizzled shared memory (two stages);
+//   warp 1 (one thread)   tcgen05.mma:  S = Q K^T  (float, tensor memory, two
+//                         buffers), then  O += P V  (float, tensor memory);
+//   warps 2..5            one thread per query row: read S with tcgen05.ld,
+//                         scale, mask (causal + window), running max and sum,
+//                         P = exp2(S - max) as bf16 into shared memory for the
+//                         second product; rescale O in tensor memory when the
+//                         running max has moved far; at the end O / sum -> out.
+//
+// A row keeps the maximum it uses for its exponentials until a later score
+// exceeds it by more than 2^8; until then P simply carries the factor (at most
+// 256, exact in float and in range for bf16), and O is rescaled only on those
+// rare moves.  The result is the same softmax (scores = q k^T / sqrt(d), causal,
+// query head h reads kv head h / (nq / nkv): crane-core/src/models/
+// hunyuan_dense/modeling.rs:611-636, 1012-1033).
+//
+// Every mbarrier wait is bounded; on a timeout the kernel records
+// CRANE_ERR_WAIT_TIMEOUT, every role leaves its loop, tensor memory is freed.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int D = 128;            // head size
+constexpr int BQ = 128;           // query rows per CTA = MMA M
+constexpr int BKV = 128;          // keys per tile
+constexpr int NUM_THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr uint32_t HALF_BYTES = 128 * 128;          // 128 rows x 64 bf16: one swizzled half tile
+constexpr uint32_t TILE_BYTES = 2 * HALF_BYTES;     // 128 x 128 bf16
+constexpr float RESCALE_THRESHOLD = 8.0f;           // in log2 units
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+// K-major operand (rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart)
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major operand: rows are positions along K (keys), each row holds 64
+// consecutive MN elements (128 bytes, swizzled); the next 64 MN elements are one
+// half tile further (leading byte offset), the next 8 rows 1024 bytes further
+// (stride byte offset).
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)(HALF_BYTES >> 4) << 16) |
+           ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// kind::f16, bf16 x bf16 -> f32, M = 128, N = 128; b_mn: B operand MN-major
+__device__ __forceinline__ uint32_t idesc(bool b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((uint32_t)(128 >> 3) << 17) |
+           ((uint32_t)(128 >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t id, uint32_t acc) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d), "l"(da), "l"(db), "r"(id), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+          "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+          "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
+          "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]),
+          "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+struct Params {
+    __nv_bfloat16* out;          // [N, nq * D]
+    const int* cu_q;
+    const int* kv_len;
+    const int* block_table;
+    int max_blocks, num_pages, page_size, n_entries, nq, nkv, window;
+    float scale_log2;
+    int* err;
+};
+
+__global__ void __launch_bounds__(NUM_THREADS)
+prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const Params p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sm_q = smem;                          // [2 halves][128][128 B]
+    uint8_t* sm_k = sm_q + TILE_BYTES;             // [2 stages][2 halves][128][128 B]
+    uint8_t* sm_v = sm_k + 2 * TILE_BYTES;         // [2 stages][2 halves (of d)][128 keys][128 B]
+    uint8_t* sm_p = sm_v + 2 * TILE_BYTES;         // [2 halves (of keys)][128 rows][128 B]
+    uint64_t* bars = (uint64_t*)(sm_p + TILE_BYTES);
+    uint64_t* q_full = bars;            // Q has landed
+    uint64_t* k_full = bars + 1;        // [2]
+    uint64_t* v_full = bars + 3;        // [2]
+    uint64_t* k_empty = bars + 5;       // [2] the S product that read the stage is done
+    uint64_t* v_empty = bars + 7;       // [2] the O product that read the stage is done
+    uint64_t* s_full = bars + 9;        // [2] S is complete in tensor memory
+    uint64_t* s_empty = bars + 11;      // [2] the softmax threads have read S out
+    uint64_t* p_full = bars + 13;       // P is in shared memory (and O rescaled if need be)
+    uint64_t* pv_done = bars + 14;      // the O product of a tile is done
+    uint32_t* tmem_slot = (uint32_t*)(bars + 15);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // which request and which of its query tiles (a request's last tiles, which read the most
+    // keys, come first)
+    int e = 0, tile = blockIdx.x;
+    for (; e < p.n_entries; ++e) {
+        const int tiles = (p.cu_q[e + 1] - p.cu_q[e] + BQ - 1) / BQ;
+        if (tile < tiles) {
+            tile = tiles - 1 - tile;
+            break;
+        }
+        tile -= tiles;
+    }
+    const bool active = e < p.n_entries;
+    const int h = blockIdx.y, g = active ? h / (p.nq / p.nkv) : 0;
+    const int row0 = active ? p.cu_q[e] : 0, q_len = active ? p.cu_q[e + 1] - row0 : 0;
+    const int pos0 = active ? p.kv_len[e] - q_len : 0;
+    const int r_begin = tile * BQ, r_end = min(q_len, r_begin + BQ);
+    const int p_first = pos0 + r_begin, p_last = pos0 + r_end - 1;
+    const int lo = (p.window > 0 && p_first - p.window + 1 > 0) ? p_first - p.window + 1 : 0;
+    const int t_begin = lo / BKV, t_end = active ? p_last / BKV + 1 : 0;
+    const int n_tiles = max(0, t_end - t_begin);
+    const int* table = p.block_table + (long long)e * p.max_blocks;
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(q_full), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&k_full[s]), 1);
+            mbar_init(smem_u32(&v_full[s]), 1);
+            mbar_init(smem_u32(&k_empty[s]), 1);
+            mbar_init(smem_u32(&v_empty[s]), 1);
+            mbar_init(smem_u32(&s_full[s]), 1);
+            mbar_init(smem_u32(&s_empty[s]), 4);
+        }
+        mbar_init(smem_u32(p_full), 4);
+        mbar_init(smem_u32(pv_done), 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(tmem_slot)),
+                     "r"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_o = tmem_base + 256;          // S buffers at columns 0 and 128, O at 256
+    pdl_launch_dependents();
+
+    if (warp == 0 && lane == 0 && n_tiles > 0) {
+        // ---------------- TMA ----------------
+        pdl_wait();
+        mbar_expect_tx(smem_u32(q_full), TILE_BYTES);
+        tma_load_2d(smem_u32(sm_q), &map_q, smem_u32(q_full), h * D, row0 + r_begin);
+        tma_load_2d(smem_u32(sm_q + HALF_BYTES), &map_q, smem_u32(q_full), h * D + 64, row0 + r_begin);
+        const int ps = p.page_size;                    // 16, 32, 64 or 128
+        const int chunks = BKV / ps;                   // pages per tile
+        for (int j = 0; j < n_tiles; ++j) {
+            const int s = j & 1;
+            const uint32_t parity = ((j >> 1) & 1) ^ 1;
+            const int key0 = (t_begin + j) * BKV;
+            for (int kv = 0; kv < 2; ++kv) {
+                uint64_t* full = kv ? &v_full[s] : &k_full[s];
+                uint64_t* empty = kv ? &v_empty[s] : &k_empty[s];
+                uint8_t* dst = (kv ? sm_v : sm_k) + s * TILE_BYTES;
+                const CUtensorMap* map = kv ? &map_v : &map_k;
+                if (!mbar_wait(smem_u32(empty), parity, abort_flag)) goto done;
+                mbar_expect_tx(smem_u32(full), TILE_BYTES);
+                for (int c = 0; c < chunks; ++c) {
+                    // a page that lies wholly after the last key is read as the last valid one:
+                    // its keys are masked, only the byte count has to be complete
+                    // (likewise a page wholly before the window's first key)
+                    int blk = (key0 + c * ps) / ps;
+                    blk = max(lo / ps, min(blk, p_last / ps));
+                    int page = table[blk];
+                    if (page < 0 || page >= p.num_pages) {
+                        atomicOr(p.err, CRANE_ERR_PAGE_RANGE);
+                        page = 0;
+                    }
+                    const int row = (page * p.nkv + g) * ps;
+                    tma_load_2d(smem_u32(dst + c * ps * 128), map, smem_u32(full), 0, row);
+                    tma_load_2d(smem_u32(dst + HALF_BYTES + c * ps * 128), map, smem_u32(full), 64, row);
+                }
+            }
+        }
+    } else if (warp == 1 && lane == 0 && n_tiles > 0) {
+        // ---------------- MMA ----------------
+        const uint32_t id_s = idesc(false), id_o = idesc(true);
+        if (!mbar_wait(smem_u32(q_full), 0, abort_flag)) goto done;
+        // S_j = Q K_j^T into S buffer j & 1
+        auto issue_s = [&](int j) -> bool {
+            const int s = j & 1;
+            if (!mbar_wait(smem_u32(&k_full[s]), (j >> 1) & 1, abort_flag)) return false;
+            if (!mbar_wait(smem_u32(&s_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag)) return false;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t qa = smem_u32(sm_q), kb = smem_u32(sm_k + s * TILE_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+                umma(tmem_base + s * 128, desc_kmajor(qa + off), desc_kmajor(kb + off), id_s, kk > 0);
+            }
+            umma_commit(smem_u32(&s_full[s]));
+            umma_commit(smem_u32(&k_empty[s]));
+            return true;
+        };
+        if (!issue_s(0)) goto done;
+        for (int j = 0; j < n_tiles; ++j) {
+            if (j + 1 < n_tiles && !issue_s(j + 1)) goto done;
+            const int s = j & 1;
+            if (!mbar_wait(smem_u32(&v_full[s]), (j >> 1) & 1, abort_flag)) goto done;
+            if (!mbar_wait(smem_u32(p_full), j & 1, abort_flag)) goto done;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t pa = smem_u32(sm_p), vb = smem_u32(sm_v + s * TILE_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < BKV / 16; ++kk) {
+                // P: 16 keys further along K = 32 bytes within a row, the second 64 keys one half on;
+                // V: 16 keys further = 16 rows = 2048 bytes
+                const uint32_t poff = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+                umma(tmem_o, desc_kmajor(pa + poff), desc_mnmajor(vb + kk * 2048), id_o, (j > 0 || kk > 0));
+            }
+            umma_commit(smem_u32(pv_done));
+            umma_commit(smem_u32(&v_empty[s]));
+        }
+    } else if (warp >= 2 && n_tiles > 0) {
+        // ---------------- softmax, correction, epilogue: one thread per query row ----------------
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;                  // row of the tile = lane of tensor memory
+        const int pos = pos0 + r_begin + r;                 // this row's position
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        float m_ref = -INFINITY, l = 0.f;                   // maximum in use, running sum
+        for (int j = 0; j < n_tiles; ++j) {
+            const int s = j & 1;
+            if (!mbar_wait(smem_u32(&s_full[s]), (j >> 1) & 1, abort_flag)) goto done;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int key_base = (t_begin + j) * BKV;
+            const bool need_mask = key_base + BKV - 1 > p_first || (p.window > 0) || key_base < lo;
+            // pass 1: this tile's maximum of the row
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BKV; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + lane_addr + s * 128 + c0, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int key = key_base + c0 + i;
+                    const bool ok = !need_mask || (key <= pos && (p.window <= 0 || key > pos - p.window));
+                    if (ok) mx = fmaxf(mx, __uint_as_float(v[i]) * p.scale_log2);
+                }
+            }
+            // keep the maximum in use unless the row moved far above it (decided per warp,
+            // because the tensor-memory accesses below are warp-wide)
+            const bool far = mx > m_ref + RESCALE_THRESHOLD;
+            const bool warp_far = __any_sync(0xffffffffu, far);
+            float factor = 1.f;
+            if (far) {
+                factor = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - mx);
+                m_ref = mx;
+            }
+            // the O product of the tile before must be done before P is overwritten or O rescaled
+            if (j > 0 && !mbar_wait(smem_u32(pv_done), (j - 1) & 1, abort_flag)) goto done;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (warp_far && j > 0) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_o + lane_addr + c0, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * factor);
+                    tmem_st32(tmem_o + lane_addr + c0, v);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            }
+            l *= factor;
+            // pass 2: P = exp2(S - m_ref), bf16, into shared memory in the swizzled K-major layout
+            const float base = (m_ref == -INFINITY) ? 0.f : m_ref;
+            float sum = 0.f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BKV; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + lane_addr + s * 128 + c0, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float p0 = 0.f, p1 = 0.f;
+                    const int key = key_base + c0 + i;
+                    const bool ok0 = !need_mask || (key <= pos && (p.window <= 0 || key > pos - p.window));
+                    const bool ok1 = !need_mask || (key + 1 <= pos && (p.window <= 0 || key + 1 > pos - p.window));
+                    if (ok0) p0 = fast_exp2(__uint_as_float(v[i]) * p.scale_log2 - base);
+                    if (ok1) p1 = fast_exp2(__uint_as_float(v[i + 1]) * p.scale_log2 - base);
+                    sum += p0 + p1;
+                    __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+                    packed[i >> 1] = *(uint32_t*)&b;
+                }
+                // 32 keys = 4 chunks of 16 bytes of this row; chunk index is xor-ed with row % 8
+                uint8_t* prow = sm_p + (c0 >> 6) * HALF_BYTES + r * 128;
+                const int chunk0 = (c0 & 63) >> 3;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int chunk = (chunk0 + q) ^ (r & 7);
+                    *(uint4*)(prow + chunk * 16) =
+                        make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                }
+            }
+            l += sum;
+            // S has been read out; P and O are ready for the second product
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(smem_u32(&s_empty[s]));
+                mbar_arrive(smem_u32(p_full));
+            }
+        }
+        // ---- epilogue: O / l ----
+        if (!mbar_wait(smem_u32(pv_done), (n_tiles - 1) & 1, abort_flag)) goto done;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const bool store = r_begin + r < r_end;
+        __nv_bfloat16* orow = p.out + ((long long)(row0 + r_begin + r) * p.nq + h) * D;
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(tmem_o + lane_addr + c0, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (store) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    uint4 w;
+                    __nv_bfloat162 b0 = __floats2bfloat162_rn(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+                    __nv_bfloat162 b1 = __floats2bfloat162_rn(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+                    __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
+                    __nv_bfloat162 b3 = __floats2bfloat162_rn(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+                    w.x = *(uint32_t*)&b0; w.y = *(uint32_t*)&b1; w.z = *(uint32_t*)&b2; w.w = *(uint32_t*)&b3;
+                    *(uint4*)(orow + c0 + i) = w;
+                }
+            }
+        }
+    }
+done:
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicOr(p.err, CRANE_ERR_WAIT_TIMEOUT);
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512)
+                     : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        fn = (EncodeTiledFn)sym;
+    }
+    return fn;
+}
+// [rows, cols] bf16, cols contiguous; box of 64 columns x box_rows rows, 128-byte swizzle
+bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+}  // namespace
+
+CRANE_API int crane_prefill_attention_tc_supports(int d, int nq, int nkv, int page_size) {
+    if (nkv <= 0 || nq % nkv != 0) return 0;
+    return d == 128 && (page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128);
+}
+
+// total_q_tiles: sum over the entries of ceil(q_len / 128).  q is [n_tokens, nq * 128].
+CRANE_API int crane_prefill_attention_tc(const void* q, void* out, const void* k_pool, const void* v_pool,
+                                         const int* cu_q, const int* kv_len, const int* block_table,
+                                         int max_blocks, int num_pages, int page_size, int n_entries,
+                                         int n_tokens, int total_q_tiles, int nq, int nkv, int d, int window,
+                                         float scale, int* err, cudaStream_t st) {
+    if (n_entries <= 0 || total_q_tiles <= 0) return 0;
+    if (!crane_prefill_attention_tc_supports(d, nq, nkv, page_size)) return (int)cudaErrorInvalidValue;
+    CUtensorMap mq, mk, mv;
+    const long long pool_rows = (long long)num_pages * nkv * page_size;
+    if (!make_map(&mq, q, n_tokens, (long long)nq * D, BQ) || !make_map(&mk, k_pool, pool_rows, D, page_size) ||
+        !make_map(&mv, v_pool, pool_rows, D, page_size))
+        return (int)cudaErrorInvalidValue;
+    Params p;
+    p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.kv_len = kv_len; p.block_table = block_table;
+    p.max_blocks = max_blocks; p.num_pages = num_pages; p.page_size = page_size; p.n_entries = n_entries;
+    p.nq = nq; p.nkv = nkv; p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.err = err;
+    constexpr size_t smem = 6 * TILE_BYTES + 16 * 8 + 16 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(prefill_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem) != cudaSuccess)
+            return (int)cudaGetLastError();
+        configured = true;
+    }
+    return crane_launch(prefill_attn_tc_kernel, dim3(total_q_tiles, nq), dim3(NUM_THREADS), smem, st, mq, mk,
+                        mv, p);
+}

@@ -24,7 +24,8 @@ from typing import Dict, List, Optional, Sequence
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 KERNEL_SOURCES = ["elementwise.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "attention_simt.cu",
-                  "attention_decode.cu", "attention_prefill.cu", "sampling.cu"]
+                  "attention_decode.cu", "attention_prefill.cu", "attention_prefill_tc.cu",
+                  "sampling.cu"]
 HOST_SOURCES = ["host/cache_manager.cpp", "host/scheduler.cpp"]
 
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",

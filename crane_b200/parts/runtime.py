@@ -43,6 +43,7 @@ class Runtime:
         self.max_decode_rows = max_decode_rows     # most single-token entries of a step
         self.launches = 0            # kernels of this package launched (a count for reports)
         self.use_tcgen05 = os.environ.get("CRANE_BF16_GEMM", "tcgen05") != "library"
+        self.use_tc_attention = os.environ.get("CRANE_PREFILL_ATTENTION", "tcgen05") != "mma"
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.split_rows = 64         # most tokens a product is computed for in slices
 

@@ -521,3 +521,44 @@ def test_gemm_tcgen05_with_silu_mul_epilogue(K, err, M, I, K_, bn):
     g, u = a.double() @ gate.double().T, a.double() @ up.double().T
     want = g / (1 + torch.exp(-g)) * u
     assert rel_err(out, want) < 5e-3
+
+
+@pytest.mark.parametrize("nq,nkv,page_size,window", [(8, 2, 64, 0), (4, 4, 16, 0), (4, 1, 128, 300),
+                                                     (16, 4, 32, 0)])
+def test_prefill_attention_tcgen05_mixed_batch(K, err, nq, nkv, page_size, window):
+    """The tensor-core flash attention (head size 128) on a mixed batch: a portion
+    of 300 rows after 211 cached positions, a single decoded token far into a long
+    context, a whole prompt of 1000, a 2-token portion and a 1-token request."""
+    d = 128
+    assert K.prefill_attention_tc_supports(d, nq, nkv, page_size)
+    torch.manual_seed(nq + window)
+    lens = [511, 1333, 1000, 67, 1]
+    q_lens = [300, 1, 1000, 2, 1]
+    ks = [torch.randn(n, nkv, d).bfloat16().float() for n in lens]
+    vs = [torch.randn(n, nkv, d).bfloat16().float() for n in lens]
+    qs = [torch.randn(ql, nq, d).bfloat16().float() for ql in q_lens]
+    far = 1333 - 40 if window else 17
+    ks[1][far] = 0.0; ks[1][far, :, 0] = 40.0
+    qs[1][0, :, 0] = 1.0 * d ** 0.5
+    k_pool, v_pool, table = paged_cache(ks, vs, page_size, torch.bfloat16, seed=nq)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    cu = np.concatenate([[0], np.cumsum(q_lens)]).tolist()
+    tiles = sum((n + 127) // 128 for n in q_lens)
+    q = torch.cat(qs).to(DEV).bfloat16().reshape(-1, nq * d)
+    out = torch.full_like(q, 9.0)
+    K.prefill_attention_tc(q, out, k_pool, v_pool, i32(cu), i32(lens), table, page_size, tiles, nq, nkv, d,
+                           window, d ** -0.5, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    # against the warp-level kernel over all rows, and against the plain computation on samples
+    ref = torch.full_like(q, -9.0)
+    K.paged_prefill_attention(q, ref, k_pool, v_pool, i32(cu), i32(lens), table, page_size,
+                              sum((n + 63) // 64 for n in q_lens), nq, nkv, d, window, d ** -0.5, err)
+    assert rel_err(out, ref.double()) < 1.5e-2
+    row = 0
+    for e, (n, ql) in enumerate(zip(lens, q_lens)):
+        for i in sorted({0, 1, ql // 2, ql - 1} & set(range(ql))):
+            want = attention_reference(qs[e][i], ks[e], vs[e], n - ql + i, window)
+            assert rel_err(out[row + i].cpu().view(nq, d), want) < 1.5e-2, (e, i)
+        row += ql
+    assert rel_err(out[300].cpu().view(nq, d)[0], vs[1][far, 0].double()) < 2e-2
