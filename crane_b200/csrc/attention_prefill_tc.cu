@@ -150,7 +150,7 @@ struct Params {
     int* err;
 };
 
-__global__ void __launch_bounds__(NUM_THREADS)
+__global__ void __launch_bounds__(NUM_THREADS, 1)
 prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const Params p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -312,21 +312,34 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (!mbar_wait(smem_u32(&s_full[s]), (j >> 1) & 1, abort_flag)) goto done;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int key_base = (t_begin + j) * BKV;
-            const bool need_mask = key_base + BKV - 1 > p_first || (p.window > 0) || key_base < lo;
-            // pass 1: this tile's maximum of the row
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BKV; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + lane_addr + s * 128 + c0, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            // the whole row of scores into registers, then the buffer is free for the next S
+            uint32_t v[BKV];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int key = key_base + c0 + i;
-                    const bool ok = !need_mask || (key <= pos && (p.window <= 0 || key > pos - p.window));
-                    if (ok) mx = fmaxf(mx, __uint_as_float(v[i]) * p.scale_log2);
+            for (int c0 = 0; c0 < BKV; c0 += 32) tmem_ld32(tmem_base + lane_addr + s * 128 + c0, v + c0);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&s_empty[s]));
+            // only tiles that touch the diagonal or the window's edge need the mask
+            const bool need_mask = key_base + BKV - 1 > p_first || key_base < lo ||
+                                   (p.window > 0 && key_base <= p_last - p.window);
+            if (need_mask) {
+#pragma unroll
+                for (int i = 0; i < BKV; ++i) {
+                    const int key = key_base + i;
+                    const bool ok = key <= pos && (p.window <= 0 || key > pos - p.window);
+                    if (!ok) v[i] = 0xff800000u;            // -inf
                 }
             }
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < BKV; i += 4) {
+                mx0 = fmaxf(mx0, __uint_as_float(v[i]));
+                mx1 = fmaxf(mx1, __uint_as_float(v[i + 1]));
+                mx2 = fmaxf(mx2, __uint_as_float(v[i + 2]));
+                mx3 = fmaxf(mx3, __uint_as_float(v[i + 3]));
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;   // scale > 0
             // keep the maximum in use unless the row moved far above it (decided per warp,
             // because the tensor-memory accesses below are warp-wide)
             const bool far = mx > m_ref + RESCALE_THRESHOLD;
@@ -336,62 +349,49 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 factor = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - mx);
                 m_ref = mx;
             }
+            // P = exp2(S * scale - m_ref), bf16 pairs, still in registers
+            const float nbase = (m_ref == -INFINITY) ? 0.f : -m_ref;
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+            for (int i = 0; i < BKV; i += 4) {
+                const float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), p.scale_log2, nbase));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, nbase));
+                const float p2 = fast_exp2(fmaf(__uint_as_float(v[i + 2]), p.scale_log2, nbase));
+                const float p3 = fast_exp2(fmaf(__uint_as_float(v[i + 3]), p.scale_log2, nbase));
+                s0 += p0; s1 += p1; s2 += p2; s3 += p3;
+                __nv_bfloat162 b0 = __floats2bfloat162_rn(p0, p1), b1 = __floats2bfloat162_rn(p2, p3);
+                v[i >> 1] = *(uint32_t*)&b0;                 // v[0..63] now hold the packed pairs
+                v[(i >> 1) + 1] = *(uint32_t*)&b1;
+            }
+            l = l * factor + ((s0 + s1) + (s2 + s3));
             // the O product of the tile before must be done before P is overwritten or O rescaled
             if (j > 0 && !mbar_wait(smem_u32(pv_done), (j - 1) & 1, abort_flag)) goto done;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (warp_far && j > 0) {
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(tmem_o + lane_addr + c0, v);
+                    uint32_t o[32];
+                    tmem_ld32(tmem_o + lane_addr + c0, o);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * factor);
-                    tmem_st32(tmem_o + lane_addr + c0, v);
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+                    tmem_st32(tmem_o + lane_addr + c0, o);
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
-            l *= factor;
-            // pass 2: P = exp2(S - m_ref), bf16, into shared memory in the swizzled K-major layout
-            const float base = (m_ref == -INFINITY) ? 0.f : m_ref;
-            float sum = 0.f;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BKV; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + lane_addr + s * 128 + c0, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                uint32_t packed[16];
+            // into shared memory in the swizzled K-major layout: 16 chunks of 16 bytes (8 keys)
+            // per row, chunk index xor-ed with row % 8, the second 64 keys one half tile on
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float p0 = 0.f, p1 = 0.f;
-                    const int key = key_base + c0 + i;
-                    const bool ok0 = !need_mask || (key <= pos && (p.window <= 0 || key > pos - p.window));
-                    const bool ok1 = !need_mask || (key + 1 <= pos && (p.window <= 0 || key + 1 > pos - p.window));
-                    if (ok0) p0 = fast_exp2(__uint_as_float(v[i]) * p.scale_log2 - base);
-                    if (ok1) p1 = fast_exp2(__uint_as_float(v[i + 1]) * p.scale_log2 - base);
-                    sum += p0 + p1;
-                    __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
-                    packed[i >> 1] = *(uint32_t*)&b;
-                }
-                // 32 keys = 4 chunks of 16 bytes of this row; chunk index is xor-ed with row % 8
-                uint8_t* prow = sm_p + (c0 >> 6) * HALF_BYTES + r * 128;
-                const int chunk0 = (c0 & 63) >> 3;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int chunk = (chunk0 + q) ^ (r & 7);
-                    *(uint4*)(prow + chunk * 16) =
-                        make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-                }
+            for (int c = 0; c < 16; ++c) {
+                uint8_t* prow = sm_p + (c >> 3) * HALF_BYTES + r * 128;
+                const int chunk = (c & 7) ^ (r & 7);
+                *(uint4*)(prow + chunk * 16) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
             }
-            l += sum;
-            // S has been read out; P and O are ready for the second product
+            // P and O are ready for the second product
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(smem_u32(&s_empty[s]));
-                mbar_arrive(smem_u32(p_full));
-            }
+            if (lane == 0) mbar_arrive(smem_u32(p_full));
         }
         // ---- epilogue: O / l ----
         if (!mbar_wait(smem_u32(pv_done), (n_tiles - 1) & 1, abort_flag)) goto done;
