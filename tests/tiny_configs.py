@@ -31,8 +31,28 @@ C = {
     "use_cla": True, "cla_share_factor": 2,
 }
 
+def _layer_sizes(hidden, heads, kv_heads, inter, layers, tied, vocab=1000):
+    """One or two layers with the layer sizes of a Hunyuan model (a small vocabulary keeps the
+    folder small): the sizes at which the serving kernels' tensor-core paths are taken."""
+    return {
+        "architectures": ["HunYuanDenseV1ForCausalLM"], "model_type": "hunyuan_v1_dense",
+        "vocab_size": vocab, "hidden_size": hidden, "intermediate_size": inter,
+        "num_hidden_layers": layers, "num_attention_heads": heads, "num_key_value_heads": kv_heads,
+        "head_dim": 128, "hidden_act": "silu", "max_position_embeddings": 2048, "rms_norm_eps": 1e-5,
+        "rope_theta": 10000.0, "rope_scaling": {"alpha": 1000.0, "type": "dynamic"},
+        "use_qk_norm": True, "tie_word_embeddings": tied, "attention_bias": False,
+    }
+
+
+S18 = _layer_sizes(2048, 16, 4, 6144, 2, True)        # Hunyuan-1.8B layer sizes
+S4 = _layer_sizes(3072, 32, 8, 8192, 1, True)         # Hunyuan-4B layer sizes
+S7 = _layer_sizes(4096, 32, 8, 14336, 1, False, 1003)  # Hunyuan-7B layer sizes, untied head
+
 TINY = {
     "A": {"config": A, "seed": 0, "std": 0.08, "norm_std": 0.05, "page_size": 64},
     "B": {"config": B, "seed": 1, "std": 0.08, "norm_std": 0.05, "page_size": 16},
     "C": {"config": C, "seed": 2, "std": 0.08, "norm_std": 0.05, "page_size": 32},
+    "S18": {"config": S18, "seed": 3, "std": 0.02, "norm_std": 0.05, "page_size": 64},
+    "S4": {"config": S4, "seed": 4, "std": 0.02, "norm_std": 0.05, "page_size": 16},
+    "S7": {"config": S7, "seed": 5, "std": 0.015, "norm_std": 0.05, "page_size": 128},
 }
