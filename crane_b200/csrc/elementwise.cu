@@ -320,6 +320,121 @@ __global__ void rope_norm_cache_kernel(GemmOut<T> qkv, int qkv_stride,
     }
 }
 
+// The same for whole bf16 rows of head size 128, eight lanes per (token, head): a
+// lane owns eight neighbours of the first half and their partners in the second
+// half (16-byte loads and stores), four heads per warp.
+__global__ void rope_norm_cache_d128_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
+                                            const int* __restrict__ positions,
+                                            const int* __restrict__ tok_entry,
+                                            const int* __restrict__ block_table, int max_blocks,
+                                            const float* __restrict__ cos_tab,
+                                            const float* __restrict__ sin_tab, int table_len,
+                                            const float* __restrict__ q_norm_w,
+                                            const float* __restrict__ k_norm_w, float eps,
+                                            __nv_bfloat16* __restrict__ q_out,
+                                            __nv_bfloat16* __restrict__ k_pool,
+                                            __nv_bfloat16* __restrict__ v_pool, int num_pages,
+                                            int page_size, int n_tokens, int nq, int nkv, int has_kv,
+                                            int rotary, int* err) {
+    constexpr int D = 128, HALF = 64;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int heads = nq + (has_kv ? 2 * nkv : 0);
+    const long long item = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;
+    const int sub = threadIdx.x & 7;                         // which eighth of a half
+    const bool live = item < (long long)n_tokens * heads;
+    const int t = live ? (int)(item / heads) : 0, h = live ? (int)(item % heads) : 0;
+    const int pos = positions[t];
+    const __nv_bfloat16* src = qkv + (long long)t * qkv_stride + (long long)h * D;
+    __nv_bfloat16* dst = nullptr;
+    const float* nw = nullptr;
+    bool is_v = false;
+    if (live) {
+        if (h < nq) {
+            dst = q_out + ((long long)t * nq + h) * D;
+            nw = q_norm_w;
+        } else {
+            const int page = block_table[(long long)tok_entry[t] * max_blocks + pos / page_size];
+            if (page < 0 || page >= num_pages) {
+                if (sub == 0) atomicOr(err, CRANE_ERR_PAGE_RANGE);
+            } else {
+                is_v = h >= nq + nkv;
+                const int g = is_v ? h - nq - nkv : h - nq;
+                dst = (is_v ? v_pool : k_pool) + (((long long)page * nkv + g) * page_size + pos % page_size) * D;
+                nw = is_v ? nullptr : k_norm_w;
+            }
+        }
+    }
+    bool rotate = rotary != 0 && !is_v;
+    if (live && rotate && (pos < 0 || pos >= table_len)) {
+        if (sub == 0) atomicOr(err, CRANE_ERR_POSITION_RANGE);
+        rotate = false;
+    }
+    float a[8], b[8];
+    {
+        uint4 ra = make_uint4(0, 0, 0, 0), rb = ra;
+        if (live) {
+            ra = *(const uint4*)(src + 8 * sub);
+            rb = *(const uint4*)(src + HALF + 8 * sub);
+        }
+        const __nv_bfloat162* pa = (const __nv_bfloat162*)&ra;
+        const __nv_bfloat162* pb = (const __nv_bfloat162*)&rb;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 fa = __bfloat1622float2(pa[i]), fb = __bfloat1622float2(pb[i]);
+            a[2 * i] = fa.x; a[2 * i + 1] = fa.y;
+            b[2 * i] = fb.x; b[2 * i + 1] = fb.y;
+        }
+    }
+    if (live && rotate) {
+        const float4* c4 = (const float4*)(cos_tab + (long long)pos * HALF + 8 * sub);
+        const float4* s4 = (const float4*)(sin_tab + (long long)pos * HALF + 8 * sub);
+        const float4 c0 = c4[0], c1 = c4[1], s0 = s4[0], s1 = s4[1];
+        const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float x1 = a[i], x2 = b[i];
+            a[i] = x1 * c[i] - x2 * sn[i];
+            b[i] = x2 * c[i] + x1 * sn[i];
+        }
+    }
+    {
+        // every lane takes part in the shuffles, whatever its head is
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
+        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+        if (nw != nullptr) {
+            const float rstd = rsqrtf(ss / (float)D + eps);
+            const float4* w4 = (const float4*)(nw + 8 * sub);
+            const float4* v4 = (const float4*)(nw + HALF + 8 * sub);
+            const float4 w0 = w4[0], w1 = w4[1], v0 = v4[0], v1 = v4[1];
+            const float wa[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+            const float wb[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                a[i] = a[i] * rstd * wa[i];
+                b[i] = b[i] * rstd * wb[i];
+            }
+        }
+    }
+    if (dst != nullptr) {
+        uint4 oa, ob;
+        __nv_bfloat162* qa = (__nv_bfloat162*)&oa;
+        __nv_bfloat162* qb = (__nv_bfloat162*)&ob;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            qa[i] = __floats2bfloat162_rn(a[2 * i], a[2 * i + 1]);
+            qb[i] = __floats2bfloat162_rn(b[2 * i], b[2 * i + 1]);
+        }
+        *(uint4*)(dst + 8 * sub) = oa;
+        *(uint4*)(dst + HALF + 8 * sub) = ob;
+    }
+}
+
 // ------------------------------------------------------------ SiLU(g) * u
 // gu rows hold [gate (inter) | up (inter)], or, `blocked`, blocks of 16 gate
 // columns followed by the 16 up columns of the same features.
@@ -436,6 +551,16 @@ CRANE_API int crane_rope_norm_cache(int dtype, const void* qkv, const float* qkv
     const long long warps = (long long)n_tokens * heads;
     const int threads = 128;
     const int blocks = (int)((warps * 32 + threads - 1) / threads);
+    if (dtype == 1 && d == 128 && qkv != nullptr && qkv_stride % 8 == 0 && n_tokens >= 32 &&
+        ((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)cos_tab |
+         (uintptr_t)sin_tab | (uintptr_t)q_norm_w | (uintptr_t)k_norm_w) % 16 == 0) {
+        const long long lanes = warps * 8;
+        return crane_launch(rope_norm_cache_d128_kernel, dim3((unsigned)((lanes + 255) / 256)), dim3(256), 0, st,
+                            (const __nv_bfloat16*)qkv, qkv_stride, positions, tok_entry, block_table,
+                            max_blocks, cos_tab, sin_tab, table_len, q_norm_w, k_norm_w, eps,
+                            (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, num_pages,
+                            page_size, n_tokens, nq, nkv, has_kv, rotary, err);
+    }
     DISPATCH_T(dtype, {
         GemmOut<T> src{(const T*)qkv, qkv_parts, n_parts, part_stride};
         // two neighbours per load when every row starts on an even element and 8-byte boundary

@@ -41,14 +41,27 @@ def _peaks():
     return out
 
 
+GRAPH = True
+
+
 def _time(fn, warmup, reps):
-    for _ in range(warmup):
+    """Seconds per launch.  The launches are captured in a CUDA graph and
+    replayed (as the engine's decode steps are), so short kernels are not timed
+    at the host's launch rate; --no-graph launches them one by one."""
+    for _ in range(max(1, warmup)):
         fn()
     torch.cuda.synchronize()
+    run = lambda: [fn() for _ in range(reps)]
+    if GRAPH:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            run()
+        run = g.replay
+        run()
+        torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
-    for _ in range(reps):
-        fn()
+    run()
     b.record()
     torch.cuda.synchronize()
     return a.elapsed_time(b) * 1e-3 / reps
@@ -163,6 +176,7 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--no-graph", action="store_true", help="launch one by one instead of replaying a graph")
     sub = ap.add_subparsers(dest="what", required=True)
     g = sub.add_parser("gemm")
     g.add_argument("--m", type=int, required=True); g.add_argument("--n", type=int, required=True)
@@ -179,6 +193,8 @@ def main(argv=None) -> int:
     r = sub.add_parser("rmsnorm")
     r.add_argument("--rows", type=int, default=2048); r.add_argument("--hidden", type=int, default=2048)
     a = ap.parse_args(argv)
+    global GRAPH
+    GRAPH = not a.no_graph
     {"gemm": gemm, "decode-attention": decode_attention, "prefill-attention": prefill_attention,
      "rmsnorm": rmsnorm}[a.what](a)
     return 0

@@ -562,3 +562,49 @@ def test_prefill_attention_tcgen05_mixed_batch(K, err, nq, nkv, page_size, windo
             assert rel_err(out[row + i].cpu().view(nq, d), want) < 1.5e-2, (e, i)
         row += ql
     assert rel_err(out[300].cpu().view(nq, d)[0], vs[1][far, 0].double()) < 2e-2
+
+
+@pytest.mark.parametrize("qk_norm", [True, False])
+def test_rope_norm_cache_wide_kernel_head_size_128(K, err, qk_norm):
+    """The 16-byte-per-lane form taken for bf16 rows of head size 128 and 32 or more tokens."""
+    d, nq, nkv, page_size, eps = 128, 6, 2, 16, 1e-5
+    lens = [37, 1, 64]                              # three entries; tokens at the end of each request
+    starts = [100, 0, 17]
+    positions = np.concatenate([np.arange(s, s + n) for s, n in zip(starts, lens)])
+    tok_entry = np.concatenate([np.full(n, i) for i, n in enumerate(lens)])
+    n_tok = len(positions)
+    cols = (nq + 2 * nkv) * d
+    qkv = torch.randn(n_tok, cols, device=DEV).bfloat16()
+    blocks = 12
+    table = torch.from_numpy(np.random.default_rng(0).permutation(3 * blocks).astype(np.int32)).view(3, blocks).to(DEV)
+    k_pool = torch.zeros(3 * blocks, nkv, page_size, d, device=DEV, dtype=torch.bfloat16)
+    v_pool = torch.zeros_like(k_pool)
+    inv = ph.rope_inv_freq(d, 10000.0, 1000.0)
+    ang = ph.rope_angles(np.arange(256), inv).astype(np.float64)
+    cos = torch.from_numpy(np.cos(ang).astype(np.float32)).to(DEV)
+    sin = torch.from_numpy(np.sin(ang).astype(np.float32)).to(DEV)
+    qw = (1 + 0.1 * torch.randn(d)).to(DEV) if qk_norm else None
+    kw = (1 + 0.1 * torch.randn(d)).to(DEV) if qk_norm else None
+    q_out = torch.empty(n_tok, nq * d, device=DEV, dtype=torch.bfloat16)
+    i32 = lambda v: torch.tensor(np.asarray(v), dtype=torch.int32, device=DEV)
+    K.rope_norm_cache(qkv, cols, torch.bfloat16, i32(positions), i32(tok_entry), table, cos, sin, qw, kw, eps,
+                      q_out, k_pool, v_pool, page_size, nq, nkv, d, True, True, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    x = qkv.double().cpu().numpy()
+    q = x[:, :nq * d].reshape(n_tok, nq, d)
+    k = x[:, nq * d:(nq + nkv) * d].reshape(n_tok, nkv, d)
+    v = x[:, (nq + nkv) * d:].reshape(n_tok, nkv, d)
+    a = ph.rope_angles(positions, inv)
+    q, k = ph.apply_rope(q, a), ph.apply_rope(k, a)
+    if qk_norm:
+        q = ph.rms_norm(q, qw.double().cpu().numpy(), eps)
+        k = ph.rms_norm(k, kw.double().cpu().numpy(), eps)
+    assert rel_err(q_out.cpu().view(n_tok, nq, d), torch.from_numpy(q)) < 1e-2
+    tab = table.cpu().numpy()
+    for t in range(n_tok):
+        p, e = int(positions[t]), int(tok_entry[t])
+        page, off = int(tab[e, p // page_size]), p % page_size
+        assert rel_err(k_pool[page, :, off].cpu(), torch.from_numpy(k[t])) < 1e-2
+        assert torch.equal(v_pool[page, :, off].cpu(), qkv[t, (nq + nkv) * d:].view(nkv, d).cpu())
+    assert int((k_pool.float().abs().sum(-1) > 0).sum()) == n_tok * nkv
