@@ -135,6 +135,12 @@ def _build(lib: str, sources: Sequence[str], compiler: str, flags: Sequence[str]
     tmp = so + f".tmp{os.getpid()}"
     _run([compiler, "-shared", "-o", tmp, *objs, *link_flags], lib)
     os.replace(tmp, so)
+    for name in os.listdir(bdir):                      # objects of earlier source versions
+        if name.startswith(lib + "_") and name.endswith(".so") and name != os.path.basename(so):
+            try:
+                os.remove(os.path.join(bdir, name))
+            except OSError:
+                pass
     for o in objs:
         try:
             os.remove(o)
