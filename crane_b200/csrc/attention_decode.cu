@@ -50,10 +50,17 @@ struct FusedArgs {
 __device__ __forceinline__ float2 raw2(const FusedArgs& a, long long idx) {
     if (a.qkv_parts == nullptr) return __bfloat1622float2(*(const __nv_bfloat162*)(a.qkv + idx));
     float2 s = make_float2(0.f, 0.f);
-    for (int i = 0; i < a.n_parts; ++i) {
-        const float2 p = *(const float2*)(a.qkv_parts + (long long)i * a.part_stride + idx);
-        s.x += p.x;
-        s.y += p.y;
+    for (int i = 0; i < a.n_parts; i += 8) {                 // eight loads in flight, added in slice order
+        float2 p[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            p[j] = (i + j < a.n_parts) ? *(const float2*)(a.qkv_parts + (long long)(i + j) * a.part_stride + idx)
+                                       : make_float2(0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            s.x += p[j].x;
+            s.y += p[j].y;
+        }
     }
     // rounded once to bf16, like a product that was written out whole
     return __bfloat1622float2(__floats2bfloat162_rn(s.x, s.y));

@@ -33,20 +33,36 @@ struct GemmOut {
     const float* parts;
     int n_parts;
     long long part_stride;
+    // The partial sums are fetched eight at a time (all loads in flight together) and added in
+    // slice order, so the sum is the same as a one-by-one loop's.
     __device__ __forceinline__ float load(long long idx) const {
         if (parts == nullptr) return to_f32(whole[idx]);
         float s = 0.f;
-        for (int i = 0; i < n_parts; ++i) s += parts[(long long)i * part_stride + idx];
+        for (int i = 0; i < n_parts; i += 8) {
+            float p[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                p[j] = (i + j < n_parts) ? parts[(long long)(i + j) * part_stride + idx] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s += p[j];
+        }
         return to_f32(from_f32<T>(s));
     }
     // two neighbours at once; idx even and the tensors' rows evenly long
     __device__ __forceinline__ float2 load2(long long idx) const {
         if (parts == nullptr) return ld2(whole + idx);
         float2 s = make_float2(0.f, 0.f);
-        for (int i = 0; i < n_parts; ++i) {
-            const float2 p = *(const float2*)(parts + (long long)i * part_stride + idx);
-            s.x += p.x;
-            s.y += p.y;
+        for (int i = 0; i < n_parts; i += 8) {
+            float2 p[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                p[j] = (i + j < n_parts) ? *(const float2*)(parts + (long long)(i + j) * part_stride + idx)
+                                         : make_float2(0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                s.x += p[j].x;
+                s.y += p[j].y;
+            }
         }
         return make_float2(to_f32(from_f32<T>(s.x)), to_f32(from_f32<T>(s.y)));
     }

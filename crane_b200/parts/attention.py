@@ -76,6 +76,7 @@ class GqaAttention(Part):
         self.k_norm = weights.get(p + "key_layernorm.weight") if a.get("qk_norm") and self.own_kv else None
         self.position = build_part(a["position"]) if a.get("position") is not None else None
         self.qkv_cols = self.qkv_w.shape[0]
+        self.max_splits = int(os.environ.get("CRANE_DECODE_SPLITS", "32"))
 
     def cache_need(self) -> CacheNeed:
         if not self.own_kv:
@@ -96,8 +97,8 @@ class GqaAttention(Part):
         if decode and self.d % 4 == 0:
             # single decoded tokens: rotary encoding, head norms, the cache write, attention over
             # key slices (enough of them to fill the device) and their merge, all in one kernel
-            splits = max(1, min(32, (2 * rt.num_sms) // max(1, ctx.n_entries * self.nkv)))
-            rows = rt.max_decode_rows * self.nq * 32
+            splits = max(1, min(self.max_splits, (2 * rt.num_sms) // max(1, ctx.n_entries * self.nkv)))
+            rows = rt.max_decode_rows * self.nq * min(self.max_splits, 32) + self.nq * self.max_splits
             part_o = rt.ws.get("attn_part_o", rows, self.d, torch.float32, cap=rows)
             part_ml = rt.ws.get("attn_part_ml", rows, 2, torch.float32, cap=rows)
             counters = None
