@@ -431,26 +431,53 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     }
 }
 
-// out[t, h, :] = sum_s w_s o_s / sum_s w_s l_s with w_s = exp2(m_s - max m)
+// out[t, h, :] = sum_s w_s o_s / sum_s w_s l_s with w_s = exp2(m_s - max m).
+// One CTA per (request, query head); the slices' (max, sum) are fetched by one
+// thread each, the weights go through shared memory, and the outputs are summed
+// with four loads in flight per thread, in slice order.
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     __nv_bfloat16* __restrict__ out, const int* __restrict__ cu_q,
                                     int nq, int d, int n_splits) {
+    __shared__ float wgt[64];
+    __shared__ float m_s[64], l_s[64];
     pdl_launch_dependents();
     pdl_wait();
     const int e = blockIdx.x, h = blockIdx.y;
     const long long base = ((long long)e * nq + h) * n_splits;
-    float M = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-    const float mb = (M == -INFINITY) ? 0.f : M;
-    float L = 0.f;
-    for (int s = 0; s < n_splits; ++s) L += exp2f(part_ml[(base + s) * 2] - mb) * part_ml[(base + s) * 2 + 1];
-    const float inv = L > 0.f ? 1.f / L : 0.f;
+    for (int s = threadIdx.x; s < n_splits; s += blockDim.x) {
+        m_s[s] = part_ml[(base + s) * 2];
+        l_s[s] = part_ml[(base + s) * 2 + 1];
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float M = -INFINITY;
+        for (int s = 0; s < n_splits; ++s) M = fmaxf(M, m_s[s]);
+        const float mb = (M == -INFINITY) ? 0.f : M;
+        float L = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float f = exp2f(m_s[s] - mb);
+            L += f * l_s[s];
+            wgt[s] = f;
+        }
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        for (int s = 0; s < n_splits; ++s) wgt[s] *= inv;
+    }
+    __syncthreads();
     const int t = cu_q[e];
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
-        float O = 0.f;
-        for (int s = 0; s < n_splits; ++s)
-            O += exp2f(part_ml[(base + s) * 2] - mb) * part_o[(base + s) * d + c];
-        out[((long long)t * nq + h) * d + c] = __float2bfloat16_rn(O * inv);
+        const float* po = part_o + base * d + c;
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        int s = 0;
+        for (; s + 4 <= n_splits; s += 4) {
+            const float v0 = po[(long long)s * d], v1 = po[(long long)(s + 1) * d];
+            const float v2 = po[(long long)(s + 2) * d], v3 = po[(long long)(s + 3) * d];
+            a0 += wgt[s] * v0;
+            a1 += wgt[s + 1] * v1;
+            a2 += wgt[s + 2] * v2;
+            a3 += wgt[s + 3] * v3;
+        }
+        for (; s < n_splits; ++s) a0 += wgt[s] * po[(long long)s * d];
+        out[((long long)t * nq + h) * d + c] = __float2bfloat16_rn((a0 + a1) + (a2 + a3));
     }
 }
 
@@ -499,7 +526,7 @@ CRANE_API int crane_paged_decode_attention(const void* q, void* out, float* part
                                            int d, int window, float scale, int n_splits, int* err,
                                            cudaStream_t st) {
     if (n_entries <= 0) return 0;
-    if (!crane_paged_decode_attention_supports(d, nq, nkv) || n_splits < 1)
+    if (!crane_paged_decode_attention_supports(d, nq, nkv) || n_splits < 1 || n_splits > 64)
         return (int)cudaErrorInvalidValue;
     const FusedArgs none = {};
 #define CASE(DD)                                                                                  \
@@ -528,7 +555,7 @@ CRANE_API int crane_paged_decode_attention_fused(
     const int* block_table, int max_blocks, int num_pages, int page_size, int n_entries, int nq, int nkv,
     int d, int window, float scale, int n_splits, int* err, cudaStream_t st) {
     if (n_entries <= 0) return 0;
-    if (!crane_paged_decode_attention_supports(d, nq, nkv) || n_splits < 1 || (d & 3) ||
+    if (!crane_paged_decode_attention_supports(d, nq, nkv) || n_splits < 1 || n_splits > 64 || (d & 3) ||
         (qkv_stride & 1) || (part_stride & 1))
         return (int)cudaErrorInvalidValue;
     FusedArgs fa;
