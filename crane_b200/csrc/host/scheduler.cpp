@@ -101,6 +101,7 @@ std::vector<PlanEntry> Scheduler::schedule(std::vector<int32_t>& tokens) {
         for (int64_t id : snapshot) {
             Sequence& s = seqs_[id];
             if (!s.running) continue;                 // preempted a moment ago
+            if (s.closing) continue;                  // waits for its last token only
             const int pend = s.pending();
             if (pend <= 0) continue;
             if ((pass == 0) != (pend == 1)) continue;
@@ -181,6 +182,34 @@ FinishReason Scheduler::on_token(int64_t id, int32_t token) {
     return s.finish;
 }
 
+void Scheduler::expect_token(int64_t id) {
+    auto it = seqs_.find(id);
+    if (it == seqs_.end() || it->second.finish != FinishReason::None) return;
+    Sequence& s = it->second;
+    s.tokens.push_back(-1);
+    ++s.unresolved;
+    if (s.generated() >= s.max_new_tokens || (int)s.tokens.size() >= cfg_.max_seq_len) s.closing = true;
+}
+
+FinishReason Scheduler::resolve_token(int64_t id, int32_t token) {
+    auto it = seqs_.find(id);
+    if (it == seqs_.end()) return FinishReason::None;
+    Sequence& s = it->second;
+    if (s.finish != FinishReason::None || s.unresolved <= 0) return s.finish;
+    const int idx = (int)s.tokens.size() - s.unresolved;
+    s.tokens[idx] = token;
+    --s.unresolved;
+    ++stats_.generated_tokens;
+    const int gen = idx + 1 - s.prompt_len;
+    const bool stop = std::find(s.eos.begin(), s.eos.end(), token) != s.eos.end();
+    if (stop || gen >= s.max_new_tokens || idx + 1 >= cfg_.max_seq_len) {
+        s.tokens.resize(idx + 1);                     // what was planned beyond it is void
+        s.unresolved = 0;
+        finish(s, stop ? FinishReason::Stop : FinishReason::Length);
+    }
+    return s.finish;
+}
+
 int Scheduler::cancel(int64_t id) {
     auto it = seqs_.find(id);
     if (it == seqs_.end()) return -2;
@@ -236,6 +265,13 @@ CRANE_HOST_API int crane_sched_on_token(void* s, int64_t id, int32_t tok) {
 CRANE_HOST_API void crane_sched_on_tokens(void* s, int n, const int64_t* ids, const int32_t* toks,
                                           int32_t* reasons) {
     for (int i = 0; i < n; ++i) reasons[i] = (int)((Scheduler*)s)->on_token(ids[i], toks[i]);
+}
+CRANE_HOST_API void crane_sched_expect_tokens(void* s, int n, const int64_t* ids) {
+    for (int i = 0; i < n; ++i) ((Scheduler*)s)->expect_token(ids[i]);
+}
+CRANE_HOST_API void crane_sched_resolve_tokens(void* s, int n, const int64_t* ids, const int32_t* toks,
+                                               int32_t* reasons) {
+    for (int i = 0; i < n; ++i) reasons[i] = (int)((Scheduler*)s)->resolve_token(ids[i], toks[i]);
 }
 CRANE_HOST_API int crane_sched_cancel(void* s, int64_t id) { return ((Scheduler*)s)->cancel(id); }
 CRANE_HOST_API int crane_sched_drop(void* s, int64_t id) { return ((Scheduler*)s)->drop(id); }

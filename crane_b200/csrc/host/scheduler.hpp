@@ -47,6 +47,8 @@ struct Sequence {
     FinishReason finish = FinishReason::None;
     int preemptions = 0;
     int64_t admit_stamp = 0;
+    int unresolved = 0;              // placeholders (-1) at the end of `tokens`: sampled, not yet known
+    bool closing = false;            // its last allowed token is sampled but not yet known: plan nothing more
 
     int generated() const { return (int)tokens.size() - prompt_len; }
     int pending() const { return (int)tokens.size() - computed; }
@@ -76,6 +78,15 @@ public:
     // The token sampled for an entry whose `sample` was 1.  Returns the finish
     // reason (None: goes on).  A finished request has given its pages back.
     FinishReason on_token(int64_t id, int32_t token);
+    // For engines that plan step N + 1 before the tokens sampled in step N have
+    // come back from the device: expect_token() puts a placeholder (-1) where the
+    // token will go, so that the request can be planned again (its next input is
+    // then read on the device from the sampler's output); resolve_token() fills the
+    // oldest placeholder in and applies the stop rules.  A request whose
+    // placeholder is its last token by count is not planned again.  If the
+    // resolved token stops the request, later placeholders are dropped.
+    void expect_token(int64_t id);
+    FinishReason resolve_token(int64_t id, int32_t token);
     int cancel(int64_t id);
     // Forget a finished request (its tokens stay readable until then).
     int drop(int64_t id);

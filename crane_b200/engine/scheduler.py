@@ -28,6 +28,8 @@ def _host():
             "crane_sched_schedule": ([P, P, P, P, P, I, P, I, P], I),
             "crane_sched_on_token": ([P, L, c_int32], I),
             "crane_sched_on_tokens": ([P, I, P, P, P], None),
+            "crane_sched_expect_tokens": ([P, I, P], None),
+            "crane_sched_resolve_tokens": ([P, I, P, P, P], None),
             "crane_sched_cancel": ([P, L], I),
             "crane_sched_drop": ([P, L], I),
             "crane_sched_has_work": ([P], I),
@@ -130,6 +132,20 @@ class Scheduler:
         t = np.asarray(tokens, dtype=np.int32)
         r = np.zeros(len(a), dtype=np.int32)
         self._lib.crane_sched_on_tokens(self._h, len(a), a.ctypes.data, t.ctypes.data, r.ctypes.data)
+        return [FINISH_REASONS[int(v)] for v in r]
+
+    def expect_tokens(self, ids: Sequence[int]) -> None:
+        """The tokens sampled for these requests are still on the device: a
+        placeholder takes each one's place so that the next step can be planned."""
+        a = np.asarray(ids, dtype=np.int64)
+        self._lib.crane_sched_expect_tokens(self._h, len(a), a.ctypes.data)
+
+    def resolve_tokens(self, ids: Sequence[int], tokens: Sequence[int]) -> List[Optional[str]]:
+        """Fills the oldest placeholder of each request in; returns the finish reasons."""
+        a = np.asarray(ids, dtype=np.int64)
+        t = np.asarray(tokens, dtype=np.int32)
+        r = np.zeros(len(a), dtype=np.int32)
+        self._lib.crane_sched_resolve_tokens(self._h, len(a), a.ctypes.data, t.ctypes.data, r.ctypes.data)
         return [FINISH_REASONS[int(v)] for v in r]
 
     def cancel(self, rid: int) -> None:

@@ -189,15 +189,16 @@ class ModelRunner:
         if len({e.request_id for e in entries}) != n_entries:
             raise ValueError("a request appears twice in one step")
         vocab = self.spec.vocab_size
-        arrays = []
+        arrays = [np.asarray(e.tokens) for e in entries]
+        if not reserved:
+            # a caller that went through the scheduler has had its tokens checked on admission
+            for e, c, t in zip(entries, counts, arrays):
+                if t.min() < 0 or t.max() >= vocab:
+                    raise ValueError(f"request {e.request_id}: token id outside [0, {vocab})")
         for e, c in zip(entries, counts):
-            t = np.asarray(e.tokens, dtype=np.int64)
-            if t.min() < 0 or t.max() >= vocab:
-                raise ValueError(f"request {e.request_id}: token id outside [0, {vocab})")
             for w in e.want:
                 if not 0 <= w < c:
                     raise ValueError(f"request {e.request_id}: wanted place {w} outside its {c} tokens")
-            arrays.append(t)
         if not reserved:
             # check everything first, so that a refused step changes nothing
             ps = self.cfg.page_size
