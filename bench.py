@@ -189,11 +189,13 @@ def time_decode_e2e(model, batch, context, steps, warmup, vocab):
         runner.table.extend(rid, context - runner.table.length(rid))
     for _ in range(warmup):
         eng.step()
+    eng.flush()                                   # nothing in flight when the clock starts
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     n = 0
     for _ in range(steps):
         n += len(eng.step())
+    n += len(eng.flush())                         # the last step's tokens are read inside the clock
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     for rid in ids:

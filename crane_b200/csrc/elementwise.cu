@@ -69,13 +69,17 @@ struct GemmOut {
 };
 
 // ---------------------------------------------------------------- embedding
+// A token id <= -2 stands for "row (-id - 2) of `deferred`": a token that an
+// earlier launch on this stream sampled and the host has not seen yet.
 template <typename T>
 __global__ void embed_gather_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
-                                    float* __restrict__ x, int hidden, int vocab, int* err) {
+                                    float* __restrict__ x, int hidden, int vocab,
+                                    const int* __restrict__ deferred, int n_deferred, int* err) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     int tok = tokens[t];
+    if (tok <= -2 && deferred != nullptr && -tok - 2 < n_deferred) tok = deferred[-tok - 2];
     if (tok < 0 || tok >= vocab) {
         if (threadIdx.x == 0) atomicOr(err, CRANE_ERR_TOKEN_RANGE);
         tok = 0;
@@ -508,10 +512,11 @@ __global__ void to_float_kernel(const T* __restrict__ in, float* __restrict__ ou
     else { using T = __nv_bfloat16; __VA_ARGS__; }
 
 CRANE_API int crane_embed_gather(int dtype, const int* tokens, const void* table, float* x,
-                                 int n_tokens, int hidden, int vocab, int* err, cudaStream_t st) {
+                                 int n_tokens, int hidden, int vocab, const int* deferred,
+                                 int n_deferred, int* err, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     DISPATCH_T(dtype, return crane_launch(embed_gather_kernel<T>, dim3(n_tokens), dim3(256), 0, st, tokens,
-                                          (const T*)table, x, hidden, vocab, err));
+                                          (const T*)table, x, hidden, vocab, deferred, n_deferred, err));
 }
 
 CRANE_API int crane_add_rmsnorm(int dtype, float* x, const void* delta, const float* delta_parts,

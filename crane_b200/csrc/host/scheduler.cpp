@@ -46,6 +46,10 @@ void Scheduler::finish(Sequence& s, FinishReason why) {
     } else {
         waiting_.erase(std::remove(waiting_.begin(), waiting_.end(), s.id), waiting_.end());
     }
+    if (s.unresolved > 0) {                           // tokens that nobody will read any more
+        s.tokens.resize(s.tokens.size() - s.unresolved);
+        s.unresolved = 0;
+    }
     s.finish = why;
     ++stats_.finished;
 }
@@ -134,6 +138,7 @@ std::vector<PlanEntry> Scheduler::schedule(std::vector<int32_t>& tokens) {
            cache_->free_slots() > 0) {
         const int64_t id = waiting_.front();
         Sequence& s = seqs_[id];
+        if (s.closing) break;                         // only its last token is still to come
         int n = std::min(std::min(s.pending(), cfg_.chunk_size), budget);
         if (cache_->admit(id) < 0) break;
         if (cache_->extend(id, n) != 0) {
@@ -145,6 +150,8 @@ std::vector<PlanEntry> Scheduler::schedule(std::vector<int32_t>& tokens) {
             if (n <= 0 || cache_->extend(id, n) != 0) {
                 cache_->release(id);
                 waiting_.pop_front();
+                s.tokens.resize(s.tokens.size() - s.unresolved);
+                s.unresolved = 0;
                 s.finish = FinishReason::CacheTooSmall;
                 ++stats_.finished;
                 last_failed_.push_back(id);

@@ -37,15 +37,36 @@ class _Live:
     params: SamplingParams
     on_token: Optional[Callable[[int, int, Optional[str]], None]]
     sampled: int = 0
+    row: int = -1                     # its row in the sampler's output of the last launched step
+
+
+@dataclass
+class _InFlight:
+    """A launched step whose sampled tokens have not been read yet."""
+    ids: List[int]
+    event: torch.cuda.Event
+    host: Optional[torch.Tensor]      # pinned int32 [len(ids)], valid after the event
+    deferred: bool                    # the scheduler holds placeholders for these tokens
 
 
 class LLMEngine:
+    """With ``async_scheduling`` the engine plans and launches step N + 1 before
+    it reads the tokens that step N sampled: the scheduler keeps a placeholder
+    for each, and the embedding of step N + 1 takes the token ids from the
+    sampler's output on the device.  The host work of a step then overlaps the
+    device work of the step before it.  A request that stops on an EOS token
+    in step N has been run one step too far; that step's token is dropped.
+    Steps are not overlapped while a live request has a repetition penalty,
+    since the penalty needs the tokens on the host."""
+
     def __init__(self, runner: ModelRunner):
         self.runner = runner
         cfg = runner.cfg
         self.scheduler = Scheduler(runner.table, cfg.max_concurrent, cfg.max_batched_tokens,
                                    min(cfg.chunk_size, cfg.max_batched_tokens), runner.max_seq_len)
-        self.sampler = Sampler(runner.rt, cfg.max_concurrent)
+        self.sampler = Sampler(runner.rt, cfg.max_concurrent, out=runner.deferred_tokens)
+        self.async_scheduling = bool(cfg.async_scheduling)
+        self._inflight: Optional[_InFlight] = None
         self._live: Dict[int, _Live] = {}
         self._next_id = 1
         self.finished: Dict[int, RequestOutput] = {}
@@ -76,7 +97,7 @@ class LLMEngine:
             self._finish(rid)
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._inflight is not None
 
     def _finish(self, rid: int) -> None:
         st = self.scheduler.state(rid)
@@ -87,45 +108,85 @@ class LLMEngine:
 
     # ---- one step -------------------------------------------------------
     def step(self) -> List[tuple]:
-        """One scheduled batch.  Returns (request id, token, finish reason) for
-        every token generated in it."""
+        """Plans and launches one batch.  Returns (request id, token, finish
+        reason) for every token that has become known: this batch's, or, when
+        steps overlap, the batch's before it."""
+        t0 = time.perf_counter()
+        out: List[tuple] = []
+        overlap = self.async_scheduling and all(
+            l.params.repetition_penalty == 1.0 for l in self._live.values())
+        if self._inflight is not None and not overlap:
+            out += self.flush()
         plan = self.scheduler.schedule()
         for rid in self.scheduler.last_failed():
             self._finish(rid)
-        if not plan:
-            return []
-        t0 = time.perf_counter()
-        entries = [StepEntry(p.request_id, p.tokens, [len(p.tokens) - 1] if p.sample else [])
-                   for p in plan]
+        cur = self._launch(plan, overlap) if plan else None
+        if self._inflight is not None:
+            out += self.flush()
+        if cur is not None:
+            self._inflight = cur
+            if not cur.deferred:
+                out += self.flush()
+            n_tok = sum(len(p.tokens) for p in plan)
+            kind = "decode" if all(len(p.tokens) == 1 for p in plan) else "prefill"
+            self.timers[kind + "_s"] += time.perf_counter() - t0
+            self.timers[kind + "_tokens"] += n_tok
+        return out
+
+    def _launch(self, plan, overlap: bool) -> _InFlight:
+        entries = []
+        for p in plan:
+            toks = p.tokens
+            if toks[-1] < 0:
+                # the request's last token is still on the device, in the row it was sampled to
+                toks = toks.copy()
+                toks[-1] = -(self._live[p.request_id].row + 2)
+            entries.append(StepEntry(p.request_id, toks, [len(toks) - 1] if p.sample else []))
         logits = self.runner.step(entries, reserved=True)
-        sampled = [p for p in plan if p.sample]
-        out: List[tuple] = []
-        if sampled:
-            params = [self._live[p.request_id].params for p in sampled]
-            need_hist = any(q.repetition_penalty != 1.0 for q in params)
-            hist = [self.scheduler.tokens(p.request_id) for p in sampled] if need_hist else None
-            counters = [self._live[p.request_id].sampled for p in sampled]
-            toks = self.sampler.sample(logits, params, hist, counters)
-            reasons = self.scheduler.on_tokens([p.request_id for p in sampled], toks)
-            for p, tok, reason in zip(sampled, toks, reasons):
-                live = self._live[p.request_id]
-                live.sampled += 1
-                out.append((p.request_id, tok, reason))
-                if live.on_token is not None:
-                    live.on_token(p.request_id, tok, reason)
-                if reason is not None:
-                    self._finish(p.request_id)
+        sampled = [p.request_id for p in plan if p.sample]
+        if not sampled:
+            event = torch.cuda.Event()
+            event.record(torch.cuda.current_stream(self.runner.rt.device))
+            return _InFlight([], event, None, overlap)
+        lives = [self._live[rid] for rid in sampled]
+        params = [l.params for l in lives]
+        need_hist = any(q.repetition_penalty != 1.0 for q in params)
+        hist = [self.scheduler.tokens(rid) for rid in sampled] if need_hist else None
+        event, host = self.sampler.sample_async(logits, params, hist, [l.sampled for l in lives])
+        for row, l in enumerate(lives):
+            l.sampled += 1
+            l.row = row
+        if overlap:
+            self.scheduler.expect_tokens(sampled)
+        return _InFlight(sampled, event, host, overlap)
+
+    def flush(self) -> List[tuple]:
+        """Waits for the launched step, if one is open, and takes its tokens in."""
+        f, self._inflight = self._inflight, None
+        if f is None:
+            return []
+        f.event.synchronize()
+        if not f.ids:
+            return []
+        toks = f.host.tolist()
+        if f.deferred:
+            reasons = self.scheduler.resolve_tokens(f.ids, toks)
         else:
-            torch.cuda.current_stream(self.runner.rt.device).synchronize()
-        dt = time.perf_counter() - t0
-        n_tok = sum(len(p.tokens) for p in plan)
-        kind = "decode" if all(len(p.tokens) == 1 for p in plan) else "prefill"
-        self.timers[kind + "_s"] += dt
-        self.timers[kind + "_tokens"] += n_tok
+            reasons = self.scheduler.on_tokens(f.ids, toks)
+        out: List[tuple] = []
+        for rid, tok, reason in zip(f.ids, toks, reasons):
+            live = self._live.get(rid)
+            if live is None:
+                continue                      # finished a step earlier; this token was one too many
+            out.append((rid, tok, reason))
+            if live.on_token is not None:
+                live.on_token(rid, tok, reason)
+            if reason is not None:
+                self._finish(rid)
         return out
 
     def run_until_done(self) -> Dict[int, RequestOutput]:
-        while self.scheduler.has_work():
+        while self.has_work():
             self.step()
         self.runner.rt.check_errors()
         done, self.finished = self.finished, {}

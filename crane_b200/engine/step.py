@@ -59,6 +59,8 @@ class StepContext:
     h_cu_q: np.ndarray
     h_kv_len: np.ndarray
     h_slots: np.ndarray
+    deferred_tokens: torch.Tensor      # int32 [max entries]: what the last step sampled, row by row;
+                                       # a token id <= -2 in ``tokens`` is read from row -id - 2
     graph_bucket: int = 0       # > 0: a decode step padded to this many entries
     real_entries: int = 0
 
@@ -124,6 +126,8 @@ class ModelRunner:
         torch.cuda.set_device(self.rt.device)
         self.model = DecoderModel(self.spec, source, self.rt, where)
         self._build_cache()
+        # the sampler writes here; the next step's embedding may read from it
+        self.deferred_tokens = torch.zeros(self.cap_entries, dtype=torch.int32, device=self.rt.device)
         self.steps = 0
         # decode steps (one token per entry) of the bfloat16 path replay a captured graph
         self._graphs: Dict[int, tuple] = {}
@@ -174,7 +178,10 @@ class ModelRunner:
     # ---- the step -------------------------------------------------------
     def prepare(self, entries: Sequence[StepEntry], reserved: bool = False) -> StepContext:
         """Takes pages for the step's tokens (unless the caller has: ``reserved``)
-        and lays the metadata out on host and device."""
+        and lays the metadata out on host and device.  A reserved step's tokens
+        were checked on admission; it may name a token that the last step
+        sampled and the host has not read yet as ``-(row + 2)``, ``row`` being
+        the token's place in ``deferred_tokens``."""
         n_entries = len(entries)
         if n_entries == 0:
             raise ValueError("a step needs at least one entry")
@@ -265,6 +272,7 @@ class ModelRunner:
         ctx.max_q_len = int(cnt.max())
         ctx.max_kv_len = int(kvl.max())
         ctx.max_positions = self.max_seq_len
+        ctx.deferred_tokens = self.deferred_tokens
         ctx.tokens = m.view("tokens", n_tokens, True)
         ctx.positions = m.view("positions", n_tokens, True)
         ctx.tok_entry = m.view("tok_entry", n_tokens, True)

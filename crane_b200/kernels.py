@@ -19,7 +19,7 @@ from .csrc import build
 P, I, L, F = c_void_p, c_int, c_longlong, c_float
 
 _SIGNATURES = {
-    "crane_embed_gather": [I, P, P, P, I, I, I, P, P],
+    "crane_embed_gather": [I, P, P, P, I, I, I, P, I, P, P],
     "crane_add_rmsnorm": [I, P, P, P, I, L, P, P, P, I, I, F, P],
     "crane_rope_norm_cache": [I, P, P, I, L, I, P, P, P, I, P, P, I, P, P, F, P, P, P, I, I, I, I,
                               I, I, I, I, P, P],
@@ -107,10 +107,13 @@ class Kernels:
             raise KernelError(f"{what}: CUDA error {code}")
 
     # ---- elementwise ---------------------------------------------------
-    def embed_gather(self, tokens, table, x, err) -> None:
+    def embed_gather(self, tokens, table, x, err, deferred=None) -> None:
+        """``deferred`` int32 [R]: a token id <= -2 is read from its row -id - 2."""
         n, hidden = x.shape
         self._check(self.lib.crane_embed_gather(_dt(table.dtype), tokens.data_ptr(), table.data_ptr(),
                                                 x.data_ptr(), n, hidden, table.shape[0],
+                                                deferred.data_ptr() if deferred is not None else None,
+                                                deferred.numel() if deferred is not None else 0,
                                                 err.data_ptr(), self._stream(x)), "embed_gather")
 
     def add_rmsnorm(self, x, delta: Optional[Act], weight, eps: float, out, rows=None) -> None:

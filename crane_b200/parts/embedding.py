@@ -26,9 +26,11 @@ class TokenEmbedding(Part):
     def load(self, weights, rt):
         self.table = weights[self.prefix + "weight"]
 
-    def forward(self, tokens, x, rt):
-        """Writes the float residual rows ``x`` [N,H] for int32 ``tokens`` [N]."""
-        rt.kernels.embed_gather(tokens, self.table, x, rt.err)
+    def forward(self, tokens, x, rt, deferred=None):
+        """Writes the float residual rows ``x`` [N,H] for int32 ``tokens`` [N].
+        A token id <= -2 names row ``-id - 2`` of ``deferred`` (int32, on the
+        device): a token sampled by an earlier launch that the host has not read."""
+        rt.kernels.embed_gather(tokens, self.table, x, rt.err, deferred)
         rt.launches += 1
 
 

@@ -72,7 +72,7 @@ class DecoderModel:
         rt = self.rt
         n = ctx.n_tokens
         x = rt.ws.get("residual", n, self.spec.hidden_size, torch.float32)
-        self.embed.forward(ctx.tokens, x, rt)
+        self.embed.forward(ctx.tokens, x, rt, getattr(ctx, "deferred_tokens", None))
         pending = None
         for place, step in enumerate(self.spec.schedule):
             pending = self.blocks[step.layer].forward(x, pending, ctx, caches[step.cache_step(place)], rt)

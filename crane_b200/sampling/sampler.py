@@ -38,13 +38,17 @@ class SamplingParams:
 
 
 class Sampler:
-    def __init__(self, rt, max_rows: int, max_context: int = 64):
+    def __init__(self, rt, max_rows: int, max_context: int = 64, out: Optional[torch.Tensor] = None):
+        """``out``: the int32 device buffer [max_rows] that the chosen ids are
+        written to (one of the sampler's own if not given)."""
         self.rt = rt
         self.max_rows = max_rows
         self.max_context = max_context
         dev = rt.device
-        self.out = torch.zeros(max_rows, dtype=torch.int32, device=dev)
-        self.out_host = torch.zeros(max_rows, dtype=torch.int32).pin_memory()
+        self.out = out if out is not None else torch.zeros(max_rows, dtype=torch.int32, device=dev)
+        # two host buffers in turn: a read-back may be in flight while the last one is read
+        self._hosts = [torch.zeros(max_rows, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._turn = 0
         self._alloc_context(max_context)
         # per-row options, staged in one pinned block: three 4-byte arrays, two 8-byte arrays
         r8 = (max_rows + 1) // 2 * 2
@@ -116,9 +120,20 @@ class Sampler:
         self.rt.launches += 1
         return out
 
-    def sample(self, logits, params, histories=None, counters=None) -> List[int]:
+    def sample_async(self, logits, params, histories=None, counters=None):
+        """Samples and starts the copy to the host.  Returns (event, pinned
+        int32 view): the ids are there once the event has happened.  At most
+        two such read-backs may be open at a time."""
         out = self.sample_device(logits, params, histories, counters)
         n = out.shape[0]
-        self.out_host[:n].copy_(out, non_blocking=True)
-        torch.cuda.current_stream(self.rt.device).synchronize()
-        return self.out_host[:n].tolist()
+        host = self._hosts[self._turn][:n]
+        self._turn ^= 1
+        host.copy_(out, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record(torch.cuda.current_stream(self.rt.device))
+        return event, host
+
+    def sample(self, logits, params, histories=None, counters=None) -> List[int]:
+        event, host = self.sample_async(logits, params, histories, counters)
+        event.synchronize()
+        return host.tolist()

@@ -161,6 +161,35 @@ def test_sampling_with_a_seed_is_reproducible(model_folders):
     assert len(rep) == 17
 
 
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_overlapped_steps_change_no_token(dtype, model_folders):
+    """The engine that launches a step before it has read the last one's tokens
+    gives the tokens of the engine that waits: with EOS tokens that stop
+    requests early, temperature sampling, and a pool so small that requests
+    are preempted and recomputed."""
+    from crane_b200.generation import GenerationConfig
+    folder = model_folders("B", "float32" if dtype == "fp32" else "bfloat16")
+    rng = np.random.default_rng(9)
+    prompts = [rng.integers(0, 300, n).tolist() for n in (40, 38, 35, 3, 17)]
+    runs = {}
+    for overlap in (False, True):
+        m = load(folder, dtype, page_size=16, num_pages=12, max_concurrent=3, max_batched_tokens=64,
+                 chunk_size=32, async_scheduling=overlap)
+        free = m.generate_batch(prompts, greedy_cfg(30, eos_token_id=-1))
+        eos = free[0][len(prompts[0]) + 11]              # stops the first request after 12 tokens
+        runs[overlap] = (free,
+                         m.generate_batch(prompts, greedy_cfg(30, eos_token_id=eos)),
+                         m.generate_batch(prompts, GenerationConfig(max_new_tokens=20, temperature=0.9,
+                                                                    top_k=30, eos_token_id=eos, seed=5)),
+                         m.generate(prompts[3], greedy_cfg(1, eos_token_id=-1)))
+        assert m.stats()["preemptions"] > 0
+        assert len(runs[overlap][1][0]) <= len(prompts[0]) + 12
+        m.runner.table.check()
+        assert m.runner.table.free_pages() == 12
+        assert not m.engine.has_work()
+    assert runs[False] == runs[True]
+
+
 def test_refusals(model_folders):
     folder = model_folders("A", "float32")
     m = load(folder, "fp32", page_size=16, num_pages=16, max_concurrent=2, max_batched_tokens=64)

@@ -197,3 +197,102 @@ def test_random_load_never_breaks_budget_or_books(seed):
     assert t.free_pages() == 24 and t.live() == 0
     st = s.stats()
     assert st["finished"] == len(lens) and st["requests"] == len(lens)
+
+
+# ---- tokens that are planned before they are known --------------------------
+def test_placeholder_lets_the_next_step_be_planned():
+    t, s = make()
+    s.add(1, [1, 2, 3], 4, [9])
+    plan = s.schedule()
+    assert plan[0].sample
+    s.expect_tokens([1])
+    nxt = s.schedule()                                             # planned with the token unknown
+    assert [(e.start, list(e.tokens), e.sample) for e in nxt] == [(3, [-1], True)]
+    assert s.resolve_tokens([1], [7]) == [None]
+    assert s.tokens(1) == [1, 2, 3, 7]
+    s.expect_tokens([1])
+    assert s.tokens(1) == [1, 2, 3, 7, -1]
+    assert s.resolve_tokens([1], [8]) == [None]
+    assert s.tokens(1) == [1, 2, 3, 7, 8]
+
+
+def test_stop_token_voids_what_was_planned_beyond_it():
+    t, s = make()
+    s.add(1, [1, 2, 3], 10, [9])
+    s.schedule()
+    s.expect_tokens([1])
+    s.schedule()                                                   # one step too far
+    s.expect_tokens([1])
+    assert s.resolve_tokens([1], [9]) == ["stop"]
+    assert s.tokens(1) == [1, 2, 3, 9]
+    assert t.free_pages() == 16 and t.live() == 0                  # pages are back
+    assert s.resolve_tokens([1], [4]) == ["stop"]                  # the late token changes nothing
+    assert s.tokens(1) == [1, 2, 3, 9]
+    assert not s.has_work()
+
+
+def test_last_token_by_count_is_not_planned_past():
+    t, s = make()
+    s.add(1, [1, 2, 3], 2, [])
+    s.schedule()
+    s.expect_tokens([1])
+    assert len(s.schedule()) == 1
+    s.expect_tokens([1])                                           # the second of two tokens
+    assert s.schedule() == [] and s.has_work()                     # nothing more, but not done
+    assert s.resolve_tokens([1], [5]) == [None]
+    assert s.schedule() == []
+    assert s.resolve_tokens([1], [6]) == ["length"]
+    assert s.tokens(1) == [1, 2, 3, 5, 6]
+    assert not s.has_work() and t.live() == 0
+
+
+def test_cancel_drops_placeholders():
+    t, s = make()
+    s.add(1, [1, 2, 3], 8, [])
+    s.schedule()
+    s.expect_tokens([1])
+    s.cancel(1)
+    assert s.tokens(1) == [1, 2, 3] and s.state(1).finish_reason == "cancelled"
+    assert s.resolve_tokens([1], [5]) == ["cancelled"]
+    assert s.tokens(1) == [1, 2, 3]
+
+
+def test_placeholders_and_preemption_give_the_same_tokens_as_plain_decoding():
+    """The same requests, once answered at once and once a step late, under a
+    pool so small that requests are preempted: same tokens for every request."""
+    def run(late):
+        t, s = make(pages=6, page_size=4, max_running=3, budget=16, chunk=8, max_seq_len=64)
+        for rid, n in ((1, 5), (2, 7), (3, 3)):
+            s.add(rid, list(range(1, n + 1)), 9, [])
+        pending, steps = None, 0
+        def answer(ids):
+            toks = [(rid * 31 + len(s.tokens(rid)) * 7) % 50 for rid in ids]
+            if late:
+                # the oldest placeholder sits one before the end if a newer one follows
+                toks = [(rid * 31 + (len(s.tokens(rid)) - s.tokens(rid).count(-1)) * 7) % 50
+                        for rid in ids]
+                return s.resolve_tokens(ids, toks)
+            return s.on_tokens(ids, toks)
+        while s.has_work() and steps < 400:
+            steps += 1
+            plan = s.schedule()
+            ids = [e.request_id for e in plan if e.sample]
+            for e in plan:
+                assert (np.asarray(e.tokens[:-1]) >= 0).all()     # only a last token may be unknown
+            if late:
+                s.expect_tokens(ids)
+                if pending:
+                    answer(pending)
+                pending = ids
+            elif ids:
+                answer(ids)
+            t.check()
+        if late and pending:
+            answer(pending)
+        assert steps < 400
+        return {rid: s.tokens(rid) for rid in (1, 2, 3)}, s.stats()["preemptions"]
+    plain, p0 = run(False)
+    late, p1 = run(True)
+    assert plain == late
+    assert p0 > 0 and p1 > 0
+    assert all(len(v) - n == 9 for v, n in zip(plain.values(), (5, 7, 3)))
