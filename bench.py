@@ -146,8 +146,9 @@ def fill_cache(model, batch, context, seed=1):
     return ids
 
 
-def time_decode(model, ids, steps, warmup, vocab):
-    """K decode steps of the whole batch, timed on the device."""
+def time_decode(model, ids, steps, warmup, vocab, mark=False):
+    """K decode steps of the whole batch, timed on the device.  `mark`: the
+    timed steps lie between cudaProfilerStart and cudaProfilerStop."""
     import torch
     from crane_b200.engine import StepEntry
     from crane_b200.sampling import SamplingParams
@@ -163,11 +164,15 @@ def time_decode(model, ids, steps, warmup, vocab):
     torch.cuda.synchronize()
     launches0 = runner.rt.launches
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if mark:
+        torch.cuda.profiler.start()
     start.record()
     for _ in range(steps):
         one()
     stop.record()
     torch.cuda.synchronize()
+    if mark:
+        torch.cuda.profiler.stop()
     runner.rt.check_errors()
     return start.elapsed_time(stop) / steps, (runner.rt.launches - launches0) // steps
 
@@ -244,6 +249,9 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
     ap.add_argument("--only-prefill", action="store_true",
                     help="measure the 2,048-token prefill alone (for profiling); prints its record only")
+    ap.add_argument("--only-decode", action="store_true",
+                    help="measure the decode step alone (for profiling: the timed steps lie between "
+                         "cudaProfilerStart and cudaProfilerStop); prints its record only")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -267,6 +275,8 @@ def main():
                 max_seq_len=args.context + 1024, max_batched_tokens=2048, chunk_size=2048)
     if args.only_prefill:
         opts.update(num_pages=2048 // page + 8, max_concurrent=4)
+    if args.only_decode:
+        opts.update(num_pages=args.batch * (args.context + args.steps + args.warmup + 64) // page + 64)
     model = build_model(cfg, opts)
     runner = model.runner
     if args.only_prefill:
@@ -279,10 +289,17 @@ def main():
 
     def decode_point(batch):
         ids = fill_cache(model, batch, args.context)
-        ms, launches = time_decode(model, ids, args.steps, args.warmup, vocab)
+        ms, launches = time_decode(model, ids, args.steps, args.warmup, vocab, mark=args.only_decode)
         for rid in ids:
             runner.end(rid)
         return ms, launches
+
+    if args.only_decode:
+        ms, launches = decode_point(args.batch)
+        print(json.dumps({"decode": {"value": round(args.batch * 1000.0 / ms, 1), "ms_per_step": round(ms, 4),
+                                     "layers": layers, "batch": args.batch, "context": args.context,
+                                     "launches_per_step": launches}}))
+        return 0
 
     with ClockSampler() as clocks:
         ms, launches = decode_point(args.batch)

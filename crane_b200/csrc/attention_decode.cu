@@ -11,6 +11,14 @@
 //
 // scores = q k^T / sqrt(d), softmax in float, keys lo..pos of the request with
 // lo = max(0, pos - window + 1) (modeling.rs:579-601).
+//
+// At head size 128 with pages of a multiple of 32 tokens the tiles come by TMA
+// instead (paged_decode_attn_tma_kernel below): one lane asks for a whole tile
+// with four bulk tensor copies and the warp waits on an mbarrier, which takes
+// the per-row address arithmetic and the 32 cp.async per lane and tile out of
+// the instruction stream that bounds this kernel at small batches.
+#include <cuda.h>
+
 #include "attention_mma.cuh"
 #include "no_alloc.h"
 
@@ -431,6 +439,368 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     }
 }
 
+// ---------------------------------------------------------------------------
+// Head size 128, tiles by TMA.  The pools are seen as matrices [rows, 128] of
+// bf16, a row per (page, kv head, token of the page); a tile of 32 keys of one
+// kv head is 32 consecutive rows inside one page.  In shared memory a tile is
+// two blocks of [32 rows][128 bytes] (elements 0..63 and 64..127) with the
+// 128-byte swizzle, so the ldmatrix reads are free of bank conflicts without
+// padding.  Differences to the kernel above, beside the copies: scores are
+// masked only in the tiles that touch the ends of the key range (whose rows
+// outside the range are cleared in shared memory instead of being zero-filled
+// by the copy), the running maximum is kept unscaled, and the output is
+// rescaled only when some row's maximum has grown.
+constexpr int D128 = 128;
+constexpr int HALF_TILE_BYTES = TILE * 128;          // one 64-element half of a tile
+constexpr int TILE128_BYTES = 2 * HALF_TILE_BYTES;   // K or V tile
+constexpr uint32_t TMA_WAIT_LIMIT = 1u << 22;
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void tma_tile_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x,
+                                            int row) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(row)
+        : "memory");
+}
+// Byte offset of 16-byte chunk `chunk` (0..15) of row `row` in a swizzled tile.
+__device__ __forceinline__ uint32_t sw_off(int row, int chunk) {
+    return (uint32_t)((chunk >> 3) * HALF_TILE_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
+
+template <bool FUSED>
+__global__ void __launch_bounds__(WARPS * 32)
+paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
+                             const __grid_constant__ CUtensorMap v_map,
+                             const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
+                             float* __restrict__ part_o, float* __restrict__ part_ml,
+                             const int* __restrict__ cu_q, const int* __restrict__ kv_len,
+                             const int* __restrict__ block_table, int max_blocks, int num_pages,
+                             int page_size, int nq, int nkv, int window, float scale_log2, int n_splits,
+                             int* err, const FusedArgs fa) {
+    constexpr int D = D128;
+    constexpr int KS = D / 16, DN = D / 8;
+    constexpr int STAGE_BYTES = 2 * TILE128_BYTES;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __nv_bfloat16* q_s = (__nv_bfloat16*)(smem + WARPS * NSTAGE * STAGE_BYTES);           // [16][D]
+    __nv_bfloat16* row_s = q_s + 16 * D;                                                  // [WARPS][D]
+    uint64_t* full = (uint64_t*)(row_s + WARPS * D);                                      // [WARPS][NSTAGE]
+
+    pdl_launch_dependents();
+    const bool early = FUSED && fa.has_kv != 0;
+    if (!early) pdl_wait();
+    const int split = blockIdx.x, g = blockIdx.y, e = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_rep = nq / nkv;
+    const int t = cu_q[e];
+    const int pos = kv_len[e] - 1;
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int* table = block_table + (long long)e * max_blocks;
+
+    const int first_tile = lo / TILE;
+    const int n_tiles = pos / TILE - first_tile + 1;
+    const int per_split = (n_tiles + n_splits - 1) / n_splits;
+    const int tile_begin = first_tile + split * per_split;
+    const int tile_end = min(first_tile + n_tiles, tile_begin + per_split);
+    const int n_my = max(0, (tile_end - tile_begin - warp + WARPS - 1) / WARPS);   // this warp's tiles
+
+    const bool makes_kv = FUSED && fa.has_kv != 0;
+    const int hi = makes_kv ? pos - 1 : pos;       // last key that is read from the pages
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < WARPS * NSTAGE; ++i) mbar_init(smem_u32(&full[i]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    const uint32_t wbase = smem_u32(smem) + warp * NSTAGE * STAGE_BYTES;
+    const uint32_t wbar = smem_u32(&full[warp * NSTAGE]);
+    bool bad_page = false;
+    // lane 0 asks for local tile `idx` (global tile `tile`) of this warp
+    auto issue = [&](int idx, int tile) {
+        if (lane == 0) {
+            const int key0 = tile * TILE;
+            int page = table[key0 / page_size];
+            if (page < 0 || page >= num_pages) {
+                bad_page = true;                   // reported below; the copy reads page 0 instead
+                page = 0;
+            }
+            const int row = (page * nkv + g) * page_size + key0 % page_size;
+            const uint32_t st = wbase + (idx % NSTAGE) * STAGE_BYTES;
+            const uint32_t bar = wbar + (idx % NSTAGE) * 8;
+            // the warp's reads of this stage (generic proxy) come before the copies (async proxy)
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect_tx(bar, STAGE_BYTES);
+            tma_tile_2d(st, &k_map, bar, 0, row);
+            tma_tile_2d(st + HALF_TILE_BYTES, &k_map, bar, 64, row);
+            tma_tile_2d(st + TILE128_BYTES, &v_map, bar, 0, row);
+            tma_tile_2d(st + TILE128_BYTES + HALF_TILE_BYTES, &v_map, bar, 64, row);
+        }
+    };
+#pragma unroll
+    for (int s = 0; s < NSTAGE - 1; ++s)
+        if (s < n_my) issue(s, tile_begin + warp + s * WARPS);
+    if (early) pdl_wait();                         // from here on q, k and v of this step are read
+
+    // ---- query rows: row r of the MMA tile is query head g * n_rep + r ----
+    uint32_t qf[KS][4];
+    bool rotate = FUSED && fa.rotary != 0;
+    if (FUSED) {
+        if (rotate && (pos < 0 || pos >= fa.table_len)) {
+            if (threadIdx.x == 0) atomicOr(err, CRANE_ERR_POSITION_RANGE);
+            rotate = false;
+        }
+        for (int i = threadIdx.x; i < 16 * D / 2; i += WARPS * 32) ((uint32_t*)q_s)[i] = 0u;
+        __syncthreads();
+        for (int r = warp; r < n_rep; r += WARPS)
+            rope_norm_row<D>(fa, (long long)t * fa.qkv_stride + (long long)(g * n_rep + r) * D, pos, rotate,
+                             fa.q_norm_w, lane, q_s + r * D, nullptr);
+        __syncthreads();
+        const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                qf[ks][i] = *(const uint32_t*)(q_s + (r0 + (i & 1) * 8) * D + ks * 16 + c0 + (i >> 1) * 8);
+    } else {
+        const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = r0 + (i & 1) * 8, c = ks * 16 + c0 + (i >> 1) * 8;
+                uint32_t v = 0;
+                if (r < n_rep)
+                    v = *(const uint32_t*)(q + ((long long)t * nq + g * n_rep + r) * D + c);
+                qf[ks][i] = v;
+            }
+        }
+    }
+
+    float o[DN][4];
+#pragma unroll
+    for (int i = 0; i < DN; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};     // m: unscaled maximum of the raw scores
+
+    // per-lane parts of the ldmatrix addresses
+    const int mi = lane >> 3, mr = lane & 7;
+    const uint32_t k_lane = (uint32_t)(((mi >> 1) * 8 + mr) * 128);   // + half * 16 rows
+    const uint32_t k_x = (uint32_t)(((mi & 1) ^ mr) << 4);            // chunk = ks * 2 + (mi & 1)
+    const uint32_t v_lane = (uint32_t)(((mi & 1) * 8 + mr) * 128);    // + kk * 16 rows
+    const uint32_t v_x = (uint32_t)(((mi >> 1) ^ mr) << 4);           // chunk = dn + (mi >> 1)
+    bool timed_out = false;
+
+    for (int it = 0; it < n_my; ++it) {
+        const int ti = tile_begin + warp + it * WARPS;
+        if (it + NSTAGE - 1 < n_my) issue(it + NSTAGE - 1, ti + (NSTAGE - 1) * WARPS);
+        const uint32_t kt = wbase + (it % NSTAGE) * STAGE_BYTES, vt = kt + TILE128_BYTES;
+        {
+            const uint32_t bar = wbar + (it % NSTAGE) * 8, parity = (it / NSTAGE) & 1;
+            uint32_t spin = 0;
+            while (!mbar_try_wait(bar, parity))
+                if (++spin > TMA_WAIT_LIMIT) { timed_out = true; break; }
+            if (timed_out) break;
+        }
+        const bool edge = ti * TILE < lo || ti * TILE + TILE - 1 > hi;
+        if (edge) {
+            // rows outside [lo, hi] hold whatever the page holds: clear them (the scores of such
+            // keys are masked below, a cleared value row keeps 0 * garbage out of the output)
+            uint8_t* stage = smem + (size_t)(warp * NSTAGE + it % NSTAGE) * STAGE_BYTES;
+            for (int r = lane >> 4; r < TILE; r += 2) {
+                const int j = ti * TILE + r;
+                if (j < lo || j > hi) {
+                    const int c = lane & 15;
+                    *(uint4*)(stage + sw_off(r, c)) = make_uint4(0u, 0u, 0u, 0u);
+                    *(uint4*)(stage + TILE128_BYTES + sw_off(r, c)) = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+            __syncwarp();
+            if (makes_kv && ti == pos / TILE) {
+                // this tile holds the new position: its key (encoded, normalised) and value are
+                // made here, for the tile in shared memory and for the page
+                const int page = table[pos / page_size];
+                if (page < 0 || page >= num_pages) {
+                    bad_page = true;
+                } else {
+                    const long long prow = (((long long)page * nkv + g) * page_size + pos % page_size) * D;
+                    const long long row_src = (long long)t * fa.qkv_stride;
+                    __nv_bfloat16* k_lin = row_s + warp * D;
+                    rope_norm_row<D>(fa, row_src + (long long)(nq + g) * D, pos, rotate, fa.k_norm_w, lane,
+                                     k_lin, fa.k_pool_w + prow);
+                    __syncwarp();
+                    const int r = pos % TILE;
+                    if (lane < 16) *(uint4*)(stage + sw_off(r, lane)) = *(const uint4*)(k_lin + lane * 8);
+                    for (int c = 2 * lane; c < D; c += 64) {
+                        const float2 x = raw2(fa, row_src + (long long)(nq + nkv + g) * D + c);
+                        const __nv_bfloat162 b = __floats2bfloat162_rn(x.x, x.y);
+                        *(__nv_bfloat162*)(stage + TILE128_BYTES + sw_off(r, c >> 3) + (c & 7) * 2) = b;
+                        *(__nv_bfloat162*)(fa.v_pool_w + prow + c) = b;
+                    }
+                }
+                __syncwarp();
+            }
+        }
+
+        // ---- scores: 16 rows x 32 keys ----
+        float s[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                // matrices: (keys +0..7, d lo), (keys +0..7, d hi), (keys +8..15, d lo), (keys +8..15, d hi)
+                const uint32_t addr = kt + (ks >> 2) * HALF_TILE_BYTES + half * 16 * 128 + k_lane +
+                                      ((uint32_t)(((ks & 3) * 2) << 4) ^ k_x);
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(addr, b0, b1, b2, b3);
+                mma_bf16(s[half * 2], qf[ks], b0, b1);
+                mma_bf16(s[half * 2 + 1], qf[ks], b2, b3);
+            }
+        }
+        // ---- running softmax ----
+        if (edge) {
+            const int key0 = ti * TILE + (lane & 3) * 2;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int j = key0 + nt * 8 + (c & 1);
+                    if (j < lo || j > pos) s[nt][c] = -INFINITY;
+                }
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) mx[c >> 1] = fmaxf(mx[c >> 1], s[nt][c]);
+        float m_new[2], base[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            m_new[h] = fmaxf(m[h], quad_max(mx[h]));
+            base[h] = (m_new[h] == -INFINITY) ? 0.f : m_new[h] * scale_log2;
+        }
+        if (__any_sync(0xffffffffu, m_new[0] != m[0] || m_new[1] != m[1])) {
+            float corr[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                corr[h] = exp2f(m[h] * scale_log2 - base[h]);       // exp2(-inf) = 0 on the first tile
+                m[h] = m_new[h];
+                l[h] *= corr[h];
+            }
+#pragma unroll
+            for (int i = 0; i < DN; ++i) {
+                o[i][0] *= corr[0]; o[i][1] *= corr[0];
+                o[i][2] *= corr[1]; o[i][3] *= corr[1];
+            }
+        }
+        float rs[2] = {0.f, 0.f};
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float p = exp2f(fmaf(s[nt][c], scale_log2, -base[c >> 1]));
+                s[nt][c] = p;
+                rs[c >> 1] += p;
+            }
+        l[0] += rs[0];
+        l[1] += rs[1];
+        // ---- output += p v ----
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+            uint32_t pf[4];
+            pf[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+            pf[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+            pf[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            pf[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int dn = 0; dn < DN; dn += 2) {
+                // matrices: (keys +0..7, d dn), (keys +8..15, d dn), (keys +0..7, d dn+1), (keys +8..15, d dn+1)
+                const uint32_t addr = vt + (dn >> 3) * HALF_TILE_BYTES + kk * 16 * 128 + v_lane +
+                                      ((uint32_t)((dn & 7) << 4) ^ v_x);
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(addr, b0, b1, b2, b3);
+                mma_bf16(o[dn], pf, b0, b1);
+                mma_bf16(o[dn + 1], pf, b2, b3);
+            }
+        }
+        __syncwarp();
+    }
+    if (__any_sync(0xffffffffu, bad_page) && lane == 0) atomicOr(err, CRANE_ERR_PAGE_RANGE);
+    if (__any_sync(0xffffffffu, timed_out)) {
+        if (lane == 0) atomicOr(err, CRANE_ERR_WAIT_TIMEOUT);
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);     // copies may still be landing
+    }
+    l[0] = quad_sum(l[0]);
+    l[1] = quad_sum(l[1]);
+    // from here on the maximum counts in the units of the scaled scores
+    m[0] *= scale_log2;
+    m[1] *= scale_log2;
+
+    // ---- merge the warps ----
+    __syncthreads();                                 // every warp is done with its tiles
+    float* sm_o = (float*)smem;                      // [WARPS][16][D]
+    float* sm_ml = sm_o + WARPS * 16 * D;            // [WARPS][16][2]
+    {
+        const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+#pragma unroll
+        for (int dn = 0; dn < DN; ++dn) {
+            float* p0 = sm_o + ((warp * 16 + r0) * D) + dn * 8 + c0;
+            float* p1 = sm_o + ((warp * 16 + r0 + 8) * D) + dn * 8 + c0;
+            p0[0] = o[dn][0]; p0[1] = o[dn][1];
+            p1[0] = o[dn][2]; p1[1] = o[dn][3];
+        }
+        if ((lane & 3) == 0) {
+            sm_ml[(warp * 16 + r0) * 2] = m[0];      sm_ml[(warp * 16 + r0) * 2 + 1] = l[0];
+            sm_ml[(warp * 16 + r0 + 8) * 2] = m[1];  sm_ml[(warp * 16 + r0 + 8) * 2 + 1] = l[1];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n_rep * D; idx += WARPS * 32) {
+        const int r = idx / D, c = idx % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) M = fmaxf(M, sm_ml[(w * 16 + r) * 2]);
+        const float mb = (M == -INFINITY) ? 0.f : M;
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            const float f = exp2f(sm_ml[(w * 16 + r) * 2] - mb);
+            L += f * sm_ml[(w * 16 + r) * 2 + 1];
+            O += f * sm_o[(w * 16 + r) * D + c];
+        }
+        const int h = g * n_rep + r;
+        if (n_splits == 1) {
+            out[((long long)t * nq + h) * D + c] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        } else {
+            const long long pi = ((long long)e * nq + h) * n_splits + split;
+            part_o[pi * D + c] = O;
+            if (c == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
+        }
+    }
+}
+
 // out[t, h, :] = sum_s w_s o_s / sum_s w_s l_s with w_s = exp2(m_s - max m).
 // One CTA per (request, query head); the slices' (max, sum) are fetched by one
 // thread each, the weights go through shared memory, and the outputs are summed
@@ -481,6 +851,71 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
     }
 }
 
+// ---- host side of the TMA path ----
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qr) != cudaSuccess ||
+            qr != cudaDriverEntryPointSuccess)
+            return nullptr;
+        fn = (EncodeTiledFn)sym;
+    }
+    return fn;
+}
+// CRANE_DECODE_TMA=0 keeps the cp.async kernel at head size 128 too.
+bool tma_path_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* v = getenv("CRANE_DECODE_TMA");
+        on = (v == nullptr || v[0] != '0') ? 1 : 0;
+    }
+    return on == 1;
+}
+// The pool as [rows, 128] bf16; box of 64 elements x TILE rows, 128-byte swizzle.
+bool pool_map(CUtensorMap* map, const void* pool, long long rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn || ((uintptr_t)pool & 15)) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)D128, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)D128 * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)TILE};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <bool FUSED>
+int launch_decode_tma(const void* q, void* out, float* part_o, float* part_ml, const void* k_pool,
+                      const void* v_pool, const int* cu_q, const int* kv_len, const int* block_table,
+                      int max_blocks, int num_pages, int page_size, int nq, int nkv, int window,
+                      float scale, int n_splits, int* err, const FusedArgs& fa, dim3 grid,
+                      cudaStream_t st) {
+    constexpr int tiles = WARPS * NSTAGE * 2 * TILE128_BYTES + 16 * D128 * 2 + WARPS * D128 * 2 +
+                          WARPS * NSTAGE * 8;
+    constexpr int merge = WARPS * 16 * (D128 + 2) * 4;
+    constexpr int smem = (tiles > merge ? tiles : merge) + 1024;
+    CUtensorMap km, vm;
+    const long long rows = (long long)num_pages * nkv * page_size;
+    if (!pool_map(&km, k_pool, rows) || !pool_map(&vm, v_pool, rows)) return (int)cudaErrorInvalidValue;
+    auto kern = paged_decode_attn_tma_kernel<FUSED>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return (int)cudaGetLastError();
+        configured = true;
+    }
+    return crane_launch(kern, grid, dim3(WARPS * 32), smem, st, km, vm, (const __nv_bfloat16*)q,
+                        (__nv_bfloat16*)out, part_o, part_ml, cu_q, kv_len, block_table, max_blocks,
+                        num_pages, page_size, nq, nkv, window, scale * 1.4426950408889634f, n_splits, err,
+                        fa);
+}
+
 template <int D, bool FUSED>
 int launch_decode(const void* q, void* out, float* part_o, float* part_ml, const void* k_pool,
                   const void* v_pool, const int* cu_q, const int* kv_len, const int* block_table,
@@ -497,6 +932,18 @@ int launch_decode(const void* q, void* out, float* part_o, float* part_ml, const
         configured = true;
     }
     dim3 grid(n_splits, nkv, n_entries);
+    const bool merged_in_kernel = FUSED && fa.counters != nullptr;
+    if (D == D128 && !merged_in_kernel && page_size % TILE == 0 && tma_path_enabled()) {
+        const int rc = launch_decode_tma<FUSED>(q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len,
+                                                block_table, max_blocks, num_pages, page_size, nq, nkv,
+                                                window, scale, n_splits, err, fa, grid, st);
+        if (rc != 0) return rc;
+        if (n_splits > 1)
+            return crane_launch(decode_merge_kernel, dim3(n_entries, nq), dim3(64), 0, st,
+                                (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, cu_q, nq,
+                                D, n_splits);
+        return 0;
+    }
     int rc = crane_launch(kern, grid, dim3(WARPS * 32), smem, st, (const __nv_bfloat16*)q,
                           (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)k_pool,
                           (const __nv_bfloat16*)v_pool, cu_q, kv_len, block_table, max_blocks, num_pages,
