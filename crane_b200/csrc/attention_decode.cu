@@ -127,6 +127,67 @@ __device__ __forceinline__ void rope_norm_row(const FusedArgs& a, long long src,
     }
 }
 
+// The same in two phases, so that the loads of several rows (and of the tables,
+// which are the same for all rows of a position) are in flight together.
+template <int D>
+struct RowRegs {
+    static constexpr int IT = (D / 2 + 63) / 64;
+    float2 u[IT], v[IT];
+};
+template <int D>
+__device__ __forceinline__ void row_load(const FusedArgs& a, long long src, int lane, RowRegs<D>& r) {
+#pragma unroll
+    for (int i = 0; i < RowRegs<D>::IT; ++i) {
+        const int j = 2 * lane + 64 * i;
+        r.u[i] = r.v[i] = make_float2(0.f, 0.f);
+        if (j < D / 2) {
+            r.u[i] = raw2(a, src + j);
+            r.v[i] = raw2(a, src + j + D / 2);
+        }
+    }
+}
+// cs/sn: this lane's cosines and sines (read when `rotate`), w1/w2: its norm weights (read when `norm`).
+template <int D>
+__device__ __forceinline__ void row_finish(const RowRegs<D>& r, bool rotate, const float2* cs, const float2* sn,
+                                           bool norm, const float2* w1, const float2* w2, float eps, int lane,
+                                           __nv_bfloat16* dst0, __nv_bfloat16* dst1) {
+    constexpr int IT = RowRegs<D>::IT;
+    float2 x1[IT], x2[IT];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < IT; ++i) {
+        const float2 u = r.u[i], v = r.v[i];
+        if (rotate) {
+            x1[i] = make_float2(u.x * cs[i].x - v.x * sn[i].x, u.y * cs[i].y - v.y * sn[i].y);
+            x2[i] = make_float2(v.x * cs[i].x + u.x * sn[i].x, v.y * cs[i].y + u.y * sn[i].y);
+        } else {
+            x1[i] = u;
+            x2[i] = v;
+        }
+        ss += x1[i].x * x1[i].x + x1[i].y * x1[i].y + x2[i].x * x2[i].x + x2[i].y * x2[i].y;
+    }
+    float rstd = 1.f;
+    if (norm) rstd = rsqrtf(warp_sum(ss) / (float)D + eps);
+#pragma unroll
+    for (int i = 0; i < IT; ++i) {
+        const int j = 2 * lane + 64 * i;
+        if (j < D / 2) {
+            float2 y1 = x1[i], y2 = x2[i];
+            if (norm) {
+                y1 = make_float2(y1.x * rstd * w1[i].x, y1.y * rstd * w1[i].y);
+                y2 = make_float2(y2.x * rstd * w2[i].x, y2.y * rstd * w2[i].y);
+            }
+            const __nv_bfloat162 b1 = __floats2bfloat162_rn(y1.x, y1.y), b2 = __floats2bfloat162_rn(y2.x, y2.y);
+            *(__nv_bfloat162*)(dst0 + j) = b1;
+            *(__nv_bfloat162*)(dst0 + j + D / 2) = b2;
+            if (dst1 != nullptr) {
+                *(__nv_bfloat162*)(dst1 + j) = b1;
+                *(__nv_bfloat162*)(dst1 + j + D / 2) = b2;
+            }
+        }
+    }
+}
+
 template <int D, bool FUSED>
 __global__ void __launch_bounds__(WARPS * 32)
 paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
@@ -571,11 +632,36 @@ paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
             if (threadIdx.x == 0) atomicOr(err, CRANE_ERR_POSITION_RANGE);
             rotate = false;
         }
+        // this lane's cosines, sines and norm weights are the same for every query row; the
+        // loads of two rows and of the tables are in flight together
+        static_assert(RowRegs<D>::IT == 1, "head size 128: one pair of neighbours per lane and half");
+        float2 cs[1], sn[1], w1[1], w2[1];
+        const int j = 2 * lane;
+        const bool norm = fa.q_norm_w != nullptr;
+        cs[0] = sn[0] = w1[0] = w2[0] = make_float2(0.f, 0.f);
+        if (rotate) {
+            cs[0] = *(const float2*)(fa.cos_tab + (long long)pos * (D / 2) + j);
+            sn[0] = *(const float2*)(fa.sin_tab + (long long)pos * (D / 2) + j);
+        }
+        if (norm) {
+            w1[0] = *(const float2*)(fa.q_norm_w + j);
+            w2[0] = *(const float2*)(fa.q_norm_w + j + D / 2);
+        }
+        const long long q_src = (long long)t * fa.qkv_stride + (long long)(g * n_rep) * D;
+        RowRegs<D> ra, rb;
+        row_load<D>(fa, q_src + (long long)warp * D, lane, ra);
+        if (warp + WARPS < n_rep) row_load<D>(fa, q_src + (long long)(warp + WARPS) * D, lane, rb);
         for (int i = threadIdx.x; i < 16 * D / 2; i += WARPS * 32) ((uint32_t*)q_s)[i] = 0u;
         __syncthreads();
-        for (int r = warp; r < n_rep; r += WARPS)
-            rope_norm_row<D>(fa, (long long)t * fa.qkv_stride + (long long)(g * n_rep + r) * D, pos, rotate,
-                             fa.q_norm_w, lane, q_s + r * D, nullptr);
+        for (int r = warp; r < n_rep; r += 2 * WARPS) {
+            if (r != warp) {
+                row_load<D>(fa, q_src + (long long)r * D, lane, ra);
+                if (r + WARPS < n_rep) row_load<D>(fa, q_src + (long long)(r + WARPS) * D, lane, rb);
+            }
+            row_finish<D>(ra, rotate, cs, sn, norm, w1, w2, fa.eps, lane, q_s + r * D, nullptr);
+            if (r + WARPS < n_rep)
+                row_finish<D>(rb, rotate, cs, sn, norm, w1, w2, fa.eps, lane, q_s + (r + WARPS) * D, nullptr);
+        }
         __syncthreads();
         const int r0 = lane >> 2, c0 = (lane & 3) * 2;
 #pragma unroll
@@ -802,9 +888,11 @@ paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
 }
 
 // out[t, h, :] = sum_s w_s o_s / sum_s w_s l_s with w_s = exp2(m_s - max m).
-// One CTA per (request, query head); the slices' (max, sum) are fetched by one
-// thread each, the weights go through shared memory, and the outputs are summed
-// with four loads in flight per thread, in slice order.
+// One CTA per (request, query head), a thread per output column.  Up to 16 slices: every
+// thread fetches the slices' (max, sum) pairs and its column of their outputs with all loads
+// in flight together and works the weights out itself.  More slices: the pairs are fetched by
+// one thread each, the weights go through shared memory, and the outputs are summed with
+// four loads in flight per thread.  Always in slice order.
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     __nv_bfloat16* __restrict__ out, const int* __restrict__ cu_q,
                                     int nq, int d, int n_splits) {
@@ -814,6 +902,31 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
     pdl_wait();
     const int e = blockIdx.x, h = blockIdx.y;
     const long long base = ((long long)e * nq + h) * n_splits;
+    const int t = cu_q[e];
+    if (n_splits <= 16) {
+        for (int c = threadIdx.x; c < d; c += blockDim.x) {
+            float2 ml[16];
+            float o[16];
+#pragma unroll
+            for (int s = 0; s < 16; ++s) {
+                ml[s] = s < n_splits ? *(const float2*)(part_ml + (base + s) * 2) : make_float2(-INFINITY, 0.f);
+                o[s] = s < n_splits ? part_o[(base + s) * d + c] : 0.f;
+            }
+            float M = -INFINITY;
+#pragma unroll
+            for (int s = 0; s < 16; ++s) M = fmaxf(M, ml[s].x);
+            const float mb = (M == -INFINITY) ? 0.f : M;
+            float L = 0.f, acc = 0.f;
+#pragma unroll
+            for (int s = 0; s < 16; ++s) {
+                const float f = exp2f(ml[s].x - mb);       // 0 for the slices beyond n_splits
+                L += f * ml[s].y;
+                acc += f * o[s];
+            }
+            out[((long long)t * nq + h) * d + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        }
+        return;
+    }
     for (int s = threadIdx.x; s < n_splits; s += blockDim.x) {
         m_s[s] = part_ml[(base + s) * 2];
         l_s[s] = part_ml[(base + s) * 2 + 1];
@@ -833,7 +946,6 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
         for (int s = 0; s < n_splits; ++s) wgt[s] *= inv;
     }
     __syncthreads();
-    const int t = cu_q[e];
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
         const float* po = part_o + base * d + c;
         float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
@@ -939,7 +1051,7 @@ int launch_decode(const void* q, void* out, float* part_o, float* part_ml, const
                                                 window, scale, n_splits, err, fa, grid, st);
         if (rc != 0) return rc;
         if (n_splits > 1)
-            return crane_launch(decode_merge_kernel, dim3(n_entries, nq), dim3(64), 0, st,
+            return crane_launch(decode_merge_kernel, dim3(n_entries, nq), dim3(D >= 128 ? 128 : 64), 0, st,
                                 (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, cu_q, nq,
                                 D, n_splits);
         return 0;
@@ -950,7 +1062,7 @@ int launch_decode(const void* q, void* out, float* part_o, float* part_ml, const
                           page_size, nq, nkv, window, scale * 1.4426950408889634f, n_splits, err, fa);
     const bool merged_inside = FUSED && fa.counters != nullptr;
     if (rc == 0 && n_splits > 1 && !merged_inside)
-        rc = crane_launch(decode_merge_kernel, dim3(n_entries, nq), dim3(64), 0, st,
+        rc = crane_launch(decode_merge_kernel, dim3(n_entries, nq), dim3(D >= 128 ? 128 : 64), 0, st,
                           (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, cu_q, nq, D,
                           n_splits);
     return rc;

@@ -80,3 +80,25 @@ static inline int crane_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, si
     const cudaError_t rc = cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
     return rc != cudaSuccess ? (int)rc : (int)cudaGetLastError();
 }
+
+// The same for a kernel whose CTAs form thread-block clusters of `cluster` CTAs.
+template <typename... KArgs, typename... Args>
+static inline int crane_launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                       dim3 cluster, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster.x;
+    attr[0].val.clusterDim.y = cluster.y;
+    attr[0].val.clusterDim.z = cluster.z;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_crane_pdl ? 2 : 1;
+    const cudaError_t rc = cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+    return rc != cudaSuccess ? (int)rc : (int)cudaGetLastError();
+}

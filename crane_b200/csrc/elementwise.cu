@@ -145,7 +145,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, GemmOut<T> delta, int 
 
 // The same, two neighbouring elements per step (rows of even length).
 template <typename T, int PER>
-__global__ void add_rmsnorm2_kernel(float* __restrict__ x, GemmOut<T> delta, int has_delta,
+__global__ void __launch_bounds__(PER <= 2 ? 512 : 1024) add_rmsnorm2_kernel(float* __restrict__ x, GemmOut<T> delta, int has_delta,
                                     const float* __restrict__ w, const int* __restrict__ rows,
                                     T* __restrict__ out, int hidden, float eps) {
     __shared__ float scratch[32];
@@ -193,6 +193,49 @@ __global__ void add_rmsnorm2_kernel(float* __restrict__ x, GemmOut<T> delta, int
         const int c = 2 * (threadIdx.x + k * blockDim.x);
         if (c < hidden) st2(o + c, v[k].x * rstd * wv[k].x, v[k].y * rstd * wv[k].y);
     }
+}
+
+// Few rows (a decode step): a row is shared by a cluster of CL CTAs, each with its
+// piece of the columns, so that CL times as many SMs fetch the row and its partial
+// sums.  Every CTA sends its sum of squares to all CTAs of the cluster through
+// distributed shared memory; after one cluster barrier each adds the CL values up in
+// rank order (so all get the same total) and finishes its piece.
+template <typename T, int CL>
+__global__ void __launch_bounds__(512) add_rmsnorm_cluster_kernel(float* __restrict__ x, GemmOut<T> delta,
+                                                                  int has_delta, const float* __restrict__ w,
+                                                                  T* __restrict__ out, int hidden, float eps) {
+    __shared__ float scratch[32];
+    __shared__ float sums[CL];
+    const int rank = blockIdx.x;                  // cluster (CL, 1, 1): the rank is the x index
+    const int row = blockIdx.y;
+    const int piece = hidden / CL;                // even, checked by the host
+    const int c = rank * piece + 2 * threadIdx.x;
+    const bool mine = 2 * (int)threadIdx.x < piece;
+    float* xr = x + (long long)row * hidden;
+    pdl_launch_dependents();
+    const float2 wv = mine ? ld2(w + c) : make_float2(0.f, 0.f);
+    pdl_wait();
+    float2 v = mine ? ld2(xr + c) : make_float2(0.f, 0.f);
+    if (has_delta && mine) {
+        const float2 d = delta.load2((long long)row * hidden + c);
+        v.x += d.x;
+        v.y += d.y;
+        st2(xr + c, v.x, v.y);
+    }
+    const float ss = block_sum(v.x * v.x + v.y * v.y, scratch);
+    if (threadIdx.x < CL) {
+        // my sum goes into slot `rank` of CTA threadIdx.x
+        uint32_t local = (uint32_t)__cvta_generic_to_shared(&sums[rank]), remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(threadIdx.x));
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(ss) : "memory");
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;\n"
+                 "barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    float total = 0.f;
+#pragma unroll
+    for (int i = 0; i < CL; ++i) total += sums[i];
+    const float rstd = rsqrtf(total / (float)hidden + eps);
+    if (mine) st2(out + (long long)row * hidden + c, v.x * rstd * wv.x, v.y * rstd * wv.y);
 }
 
 // ------------------------------------- rotary + per-head norm + cache write
@@ -505,6 +548,15 @@ __global__ void to_float_kernel(const T* __restrict__ in, float* __restrict__ ou
     if (i < n) out[i] = to_f32(in[i]);
 }
 
+static bool norm_cluster_on() {
+    static int on = -1;
+    if (on < 0) {
+        const char* v = getenv("CRANE_NORM_CLUSTER");
+        on = (v == nullptr || v[0] != '0') ? 1 : 0;
+    }
+    return on == 1;
+}
+
 // ------------------------------------------------------------------ C ABI
 // dtype: 0 = float, 1 = bf16.  Every function returns the CUDA launch status.
 #define DISPATCH_T(dtype, ...)                                   \
@@ -532,9 +584,22 @@ CRANE_API int crane_add_rmsnorm(int dtype, float* x, const void* delta, const fl
     int threads = ((hidden + per - 1) / per + 31) / 32 * 32;
     const bool aligned = ((uintptr_t)x | (uintptr_t)delta | (uintptr_t)delta_parts | (uintptr_t)w |
                           (uintptr_t)out) % 8 == 0 && part_stride % 2 == 0;
+    if (rows == nullptr && n_rows <= 64 && aligned && hidden % 16 == 0 && hidden <= 8192 && norm_cluster_on()) {
+        // few rows: a cluster of 4 CTAs per row, 8 for long rows
+        DISPATCH_T(dtype, {
+            GemmOut<T> d{(const T*)delta, delta_parts, n_parts, part_stride};
+            if (hidden >= 4096)
+                return crane_launch_cluster(add_rmsnorm_cluster_kernel<T, 8>, dim3(8, n_rows),
+                                            dim3((hidden / 16 + 31) / 32 * 32), 0, dim3(8, 1, 1), st, x, d,
+                                            has_delta, w, (T*)out, hidden, eps);
+            return crane_launch_cluster(add_rmsnorm_cluster_kernel<T, 4>, dim3(4, n_rows),
+                                        dim3((hidden / 8 + 31) / 32 * 32), 0, dim3(4, 1, 1), st, x, d,
+                                        has_delta, w, (T*)out, hidden, eps);
+        });
+    }
     if (hidden % 2 == 0 && hidden <= 8192 && aligned) {
         // pairs of neighbours: 2 or 4 pairs per thread
-        const int pp = hidden <= 4096 ? 2 : 4;
+        const int pp = hidden <= 2048 ? 2 : 4;
         const int th = ((hidden / 2 + pp - 1) / pp + 31) / 32 * 32;
         DISPATCH_T(dtype, {
             GemmOut<T> d{(const T*)delta, delta_parts, n_parts, part_stride};

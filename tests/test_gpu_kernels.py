@@ -87,6 +87,37 @@ def test_add_rmsnorm_from_partial_sums(K, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,hidden,parts", [(1, 2048, 9), (8, 2048, 0), (33, 4096, 6), (64, 176, 3)])
+def test_add_rmsnorm_few_rows_in_clusters(K, dtype, rows, hidden, parts):
+    """Few rows of a length that divides by 16 take the kernel that shares a row
+    among the CTAs of a cluster: same result as the plain formula, from a whole
+    product and from partial sums."""
+    from crane_b200.kernels import Partials
+    torch.manual_seed(rows + hidden)
+    x0 = torch.randn(rows, hidden, device=DEV) * 3
+    w = torch.rand(hidden, device=DEV) + 0.5
+    if parts:
+        cut = torch.randn(parts, rows, hidden, device=DEV)
+        total = cut[0].clone()
+        for i in range(1, parts):
+            total += cut[i]
+        delta, dval = Partials(cut), total.to(dtype).float()
+    else:
+        delta = torch.randn(rows, hidden, device=DEV).to(dtype)
+        dval = delta.float()
+    x = x0.clone()
+    out = torch.empty(rows, hidden, device=DEV, dtype=dtype)
+    K.add_rmsnorm(x, delta, w, 1e-5, out)
+    want_x = x0 + dval
+    assert torch.equal(x, want_x)
+    want = want_x.double() * torch.rsqrt((want_x.double() ** 2).mean(-1, keepdim=True) + 1e-5) * w.double()
+    assert rel_err(out, want) < (1e-6 if dtype == torch.float32 else 5e-3)
+    out2 = torch.empty_like(out)
+    K.add_rmsnorm(x, None, w, 1e-5, out2)                     # nothing to add: x stays
+    assert torch.equal(x, want_x) and rel_err(out2, want) < (1e-6 if dtype == torch.float32 else 5e-3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_silu_mul(K, dtype):
     n, inter = 9, 353
     gu = (3 * torch.randn(n, 2 * inter, device=DEV)).to(dtype)
