@@ -210,7 +210,8 @@ def time_decode_e2e(model, batch, context, steps, warmup, vocab):
     return n / dt, m.total * 4, batch * 4
 
 
-def time_prefill(model, tokens, vocab, reps=3):
+def time_prefill(model, tokens, vocab, reps=3, mark=False):
+    """`mark`: the last repetition lies between cudaProfilerStart and cudaProfilerStop."""
     import torch
     from crane_b200.engine import StepEntry
     runner = model.runner
@@ -219,10 +220,14 @@ def time_prefill(model, tokens, vocab, reps=3):
     for r in range(reps + 1):
         rid = 5000 + r
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if mark and r == reps:
+            torch.cuda.profiler.start()
         start.record()
         runner.step([StepEntry(rid, prompt, [tokens - 1])])
         stop.record()
         torch.cuda.synchronize()
+        if mark and r == reps:
+            torch.cuda.profiler.stop()
         runner.end(rid)
         if r > 0:                                 # the first run warms up
             ms = start.elapsed_time(stop)
@@ -280,7 +285,7 @@ def main():
     model = build_model(cfg, opts)
     runner = model.runner
     if args.only_prefill:
-        pms = time_prefill(model, 2048, vocab, reps=max(1, args.steps))
+        pms = time_prefill(model, 2048, vocab, reps=max(1, args.steps), mark=True)
         flops = prefill_flops(cfg, layers, 2048)
         print(json.dumps({"prefill": {"value": round(2048 * 1000.0 / pms, 1), "tokens": 2048,
                                       "ms": round(pms, 3), "layers": layers,

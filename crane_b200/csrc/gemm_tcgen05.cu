@@ -336,6 +336,80 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+// 32 consecutive accumulator columns of row `a` (values r[], first column b_first) go out:
+// with bias, as float or bf16, in whole 16-byte stores where the row allows it, or as
+// silu(gate) * up of 16 features.
+template <bool OUT_F32, bool SILU>
+__device__ __forceinline__ void store_chunk32(const GemmParams& p, const uint32_t (&r)[32], int a, int b_first) {
+    if (SILU) {
+        // columns 0..15 of the chunk: gate, 16..31: up, of features b_first / 2 + 0..15
+        __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (long long)a * p.ld_out + (b_first >> 1);
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float g = __uint_as_float(r[j]), u = __uint_as_float(r[16 + j]);
+            v[j] = g / (1.f + expf(-g)) * u;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; j += 8) {
+            uint4 w;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+            w.x = *(uint32_t*)&h0; w.y = *(uint32_t*)&h1;
+            w.z = *(uint32_t*)&h2; w.w = *(uint32_t*)&h3;
+            *(uint4*)(dst + j) = w;
+        }
+        return;
+    }
+    const long long idx = (long long)a * p.ld_out + b_first;
+    const bool whole = b_first + 32 <= p.rows_b;
+    if (OUT_F32) {
+        float* dst = (float*)p.out + idx;
+        if (whole && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                       __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                if (p.bias) { v.x += p.bias[b_first + j]; v.y += p.bias[b_first + j + 1];
+                              v.z += p.bias[b_first + j + 2]; v.w += p.bias[b_first + j + 3]; }
+                *(float4*)(dst + j) = v;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (b_first + j < p.rows_b)
+                    dst[j] = __uint_as_float(r[j]) + (p.bias ? p.bias[b_first + j] : 0.f);
+        }
+    } else {
+        __nv_bfloat16* dst = (__nv_bfloat16*)p.out + idx;
+        if (whole && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+                float v[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    v[q] = __uint_as_float(r[j + q]) + (p.bias ? p.bias[b_first + j + q] : 0.f);
+                uint4 w;
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]);
+                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[2], v[3]);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]);
+                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[6], v[7]);
+                w.x = *(uint32_t*)&h0; w.y = *(uint32_t*)&h1;
+                w.z = *(uint32_t*)&h2; w.w = *(uint32_t*)&h3;
+                *(uint4*)(dst + j) = w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (b_first + j < p.rows_b)
+                    dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]) +
+                                                 (p.bias ? p.bias[b_first + j] : 0.f));
+        }
+    }
+}
+
 // SILU: the B rows (weights) come in blocks of 32 = 16 gate rows then the 16 up
 // rows of the same features; the epilogue writes silu(gate) * up, half as many
 // columns as the product has (silu(x) = x / (1 + exp(-x)) in float:
@@ -345,8 +419,8 @@ __global__ void __launch_bounds__(NUM_THREADS)
 gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                             const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
     constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-    constexpr uint32_t TMEM_COLS = 2 * BN;                  // two accumulators
-    static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "tensor memory comes in powers of two");
+    static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "the epilogue reads 32 columns at a time");
+    constexpr uint32_t TMEM_COLS = 2 * BN <= 256 ? 256 : 512;   // two accumulators; powers of two only
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* smem_a = smem;
@@ -447,73 +521,7 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                 if (a >= p.rows_a) continue;
                 const int b_first = b0 + c0;
                 if (b_first >= p.rows_b) continue;
-                if (SILU) {
-                    // columns 0..15 of the chunk: gate, 16..31: up, of features b_first / 2 + 0..15
-                    __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (long long)a * p.ld_out + (b_first >> 1);
-                    float v[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const float g = __uint_as_float(r[j]), u = __uint_as_float(r[16 + j]);
-                        v[j] = g / (1.f + expf(-g)) * u;
-                    }
-#pragma unroll
-                    for (int j = 0; j < 16; j += 8) {
-                        uint4 w;
-                        __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
-                        __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-                        __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                        w.x = *(uint32_t*)&h0; w.y = *(uint32_t*)&h1;
-                        w.z = *(uint32_t*)&h2; w.w = *(uint32_t*)&h3;
-                        *(uint4*)(dst + j) = w;
-                    }
-                    continue;
-                }
-                const long long idx = (long long)a * p.ld_out + b_first;
-                const bool whole = b_first + 32 <= p.rows_b;
-                if (OUT_F32) {
-                    float* dst = (float*)p.out + idx;
-                    if (whole && ((uintptr_t)dst & 15) == 0) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                   __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                            if (p.bias) { v.x += p.bias[b_first + j]; v.y += p.bias[b_first + j + 1];
-                                          v.z += p.bias[b_first + j + 2]; v.w += p.bias[b_first + j + 3]; }
-                            *(float4*)(dst + j) = v;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (b_first + j < p.rows_b)
-                                dst[j] = __uint_as_float(r[j]) + (p.bias ? p.bias[b_first + j] : 0.f);
-                    }
-                } else {
-                    __nv_bfloat16* dst = (__nv_bfloat16*)p.out + idx;
-                    if (whole && ((uintptr_t)dst & 15) == 0) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            float v[8];
-#pragma unroll
-                            for (int q = 0; q < 8; ++q)
-                                v[q] = __uint_as_float(r[j + q]) + (p.bias ? p.bias[b_first + j + q] : 0.f);
-                            uint4 w;
-                            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]);
-                            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[2], v[3]);
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]);
-                            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[6], v[7]);
-                            w.x = *(uint32_t*)&h0; w.y = *(uint32_t*)&h1;
-                            w.z = *(uint32_t*)&h2; w.w = *(uint32_t*)&h3;
-                            *(uint4*)(dst + j) = w;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (b_first + j < p.rows_b)
-                                dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]) +
-                                                             (p.bias ? p.bias[b_first + j] : 0.f));
-                    }
-                }
+                store_chunk32<OUT_F32, SILU>(p, r, a, b_first);
             }
             // this warp is done with the accumulator: let the MMA warp reuse it
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -531,6 +539,206 @@ done:
     }
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Many tokens, two SMs per tile (tcgen05 cta_group::2).
+//
+// A cluster of two CTAs computes a 256 x BN tile: each CTA loads its own 128 rows of A and only
+// HALF of the tile's rows of B; the MMA, issued by the first CTA of the pair for both, reads A
+// and B from the shared memory of both SMs and leaves each CTA's 128 rows of the accumulator in
+// that CTA's tensor memory.  Per k-block a CTA thus takes in 16 KB + BN / 2 x 128 bytes instead
+// of 16 KB + BN x 128 bytes, which is what the single-CTA kernel above is bound by.
+//
+// Barriers: the stage-full barriers that count live in the first CTA (the peer's copies signal
+// them through the cta_group::2 form of the TMA load); stage-empty and accumulator-full are
+// signalled in both CTAs by one multicast commit; accumulator-empty lives in the first CTA and
+// takes the arrivals of the epilogue warps of both.  Every wait is bounded as above.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    return remote;
+}
+// dst in this CTA, the barrier (a shared::cluster address) in either CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                                 int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
+                                               uint32_t accumulate) {
+    const uint32_t z = 0;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n"
+        "}\n" ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(z)
+        : "memory");
+}
+// arrives on the barrier at this shared-memory offset in every CTA of `mask`
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t mask) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(bar), "h"(mask)
+        : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t local_bar, uint32_t rank) {
+    asm volatile(
+        "{\n"
+        ".reg .b32 remote;\n"
+        "mapa.shared::cluster.u32 remote, %0, %1;\n"
+        "mbarrier.arrive.shared::cluster.b64 _, [remote];\n"
+        "}\n" ::"r"(local_bar), "r"(rank)
+        : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n"
+                 "barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <int BN, int STAGES, bool SILU>
+__global__ void __launch_bounds__(NUM_THREADS)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                      const GemmParams p) {
+    static_assert(BN % 32 == 0 && BN >= 64 && BN <= 256, "BN / 2 rows of B per CTA, 32 columns per epilogue step");
+    constexpr int BH = BN / 2;                                   // rows of B that one CTA loads
+    constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BH * BK * 2;
+    constexpr uint32_t TMEM_COLS = 2 * BN <= 256 ? 256 : 512;    // two accumulators
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // both CTAs of a pair round up by the same amount, so offsets match across them
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + STAGES * A_BYTES;
+    uint64_t* bars = (uint64_t*)(smem + STAGES * (A_BYTES + B_BYTES));
+    uint64_t* full = bars;                       // [STAGES] used in the first CTA only
+    uint64_t* empty = bars + STAGES;             // [STAGES] in both
+    uint64_t* acc_full = bars + 2 * STAGES;      // [2] in both
+    uint64_t* acc_empty = bars + 2 * STAGES + 2; // [2] used in the first CTA only
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();                     // 0: issues the MMAs
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int tiles_a = (p.rows_a + 2 * BM - 1) / (2 * BM), tiles_b = (p.rows_b + BN - 1) / BN;
+    const int num_tiles = tiles_a * tiles_b;
+    const int num_kb = (p.k + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&full[s]), 1);
+            mbar_init(smem_u32(&empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&acc_full[b]), 1);
+            mbar_init(smem_u32(&acc_empty[b]), 8);               // the epilogue warps of both CTAs
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        // the same warp of both CTAs, the same slot offset
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(tmem_slot)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                          // the peer's barriers exist before anything signals them
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        pdl_wait();
+        int it = 0;
+        for (int tile = pair; tile < num_tiles; tile += num_pairs) {
+            const int a0 = (tile % tiles_a) * 2 * BM + (int)rank * BM;
+            const int b0 = (tile / tiles_a) * BN + (int)rank * BH;
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int s = it % STAGES;
+                if (!mbar_wait(smem_u32(&empty[s]), ((it / STAGES) & 1) ^ 1, abort_flag)) goto done;
+                const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
+                if (rank == 0) mbar_expect_tx(smem_u32(&full[s]), 2 * (A_BYTES + B_BYTES));   // both CTAs' bytes
+                tma_load_2d_pair(smem_u32(smem_a + s * A_BYTES), &map_a, bar, kb * BK, a0);
+                tma_load_2d_pair(smem_u32(smem_b + s * B_BYTES), &map_b, bar, kb * BK, b0);
+            }
+        }
+    } else if (warp == 1 && lane == 0 && rank == 0) {
+        // ---------------- MMA issuer (first CTA, for the pair) ----------------
+        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                               ((uint32_t)((2 * BM) >> 4) << 24);
+        int it = 0, local = 0;
+        for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local) {
+            const int acc = local & 1;
+            if (!mbar_wait(smem_u32(&acc_empty[acc]), ((local >> 1) & 1) ^ 1, abort_flag)) goto done;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int s = it % STAGES;
+                if (!mbar_wait(smem_u32(&full[s]), (it / STAGES) & 1, abort_flag)) goto done;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t da = smem_desc_sw128(smem_u32(smem_a + s * A_BYTES));
+                const uint64_t db = smem_desc_sw128(smem_u32(smem_b + s * B_BYTES));
+#pragma unroll
+                for (int kk = 0; kk < BK / UMMA_K; ++kk)
+                    umma_bf16_pair(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                umma_commit_pair(smem_u32(&empty[s]), 3);        // the stage is free in both CTAs
+            }
+            umma_commit_pair(smem_u32(&acc_full[acc]), 3);
+        }
+    } else if (warp >= 2) {
+        // ---------------- epilogue (both CTAs, each its 128 rows) ----------------
+        const int quarter = warp & 3;
+        int local = 0;
+        for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local) {
+            const int acc = local & 1;
+            const int a0 = (tile % tiles_a) * 2 * BM + (int)rank * BM, b0 = (tile / tiles_a) * BN;
+            if (!mbar_wait(smem_u32(&acc_full[acc]), (local >> 1) & 1, abort_flag)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int a = a0 + quarter * 32 + lane;
+            const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(trow + (uint32_t)c0, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (a >= p.rows_a) continue;
+                const int b_first = b0 + c0;
+                if (b_first >= p.rows_b) continue;
+                store_chunk32<false, SILU>(p, r, a, b_first);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(smem_u32(&acc_empty[acc]), 0);
+        }
+    }
+done:
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicOr(p.err, CRANE_ERR_WAIT_TIMEOUT);
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        __syncthreads();
+    }
+    cluster_sync_all();                          // neither CTA frees tensor memory the other's MMA may touch
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                      "r"(TMEM_COLS)
                      : "memory");
     }
@@ -601,6 +809,29 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPa
     return crane_launch(kern, dim3(ctas), dim3(NUM_THREADS), smem, st, ma, mb, p);
 }
 
+template <int BN, int STAGES, bool SILU>
+int launch_pair(const void* A, const void* B, int rows_a, int rows_b, int k, long long lda, long long ldb,
+                const GemmParams& p, cudaStream_t st) {
+    constexpr size_t smem = STAGES * (BM * BK * 2 + (BN / 2) * BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
+    auto kern = gemm_bf16_pair_kernel<BN, STAGES, SILU>;
+    static bool configured = false;
+    static int sms = 0;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return (int)cudaGetLastError();
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        configured = true;
+    }
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, A, rows_a, k, lda, BM) || !make_map(&mb, B, rows_b, k, ldb, BN / 2))
+        return (int)cudaErrorInvalidValue;
+    const int tiles = ((rows_a + 2 * BM - 1) / (2 * BM)) * ((rows_b + BN - 1) / BN);
+    const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+    return crane_launch_cluster(kern, dim3(2 * pairs), dim3(NUM_THREADS), smem, dim3(2, 1, 1), st, ma, mb, p);
+}
+
 template <bool OUT_F32, bool TRANSPOSED>
 int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid,
                 cudaStream_t st) {
@@ -646,13 +877,26 @@ CRANE_API int crane_gemm_bf16_tcgen05(const void* A, const void* B, const float*
     if (epilogue == 1) {
         // silu(gate) * up: bf16 output of rows_b / 2 columns; the weights' rows in blocks of 16 + 16
         if (transposed || split_k != 1 || out_f32 || bias != nullptr || (rows_b & 31) || (ld_out & 7) ||
-            ((uintptr_t)out & 15) || (bn != 128 && bn != 256))
+            ((uintptr_t)out & 15))
             return (int)cudaErrorInvalidValue;
         const int tiles = (int)(grid.x * grid.y);
-        return bn == 256 ? launch_persistent<256, 4, false, true>(ma, mb, p, tiles, st)
-                         : launch_persistent<128, 6, false, true>(ma, mb, p, tiles, st);
+        switch (bn) {
+            case 128: return launch_persistent<128, 6, false, true>(ma, mb, p, tiles, st);
+            case 160: return launch_persistent<160, 6, false, true>(ma, mb, p, tiles, st);
+            case 192: return launch_persistent<192, 5, false, true>(ma, mb, p, tiles, st);
+            case 224: return launch_persistent<224, 5, false, true>(ma, mb, p, tiles, st);
+            case 256: return launch_persistent<256, 4, false, true>(ma, mb, p, tiles, st);
+        }
+        return (int)cudaErrorInvalidValue;
     }
     if (epilogue != 0) return (int)cudaErrorInvalidValue;
+    if (!transposed && split_k == 1 && !out_f32 && (bn == 160 || bn == 192 || bn == 224)) {
+        // widths between 128 and 256: chosen when they fill the last wave of tiles better
+        const int tiles = (int)(grid.x * grid.y);
+        if (bn == 160) return launch_persistent<160, 6, false>(ma, mb, p, tiles, st);
+        if (bn == 192) return launch_persistent<192, 5, false>(ma, mb, p, tiles, st);
+        return launch_persistent<224, 5, false>(ma, mb, p, tiles, st);
+    }
     if (!transposed && split_k == 1 && (bn == 128 || bn == 256)) {
         const int tiles = (int)(grid.x * grid.y);
         if (bn == 256)
@@ -666,4 +910,35 @@ CRANE_API int crane_gemm_bf16_tcgen05(const void* A, const void* B, const float*
                           : dispatch_bn<true, false>(bn, ma, mb, p, grid, st);
     return transposed ? dispatch_bn<false, true>(bn, ma, mb, p, grid, st)
                       : dispatch_bn<false, false>(bn, ma, mb, p, grid, st);
+}
+
+// The same product as crane_gemm_bf16_tcgen05 for many tokens (bf16 output, untransposed, no
+// slices) on pairs of SMs: 256 x bn tiles, bn in 128, 192, 224, 256.  epilogue as there.
+CRANE_API int crane_gemm_bf16_pair(const void* A, const void* B, const float* bias, void* out, int rows_a,
+                                   int rows_b, int k, long long lda, long long ldb, long long ld_out,
+                                   int bn, int epilogue, int* err, cudaStream_t st) {
+    if (rows_a <= 0 || rows_b <= 0) return 0;
+    if (k <= 0 || (k & 7) || (lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15))
+        return (int)cudaErrorInvalidValue;
+    GemmParams p;
+    p.rows_a = rows_a; p.rows_b = rows_b; p.k = k;
+    p.out = out; p.ld_out = ld_out; p.split_stride = 0; p.bias = bias; p.err = err;
+    if (epilogue == 1) {
+        if (bias != nullptr || (rows_b & 31) || (ld_out & 7) || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
+        switch (bn) {
+            case 128: return launch_pair<128, 8, true>(A, B, rows_a, rows_b, k, lda, ldb, p, st);
+            case 192: return launch_pair<192, 7, true>(A, B, rows_a, rows_b, k, lda, ldb, p, st);
+            case 224: return launch_pair<224, 6, true>(A, B, rows_a, rows_b, k, lda, ldb, p, st);
+            case 256: return launch_pair<256, 6, true>(A, B, rows_a, rows_b, k, lda, ldb, p, st);
+        }
+        return (int)cudaErrorInvalidValue;
+    }
+    if (epilogue != 0) return (int)cudaErrorInvalidValue;
+    switch (bn) {
+        case 128: return launch_pair<128, 8, false>(A, B, rows_a, rows_b, k, lda, ldb, p, st);
+        case 192: return launch_pair<192, 7, false>(A, B, rows_a, rows_b, k, lda, ldb, p, st);
+        case 224: return launch_pair<224, 6, false>(A, B, rows_a, rows_b, k, lda, ldb, p, st);
+        case 256: return launch_pair<256, 6, false>(A, B, rows_a, rows_b, k, lda, ldb, p, st);
+    }
+    return (int)cudaErrorInvalidValue;
 }

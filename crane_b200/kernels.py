@@ -27,6 +27,7 @@ _SIGNATURES = {
     "crane_to_float": [I, P, P, L, P],
     "crane_gemm_simt": [I, I, P, P, P, P, I, I, I, L, L, L, P],
     "crane_gemm_bf16_tcgen05": [P, P, P, P, I, I, I, L, L, L, I, I, I, I, L, I, P, P],
+    "crane_gemm_bf16_pair": [P, P, P, P, I, I, I, L, L, L, I, I, P, P],
     "crane_paged_attention_simt": [I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P],
     "crane_paged_decode_attention_supports": [I, I, I],
     "crane_paged_decode_attention": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P],
@@ -194,6 +195,51 @@ class Kernels:
             eff = ctas / (-(-ctas // sms) * sms)
             if eff > best_eff + 0.02:
                 best, best_eff = s, eff
+        return best
+
+    PAIR_TILES = (256, 224, 192, 128)
+
+    def gemm_pair(self, x, w, bias, out, err, bn: int = 256, silu_mul: bool = False) -> None:
+        """out[M,N] (bf16) = x[M,K] @ w[N,K]^T (+ bias) for many tokens, every
+        256 x ``bn`` tile computed by two SMs together (tcgen05 cta_group::2).
+        ``silu_mul`` as in ``gemm_tcgen05``."""
+        M, K = x.shape
+        N = w.shape[0]
+        assert out.dtype == torch.bfloat16 and out.stride(1) == 1 and bn in self.PAIR_TILES
+        assert tuple(out.shape) == ((M, N // 2) if silu_mul else (M, N))
+        self._check(self.lib.crane_gemm_bf16_pair(
+            x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K, x.stride(0), w.stride(0),
+            out.stride(0), bn, 1 if silu_mul else 0, err.data_ptr(), self._stream(x)), "gemm_pair")
+
+    WIDE_TILES = (256, 224, 192, 160, 128)
+
+    @classmethod
+    def tile_width_for(cls, m: int, n: int, sms: int) -> int:
+        """The width of the 128 x width output tiles of a many-token product that
+        takes the fewest rounds of tiles over the SMs, times the width (plus a
+        little per tile); the widest among equals."""
+        best, best_cost = 256, None
+        for bn in cls.WIDE_TILES:
+            tiles = -(-m // 128) * -(-n // bn)
+            cost = -(-tiles // sms) * (bn + 16)
+            if best_cost is None or cost < best_cost:
+                best, best_cost = bn, cost
+        return best
+
+    PAIR_MIN_FLOPS = 4e10      # below this the pair kernel's set-up outweighs its better feeding
+
+    @classmethod
+    def pair_width_for(cls, m: int, n: int, k: int, sms: int) -> int:
+        """The tile width for ``gemm_pair``, or 0 where the single-SM kernel is the
+        better choice (small products, fewer than 256 rows)."""
+        if m < 256 or 2.0 * m * n * k < cls.PAIR_MIN_FLOPS:
+            return 0
+        best, best_cost = 0, None
+        for bn in cls.PAIR_TILES:
+            tiles = -(-m // 256) * -(-n // bn)
+            cost = -(-tiles // (sms // 2)) * (bn + 16)
+            if best_cost is None or cost < best_cost:
+                best, best_cost = bn, cost
         return best
 
     def gemm_tcgen05(self, x, w, bias, out, err, split_k: int = 1, swap: bool = False,

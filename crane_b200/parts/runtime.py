@@ -80,8 +80,12 @@ class Runtime:
             return False
         if w.shape[0] % 32 or out.stride(0) % 8 or out.data_ptr() % 16:
             return False
-        self.kernels.gemm_tcgen05(x, w, None, out, self.err, bn=256 if w.shape[0] >= 2048 else 128,
-                                  silu_mul=True)
+        pair = self.kernels.pair_width_for(M, w.shape[0], x.shape[1], self.num_sms)
+        if pair:
+            self.kernels.gemm_pair(x, w, None, out, self.err, bn=pair, silu_mul=True)
+        else:
+            self.kernels.gemm_tcgen05(x, w, None, out, self.err,
+                                      bn=self.kernels.tile_width_for(M, w.shape[0], self.num_sms), silu_mul=True)
         self.launches += 1
         return True
 
@@ -108,7 +112,14 @@ class Runtime:
                     return Partials(parts)
                 k.gemm_tcgen05(x, w, bias, out, self.err, swap=True, bn=bn)
             else:
-                k.gemm_tcgen05(x, w, bias, out, self.err, bn=256 if N >= 2048 else 128)
+                pair = k.pair_width_for(M, N, K, self.num_sms) if out.dtype == torch.bfloat16 else 0
+                bn = k.tile_width_for(M, N, self.num_sms)
+                if out.dtype == torch.float32 and bn not in (128, 256):
+                    bn = 256 if N >= 2048 else 128
+                if pair:
+                    k.gemm_pair(x, w, bias, out, self.err, bn=pair)       # two SMs per 256-row tile
+                else:
+                    k.gemm_tcgen05(x, w, bias, out, self.err, bn=bn)
             self.launches += 1
             return out
         if out.dtype == torch.bfloat16:

@@ -100,8 +100,11 @@ def gemm(a):
 
         def fn():
             w = ws[state["i"] % a.sets]; state["i"] += 1
-            K.gemm_tcgen05(x, w, None, out, err, bn=bn, silu_mul=a.silu_mul)
-        extra = {"mode": "persistent", "bn": bn, "silu_mul": a.silu_mul}
+            if a.pair:
+                K.gemm_pair(x, w, None, out, err, bn=bn, silu_mul=a.silu_mul)
+            else:
+                K.gemm_tcgen05(x, w, None, out, err, bn=bn, silu_mul=a.silu_mul)
+        extra = {"mode": "pairs of SMs" if a.pair else "persistent", "bn": bn, "silu_mul": a.silu_mul}
     t = _time(fn, a.warmup, a.reps)
     assert int(err.item()) == 0
     nbytes = 2 * (a.m * a.k + a.n * a.k) + out.numel() * out.element_size()
@@ -183,6 +186,7 @@ def main(argv=None) -> int:
     g.add_argument("--k", type=int, required=True); g.add_argument("--bn", type=int, default=0)
     g.add_argument("--slices", type=int, default=0); g.add_argument("--sets", type=int, default=1)
     g.add_argument("--silu-mul", action="store_true")
+    g.add_argument("--pair", action="store_true", help="many tokens: the kernel in which two SMs share a tile")
     for name in ("decode-attention", "prefill-attention"):
         p = sub.add_parser(name)
         p.add_argument("--q-heads", type=int, default=16); p.add_argument("--kv-heads", type=int, default=4)

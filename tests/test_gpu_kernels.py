@@ -357,13 +357,16 @@ def test_sampling_frequencies_follow_the_softmax(K):
 
 
 @pytest.mark.parametrize("M,N,K_,bn", [(128, 128, 64, 128), (128, 256, 128, 256), (300, 520, 160, 128),
-                                       (2048, 3072, 2048, 256), (77, 1000, 352, 128)])
+                                       (2048, 3072, 2048, 256), (77, 1000, 352, 128), (2048, 3072, 2048, 192),
+                                       (300, 1000, 352, 224), (260, 520, 160, 160)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemm_tcgen05_many_tokens(K, err, M, N, K_, bn, out_dtype):
     a = torch.randn(M, K_, device=DEV).bfloat16()
     w = torch.randn(N, K_, device=DEV).bfloat16()
     bias = torch.randn(N, device=DEV)
     out = torch.full((M, N), 7.0, device=DEV, dtype=out_dtype)
+    if out_dtype == torch.float32 and bn not in (128, 256):
+        bn = 256                                  # the widths between 128 and 256 write bfloat16 only
     K.gemm_tcgen05(a, w, bias, out, err, bn=bn)
     torch.cuda.synchronize()
     assert int(err.item()) == 0
@@ -371,6 +374,41 @@ def test_gemm_tcgen05_many_tokens(K, err, M, N, K_, bn, out_dtype):
     assert rel_err(out, want) < (acc_tol(K_) if out_dtype == torch.float32 else 5e-3)
     K.gemm_tcgen05(a, w, None, out, err, bn=bn)
     assert rel_err(out, a.double() @ w.double().T) < (acc_tol(K_) if out_dtype == torch.float32 else 5e-3)
+
+
+@pytest.mark.parametrize("M,N,K_,bn", [(256, 256, 64, 256), (256, 512, 128, 256), (300, 520, 160, 128),
+                                       (2048, 3072, 2048, 192), (700, 1000, 352, 224), (2048, 2048, 6144, 256)])
+def test_gemm_on_pairs_of_sms(K, err, M, N, K_, bn):
+    """The kernel in which two SMs share a 256-row tile: each loads half of the
+    weights' rows, both halves must land in the right columns."""
+    torch.manual_seed(M + N)
+    a = torch.randn(M, K_, device=DEV).bfloat16()
+    w = torch.randn(N, K_, device=DEV).bfloat16()
+    bias = torch.randn(N, device=DEV)
+    out = torch.full((M, N), 7.0, device=DEV, dtype=torch.bfloat16)
+    K.gemm_pair(a, w, bias, out, err, bn=bn)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    assert rel_err(out, a.double() @ w.double().T + bias.double()) < 5e-3
+    K.gemm_pair(a, w, None, out, err, bn=bn)
+    assert rel_err(out, a.double() @ w.double().T) < 5e-3
+
+
+@pytest.mark.parametrize("M,I,K_,bn", [(256, 128, 64, 128), (300, 352, 160, 192), (2048, 6144, 2048, 224),
+                                       (130, 1008, 64, 256)])
+def test_gemm_on_pairs_of_sms_with_silu_mul(K, err, M, I, K_, bn):
+    torch.manual_seed(I + M)
+    a = torch.randn(M, K_, device=DEV).bfloat16()
+    gate = (torch.randn(I, K_, device=DEV) * 0.05).bfloat16()
+    up = (torch.randn(I, K_, device=DEV) * 0.05).bfloat16()
+    w = torch.stack([gate.view(-1, 16, K_), up.view(-1, 16, K_)], dim=1).reshape(2 * I, K_).contiguous()
+    out = torch.full((M, I), 7.0, device=DEV, dtype=torch.bfloat16)
+    K.gemm_pair(a, w, None, out, err, bn=bn, silu_mul=True)
+    g = a.double() @ gate.double().T
+    u = a.double() @ up.double().T
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    assert rel_err(out, g / (1 + torch.exp(-g)) * u) < 6e-3
 
 
 @pytest.mark.parametrize("M,bn", [(1, 16), (8, 16), (16, 16), (17, 32), (33, 64), (64, 64)])
@@ -539,7 +577,8 @@ def test_fused_decode_attention_equals_the_separate_kernels(K, err, d, nq, nkv, 
         assert rel_err(got, want.double()) < 4e-3
 
 
-@pytest.mark.parametrize("M,I,K_,bn", [(128, 128, 64, 128), (300, 352, 160, 128), (2048, 6144, 2048, 256)])
+@pytest.mark.parametrize("M,I,K_,bn", [(128, 128, 64, 128), (300, 352, 160, 128), (2048, 6144, 2048, 256),
+                                       (2048, 6144, 2048, 224), (300, 352, 160, 192), (130, 1008, 64, 160)])
 def test_gemm_tcgen05_with_silu_mul_epilogue(K, err, M, I, K_, bn):
     a = torch.randn(M, K_, device=DEV).bfloat16()
     gate = (torch.randn(I, K_, device=DEV) / K_ ** 0.5).bfloat16()
