@@ -195,6 +195,65 @@ __global__ void __launch_bounds__(PER <= 2 ? 512 : 1024) add_rmsnorm2_kernel(flo
     }
 }
 
+// Many rows: a warp per row and no block-wide barrier.  A lane owns CH pieces of 8
+// neighbouring elements (piece c at column (c * 32 + lane) * 8), all of whose loads are in
+// flight together; the sum of squares goes around the warp by shuffles.  For a delta that is
+// one tensor (not partial sums) and rows of CH * 256 elements.
+template <typename T, int CH>
+__global__ void __launch_bounds__(256) add_rmsnorm_warp_kernel(float* __restrict__ x, const T* __restrict__ delta,
+                                                               const float* __restrict__ w, T* __restrict__ out,
+                                                               int n_rows, float eps) {
+    constexpr int HIDDEN = CH * 256;
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (row >= n_rows) return;
+    float* xr = x + (long long)row * HIDDEN;
+    float v[CH][8];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+        const int col = (c * 32 + lane) * 8;
+        const float4 a = *(const float4*)(xr + col), b = *(const float4*)(xr + col + 4);
+        v[c][0] = a.x; v[c][1] = a.y; v[c][2] = a.z; v[c][3] = a.w;
+        v[c][4] = b.x; v[c][5] = b.y; v[c][6] = b.z; v[c][7] = b.w;
+    }
+    if (delta != nullptr) {
+        const T* dr = delta + (long long)row * HIDDEN;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            const int col = (c * 32 + lane) * 8;
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                const float2 d = ld2(dr + col + j);
+                v[c][j] += d.x;
+                v[c][j + 1] += d.y;
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            const int col = (c * 32 + lane) * 8;
+            *(float4*)(xr + col) = make_float4(v[c][0], v[c][1], v[c][2], v[c][3]);
+            *(float4*)(xr + col + 4) = make_float4(v[c][4], v[c][5], v[c][6], v[c][7]);
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; ++c)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += v[c][j] * v[c][j];
+    const float rstd = rsqrtf(warp_sum(ss) / (float)HIDDEN + eps);
+    T* o = out + (long long)row * HIDDEN;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+        const int col = (c * 32 + lane) * 8;
+        const float4 wa = *(const float4*)(w + col), wb = *(const float4*)(w + col + 4);
+        st2(o + col, v[c][0] * rstd * wa.x, v[c][1] * rstd * wa.y);
+        st2(o + col + 2, v[c][2] * rstd * wa.z, v[c][3] * rstd * wa.w);
+        st2(o + col + 4, v[c][4] * rstd * wb.x, v[c][5] * rstd * wb.y);
+        st2(o + col + 6, v[c][6] * rstd * wb.z, v[c][7] * rstd * wb.w);
+    }
+}
+
 // Few rows (a decode step): a row is shared by a cluster of CL CTAs, each with its
 // piece of the columns, so that CL times as many SMs fetch the row and its partial
 // sums.  Every CTA sends its sum of squares to all CTAs of the cluster through
@@ -596,6 +655,19 @@ CRANE_API int crane_add_rmsnorm(int dtype, float* x, const void* delta, const fl
                                         dim3((hidden / 8 + 31) / 32 * 32), 0, dim3(4, 1, 1), st, x, d,
                                         has_delta, w, (T*)out, hidden, eps);
         });
+    }
+    if (rows == nullptr && n_rows >= 256 && delta_parts == nullptr && hidden % 256 == 0 && hidden <= 2048 &&
+        ((uintptr_t)x | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)out) % 16 == 0) {
+        // many rows: a warp per row
+        const dim3 g((n_rows + 7) / 8), b(256);
+#define WARP_CASE(CH)                                                                                  \
+    case CH:                                                                                           \
+        DISPATCH_T(dtype, return crane_launch(add_rmsnorm_warp_kernel<T, CH>, g, b, 0, st, x, (const T*)delta, w, \
+                                              (T*)out, n_rows, eps));
+        switch (hidden / 256) {
+            WARP_CASE(1) WARP_CASE(2) WARP_CASE(3) WARP_CASE(4) WARP_CASE(5) WARP_CASE(6) WARP_CASE(7) WARP_CASE(8)
+        }
+#undef WARP_CASE
     }
     if (hidden % 2 == 0 && hidden <= 8192 && aligned) {
         // pairs of neighbours: 2 or 4 pairs per thread

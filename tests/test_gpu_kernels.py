@@ -87,6 +87,24 @@ def test_add_rmsnorm_from_partial_sums(K, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,hidden", [(300, 2048), (257, 768), (2048, 256)])
+def test_add_rmsnorm_many_rows_a_warp_per_row(K, dtype, rows, hidden):
+    """Many rows of a length that divides by 256 take the kernel with a warp per row."""
+    torch.manual_seed(rows)
+    x0 = torch.randn(rows, hidden, device=DEV) * 2
+    delta = torch.randn(rows, hidden, device=DEV).to(dtype)
+    w = torch.rand(hidden, device=DEV) + 0.5
+    for d in (delta, None):
+        x = x0.clone()
+        out = torch.empty(rows, hidden, device=DEV, dtype=dtype)
+        K.add_rmsnorm(x, d, w, 1e-5, out)
+        want_x = x0 + (d.float() if d is not None else 0)
+        assert torch.equal(x, want_x)
+        want = want_x.double() * torch.rsqrt((want_x.double() ** 2).mean(-1, keepdim=True) + 1e-5) * w.double()
+        assert rel_err(out, want) < (1e-6 if dtype == torch.float32 else 5e-3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("rows,hidden,parts", [(1, 2048, 9), (8, 2048, 0), (33, 4096, 6), (64, 176, 3)])
 def test_add_rmsnorm_few_rows_in_clusters(K, dtype, rows, hidden, parts):
     """Few rows of a length that divides by 16 take the kernel that shares a row
