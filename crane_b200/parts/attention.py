@@ -75,6 +75,8 @@ class GqaAttention(Part):
         self.q_norm = weights.get(p + "query_layernorm.weight") if a.get("qk_norm") else None
         self.k_norm = weights.get(p + "key_layernorm.weight") if a.get("qk_norm") and self.own_kv else None
         self.position = build_part(a["position"]) if a.get("position") is not None else None
+        if self.position is not None:
+            self.position.load(weights, rt)          # a position encoding may have tensors of its own
         self.qkv_cols = self.qkv_w.shape[0]
         self.max_splits = int(os.environ.get("CRANE_DECODE_SPLITS", "32"))
 
