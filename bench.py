@@ -32,6 +32,12 @@ MODEL = {
     "rope_scaling": {"alpha": 1000.0, "type": "dynamic"}, "use_qk_norm": True,
     "tie_word_embeddings": True, "attention_bias": False,
 }
+# the other layer sizes of the baseline's configurations, for --sizes (the default run keeps 1.8B)
+OTHER_SIZES = {
+    "4b": {"hidden_size": 3072, "intermediate_size": 8192, "num_attention_heads": 32, "num_key_value_heads": 8},
+    "7b": {"hidden_size": 4096, "intermediate_size": 14336, "num_attention_heads": 32, "num_key_value_heads": 8,
+           "vocab_size": 128167, "tie_word_embeddings": False},
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -254,6 +260,8 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
     ap.add_argument("--only-prefill", action="store_true",
                     help="measure the 2,048-token prefill alone (for profiling); prints its record only")
+    ap.add_argument("--sizes", default="1.8b", choices=["1.8b", "4b", "7b"],
+                    help="layer sizes: Hunyuan 1.8B (the default, the headline configuration), 4B or 7B")
     ap.add_argument("--only-decode", action="store_true",
                     help="measure the decode step alone (for profiling: the timed steps lie between "
                          "cudaProfilerStart and cudaProfilerStop); prints its record only")
@@ -267,6 +275,7 @@ def main():
 
     import torch
     cfg = dict(MODEL)
+    cfg.update(OTHER_SIZES.get(args.sizes, {}))
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
@@ -315,11 +324,11 @@ def main():
     e2e_value, h2d, d2h = time_decode_e2e(model, args.batch, args.context, args.steps, args.warmup, vocab)
 
     out = {
-        "metric": "decode tokens/s (Hunyuan-1.8B sizes, batch %d, context %d)" % (args.batch, args.context),
+        "metric": "decode tokens/s (Hunyuan-%s sizes, batch %d, context %d)" % (args.sizes.upper(), args.batch, args.context),
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"model": "Hunyuan-1.8B-sized, random weights", "layers": layers,
+        "config": {"model": "Hunyuan-%s-sized, random weights" % args.sizes.upper(), "layers": layers,
                    "layers_of_model": full_layers, "hidden": cfg["hidden_size"],
                    "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],

@@ -99,7 +99,8 @@ class Runtime:
                 # dimension is cut into slices until every SM has a tile to stream
                 bn = 16 if M <= 16 else 32 if M <= 32 else 64
                 tiles = (N + 127) // 128
-                slices = k.slices_for(tiles, K, self.num_sms)
+                # at most 8: the consumers of partial sums fetch eight slices at a time
+                slices = min(k.slices_for(tiles, K, self.num_sms), 8)
                 if slices > 1:
                     parts = self.ws.get("splitk:" + str(N), slices * self.split_rows, N,
                                         torch.float32, cap=slices * self.split_rows)
