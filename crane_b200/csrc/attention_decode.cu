@@ -887,8 +887,37 @@ paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
     }
 }
 
+// One thread per output column: the (max, sum) pairs and this column of up to MAXS slices,
+// all loads in flight together, added in slice order.
+template <int MAXS>
+__device__ __forceinline__ void merge_column(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                             __nv_bfloat16* __restrict__ out, long long base, int t, int nq,
+                                             int h, int d, int n_splits) {
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        float2 ml[MAXS];
+        float o[MAXS];
+#pragma unroll
+        for (int s = 0; s < MAXS; ++s) {
+            ml[s] = s < n_splits ? *(const float2*)(part_ml + (base + s) * 2) : make_float2(-INFINITY, 0.f);
+            o[s] = s < n_splits ? part_o[(base + s) * d + c] : 0.f;
+        }
+        float M = -INFINITY;
+#pragma unroll
+        for (int s = 0; s < MAXS; ++s) M = fmaxf(M, ml[s].x);
+        const float mb = (M == -INFINITY) ? 0.f : M;
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int s = 0; s < MAXS; ++s) {
+            const float f = exp2f(ml[s].x - mb);           // 0 for the slices beyond n_splits
+            L += f * ml[s].y;
+            acc += f * o[s];
+        }
+        out[((long long)t * nq + h) * d + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    }
+}
+
 // out[t, h, :] = sum_s w_s o_s / sum_s w_s l_s with w_s = exp2(m_s - max m).
-// One CTA per (request, query head), a thread per output column.  Up to 16 slices: every
+// One CTA per (request, query head), a thread per output column.  Up to 32 slices: every
 // thread fetches the slices' (max, sum) pairs and its column of their outputs with all loads
 // in flight together and works the weights out itself.  More slices: the pairs are fetched by
 // one thread each, the weights go through shared memory, and the outputs are summed with
@@ -903,28 +932,11 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
     const int e = blockIdx.x, h = blockIdx.y;
     const long long base = ((long long)e * nq + h) * n_splits;
     const int t = cu_q[e];
-    if (n_splits <= 16) {
-        for (int c = threadIdx.x; c < d; c += blockDim.x) {
-            float2 ml[16];
-            float o[16];
-#pragma unroll
-            for (int s = 0; s < 16; ++s) {
-                ml[s] = s < n_splits ? *(const float2*)(part_ml + (base + s) * 2) : make_float2(-INFINITY, 0.f);
-                o[s] = s < n_splits ? part_o[(base + s) * d + c] : 0.f;
-            }
-            float M = -INFINITY;
-#pragma unroll
-            for (int s = 0; s < 16; ++s) M = fmaxf(M, ml[s].x);
-            const float mb = (M == -INFINITY) ? 0.f : M;
-            float L = 0.f, acc = 0.f;
-#pragma unroll
-            for (int s = 0; s < 16; ++s) {
-                const float f = exp2f(ml[s].x - mb);       // 0 for the slices beyond n_splits
-                L += f * ml[s].y;
-                acc += f * o[s];
-            }
-            out[((long long)t * nq + h) * d + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
-        }
+    if (n_splits <= 64) {
+        // all loads of a thread go out together; 16 slices' worth of registers when that is enough
+        if (n_splits <= 16) merge_column<16>(part_o, part_ml, out, base, t, nq, h, d, n_splits);
+        else if (n_splits <= 32) merge_column<32>(part_o, part_ml, out, base, t, nq, h, d, n_splits);
+        else merge_column<64>(part_o, part_ml, out, base, t, nq, h, d, n_splits);
         return;
     }
     for (int s = threadIdx.x; s < n_splits; s += blockDim.x) {
