@@ -98,8 +98,13 @@ class Kernels:
         self.lib.crane_set_pdl.restype = None
         self.lib.crane_set_pdl(0 if os.environ.get("CRANE_PDL", "1") == "0" else 1)
 
-    @staticmethod
-    def _stream(t: torch.Tensor) -> int:
+    # While a model runs a step, every launch goes to the stream that was current when the step
+    # began (looked up once, not per launch); outside a step the current stream is asked for.
+    pinned_stream: Optional[int] = None
+
+    def _stream(self, t: torch.Tensor) -> int:
+        if self.pinned_stream is not None:
+            return self.pinned_stream
         return torch.cuda.current_stream(t.device).cuda_stream
 
     @staticmethod

@@ -120,21 +120,29 @@ class Workspace:
         self.device = device
         self.max_rows = max_rows
         self._bufs: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
+        self._views: Dict[Tuple[str, int, int, torch.dtype], torch.Tensor] = {}
         self.generation = 0          # goes up whenever a buffer is replaced by a larger one
 
     def get(self, name: str, rows: int, cols: int, dtype: torch.dtype,
             cap: Optional[int] = None) -> torch.Tensor:
         """[rows, cols] of the buffer ``name``.  It is allocated for ``cap`` rows
         (default: the largest step) and only ever replaced by a larger one."""
+        view = self._views.get((name, rows, cols, dtype))
+        if view is not None:
+            return view
         key = (name, cols, dtype)
         buf = self._bufs.get(key)
         if buf is None or buf.shape[0] < rows:
             cap = max(rows, self.max_rows if cap is None else cap)
             if buf is not None:
                 self.generation += 1
+                self._views = {k: v for k, v in self._views.items() if (k[0], k[2], k[3]) != key}
             buf = torch.empty((cap, cols), dtype=dtype, device=self.device)
             self._bufs[key] = buf
-        return buf[:rows]
+        view = buf[:rows]
+        if len(self._views) < 4096:
+            self._views[(name, rows, cols, dtype)] = view
+        return view
 
     def zeros(self, name: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
         """A buffer that starts as zeros and is never replaced (counters that
@@ -144,6 +152,7 @@ class Workspace:
         if buf is None or buf.shape[0] < rows:
             if buf is not None:
                 self.generation += 1
+                self._views = {k: v for k, v in self._views.items() if (k[0], k[2], k[3]) != key}
             buf = torch.zeros((rows, cols), dtype=dtype, device=self.device)
             self._bufs[key] = buf
         return buf[:rows]

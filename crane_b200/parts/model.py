@@ -70,6 +70,16 @@ class DecoderModel:
         per step of the schedule) and returns float logits
         [wanted rows, vocab] (an empty tensor if nothing is wanted)."""
         rt = self.rt
+        k = rt.kernels
+        outer = k.pinned_stream
+        k.pinned_stream = torch.cuda.current_stream(rt.device).cuda_stream
+        try:
+            return self._forward(ctx, caches)
+        finally:
+            k.pinned_stream = outer
+
+    def _forward(self, ctx, caches: List[LayerCache]) -> torch.Tensor:
+        rt = self.rt
         n = ctx.n_tokens
         x = rt.ws.get("residual", n, self.spec.hidden_size, torch.float32)
         self.embed.forward(ctx.tokens, x, rt, getattr(ctx, "deferred_tokens", None))
