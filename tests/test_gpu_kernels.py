@@ -429,7 +429,7 @@ def test_gemm_on_pairs_of_sms_with_silu_mul(K, err, M, I, K_, bn):
     assert rel_err(out, g / (1 + torch.exp(-g)) * u) < 6e-3
 
 
-@pytest.mark.parametrize("M,bn", [(1, 16), (8, 16), (16, 16), (17, 32), (33, 64), (64, 64)])
+@pytest.mark.parametrize("M,bn", [(1, 16), (8, 16), (16, 16), (17, 32), (33, 64), (64, 64), (100, 128), (200, 256)])
 @pytest.mark.parametrize("N,K_,split", [(256, 128, 1), (3072, 2048, 6), (1000, 352, 3), (120818, 256, 1),
                                         (2048, 6144, 9)])
 def test_gemm_tcgen05_few_tokens_swapped_and_split(K, err, M, bn, N, K_, split):
