@@ -226,40 +226,48 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t tmem_o = tmem_base + 256;          // S buffers at columns 0 and 128, O at 256
     pdl_launch_dependents();
 
-    if (warp == 0 && lane == 0 && n_tiles > 0) {
-        // ---------------- TMA ----------------
+    if (warp == 0 && n_tiles > 0) {
+        // ---------------- TMA: the whole warp ----------------
+        // A tile of K and a tile of V are 2 x (pages per tile) x 2 halves copies, at most 32: every
+        // lane looks its page number up and issues its one copy, so that the look-ups and the
+        // issue of the copies take the time of one, not of all in a row (one lane doing them all
+        // took longer per tile than the softmax or the products).
         pdl_wait();
-        mbar_expect_tx(smem_u32(q_full), TILE_BYTES);
-        tma_load_2d(smem_u32(sm_q), &map_q, smem_u32(q_full), h * D, row0 + r_begin);
-        tma_load_2d(smem_u32(sm_q + HALF_BYTES), &map_q, smem_u32(q_full), h * D + 64, row0 + r_begin);
+        if (lane == 0) {
+            mbar_expect_tx(smem_u32(q_full), TILE_BYTES);
+            tma_load_2d(smem_u32(sm_q), &map_q, smem_u32(q_full), h * D, row0 + r_begin);
+            tma_load_2d(smem_u32(sm_q + HALF_BYTES), &map_q, smem_u32(q_full), h * D + 64, row0 + r_begin);
+        }
         const int ps = p.page_size;                    // 16, 32, 64 or 128
-        const int chunks = BKV / ps;                   // pages per tile
+        const int shift = 31 - __clz(ps);
+        const int chunks = BKV >> shift;               // pages per tile: 8, 4, 2 or 1
+        const int per_kv = 2 * chunks;                 // copies per tile of K (or V)
+        const bool worker = lane < 2 * per_kv;
+        const int my_kv = lane / per_kv, c = (lane % per_kv) >> 1, hf = lane & 1;
         for (int j = 0; j < n_tiles; ++j) {
             const int s = j & 1;
             const uint32_t parity = ((j >> 1) & 1) ^ 1;
-            const int key0 = (t_begin + j) * BKV;
+            // a page that lies wholly after the last key is read as the last valid one: its keys
+            // are masked, only the byte count has to be complete (likewise a page wholly before
+            // the window's first key)
+            int blk = (((t_begin + j) * BKV) >> shift) + c;
+            blk = max(lo >> shift, min(blk, p_last >> shift));
+            int page = worker ? table[blk] : 0;
+            if (page < 0 || page >= p.num_pages) {
+                atomicOr(p.err, CRANE_ERR_PAGE_RANGE);
+                page = 0;
+            }
+            const int row = (page * p.nkv + g) << shift;
             for (int kv = 0; kv < 2; ++kv) {
                 uint64_t* full = kv ? &v_full[s] : &k_full[s];
                 uint64_t* empty = kv ? &v_empty[s] : &k_empty[s];
                 uint8_t* dst = (kv ? sm_v : sm_k) + s * TILE_BYTES;
-                const CUtensorMap* map = kv ? &map_v : &map_k;
                 if (!mbar_wait(smem_u32(empty), parity, abort_flag)) goto done;
-                mbar_expect_tx(smem_u32(full), TILE_BYTES);
-                for (int c = 0; c < chunks; ++c) {
-                    // a page that lies wholly after the last key is read as the last valid one:
-                    // its keys are masked, only the byte count has to be complete
-                    // (likewise a page wholly before the window's first key)
-                    int blk = (key0 + c * ps) / ps;
-                    blk = max(lo / ps, min(blk, p_last / ps));
-                    int page = table[blk];
-                    if (page < 0 || page >= p.num_pages) {
-                        atomicOr(p.err, CRANE_ERR_PAGE_RANGE);
-                        page = 0;
-                    }
-                    const int row = (page * p.nkv + g) * ps;
-                    tma_load_2d(smem_u32(dst + c * ps * 128), map, smem_u32(full), 0, row);
-                    tma_load_2d(smem_u32(dst + HALF_BYTES + c * ps * 128), map, smem_u32(full), 64, row);
-                }
+                if (lane == 0) mbar_expect_tx(smem_u32(full), TILE_BYTES);
+                __syncwarp();
+                if (worker && my_kv == kv)
+                    tma_load_2d(smem_u32(dst + hf * HALF_BYTES + c * ps * 128), kv ? &map_v : &map_k,
+                                smem_u32(full), hf * 64, row);
             }
         }
     } else if (warp == 1 && lane == 0 && n_tiles > 0) {
