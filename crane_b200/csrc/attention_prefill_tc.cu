@@ -31,7 +31,7 @@ namespace {
 constexpr int D = 128;            // head size
 constexpr int BQ = 128;           // query rows per CTA = MMA M
 constexpr int BKV = 128;          // keys per tile
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;      // warp 0: TMA, warp 1: MMA, warps 2..9: softmax, two threads per query row
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 constexpr uint32_t HALF_BYTES = 128 * 128;          // 128 rows x 64 bf16: one swizzled half tile
 constexpr uint32_t TILE_BYTES = 2 * HALF_BYTES;     // 128 x 128 bf16
@@ -171,6 +171,8 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint64_t* pv_done = bars + 14;      // the O product of a tile is done
     uint32_t* tmem_slot = (uint32_t*)(bars + 15);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    float* sm_x = (float*)(bars + 16);             // [2 tiles in turn][2 halves][128 rows]: what the two
+                                                   // threads of a row tell each other (maximum, sum)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -204,9 +206,9 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_init(smem_u32(&k_empty[s]), 1);
             mbar_init(smem_u32(&v_empty[s]), 1);
             mbar_init(smem_u32(&s_full[s]), 1);
-            mbar_init(smem_u32(&s_empty[s]), 4);
+            mbar_init(smem_u32(&s_empty[s]), 8);
         }
-        mbar_init(smem_u32(p_full), 4);
+        mbar_init(smem_u32(p_full), 8);
         mbar_init(smem_u32(pv_done), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -309,31 +311,40 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             umma_commit(smem_u32(&v_empty[s]));
         }
     } else if (warp >= 2 && n_tiles > 0) {
-        // ---------------- softmax, correction, epilogue: one thread per query row ----------------
+        // ---------------- softmax, correction, epilogue: two threads per query row ----------------
+        // Warps w and w + 4 own the same 32 rows (a warp reaches the lanes of tensor memory given by
+        // its index modulo 4); the first takes keys 0..63 of every tile and columns 0..63 of O, the
+        // second the other halves.  They agree on the row's maximum through shared memory once per
+        // tile and keep a partial sum each.  Eight softmax warps give every scheduler two warps to
+        // alternate between and halve the chain of exponentials and conversions per tile.
+        constexpr int HK = BKV / 2;
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;                  // row of the tile = lane of tensor memory
         const int pos = pos0 + r_begin + r;                 // this row's position
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        float m_ref = -INFINITY, l = 0.f;                   // maximum in use, running sum
+        const int pair_bar = 1 + quarter;                   // named barrier of the two warps of these rows
+        float m_ref = -INFINITY, l = 0.f;                   // maximum in use, running sum of this half
         for (int j = 0; j < n_tiles; ++j) {
             const int s = j & 1;
             if (!mbar_wait(smem_u32(&s_full[s]), (j >> 1) & 1, abort_flag)) goto done;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int key_base = (t_begin + j) * BKV;
-            // the whole row of scores into registers, then the buffer is free for the next S
-            uint32_t v[BKV];
+            const int tile_base = (t_begin + j) * BKV;
+            const int key_base = tile_base + half * HK;     // first key of this thread's half
+            // this half of the row of scores into registers, then the buffer is free for the next S
+            uint32_t v[HK];
 #pragma unroll
-            for (int c0 = 0; c0 < BKV; c0 += 32) tmem_ld32(tmem_base + lane_addr + s * 128 + c0, v + c0);
+            for (int c0 = 0; c0 < HK; c0 += 32) tmem_ld32(tmem_base + lane_addr + s * 128 + half * HK + c0, v + c0);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&s_empty[s]));
             // only tiles that touch the diagonal or the window's edge need the mask
-            const bool need_mask = key_base + BKV - 1 > p_first || key_base < lo ||
-                                   (p.window > 0 && key_base <= p_last - p.window);
+            const bool need_mask = tile_base + BKV - 1 > p_first || tile_base < lo ||
+                                   (p.window > 0 && tile_base <= p_last - p.window);
             if (need_mask) {
 #pragma unroll
-                for (int i = 0; i < BKV; ++i) {
+                for (int i = 0; i < HK; ++i) {
                     const int key = key_base + i;
                     const bool ok = key <= pos && (p.window <= 0 || key > pos - p.window);
                     if (!ok) v[i] = 0xff800000u;            // -inf
@@ -341,15 +352,20 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < BKV; i += 4) {
+            for (int i = 0; i < HK; i += 4) {
                 mx0 = fmaxf(mx0, __uint_as_float(v[i]));
                 mx1 = fmaxf(mx1, __uint_as_float(v[i + 1]));
                 mx2 = fmaxf(mx2, __uint_as_float(v[i + 2]));
                 mx3 = fmaxf(mx3, __uint_as_float(v[i + 3]));
             }
-            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;   // scale > 0
-            // keep the maximum in use unless the row moved far above it (decided per warp,
-            // because the tensor-memory accesses below are warp-wide)
+            // the row's maximum over both halves
+            float* xch = sm_x + (j & 1) * 2 * BQ;
+            const float mine = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            xch[half * BQ + r] = mine;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            const float mx = fmaxf(mine, xch[(half ^ 1) * BQ + r]) * p.scale_log2;   // scale > 0
+            // keep the maximum in use unless the row moved far above it (decided per warp, because
+            // the tensor-memory accesses below are warp-wide; both warps of a row decide alike)
             const bool far = mx > m_ref + RESCALE_THRESHOLD;
             const bool warp_far = __any_sync(0xffffffffu, far);
             float factor = 1.f;
@@ -361,14 +377,14 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const float nbase = (m_ref == -INFINITY) ? 0.f : -m_ref;
             float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
-            for (int i = 0; i < BKV; i += 4) {
+            for (int i = 0; i < HK; i += 4) {
                 const float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), p.scale_log2, nbase));
                 const float p1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, nbase));
                 const float p2 = fast_exp2(fmaf(__uint_as_float(v[i + 2]), p.scale_log2, nbase));
                 const float p3 = fast_exp2(fmaf(__uint_as_float(v[i + 3]), p.scale_log2, nbase));
                 s0 += p0; s1 += p1; s2 += p2; s3 += p3;
                 __nv_bfloat162 b0 = __floats2bfloat162_rn(p0, p1), b1 = __floats2bfloat162_rn(p2, p3);
-                v[i >> 1] = *(uint32_t*)&b0;                 // v[0..63] now hold the packed pairs
+                v[i >> 1] = *(uint32_t*)&b0;                 // v[0..31] now hold the packed pairs
                 v[(i >> 1) + 1] = *(uint32_t*)&b1;
             }
             l = l * factor + ((s0 + s1) + (s2 + s3));
@@ -376,8 +392,9 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (j > 0 && !mbar_wait(smem_u32(pv_done), (j - 1) & 1, abort_flag)) goto done;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (warp_far && j > 0) {
+                // this thread's half of the row of O
 #pragma unroll 1
-                for (int c0 = 0; c0 < D; c0 += 32) {
+                for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
                     uint32_t o[32];
                     tmem_ld32(tmem_o + lane_addr + c0, o);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -387,13 +404,15 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
-            // into shared memory in the swizzled K-major layout: 16 chunks of 16 bytes (8 keys)
-            // per row, chunk index xor-ed with row % 8, the second 64 keys one half tile on
+            // into shared memory in the swizzled K-major layout: this half's 64 keys are one half
+            // tile, 8 chunks of 16 bytes (8 keys) per row, chunk index xor-ed with row % 8
+            {
+                uint8_t* prow = sm_p + half * HALF_BYTES + r * 128;
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                uint8_t* prow = sm_p + (c >> 3) * HALF_BYTES + r * 128;
-                const int chunk = (c & 7) ^ (r & 7);
-                *(uint4*)(prow + chunk * 16) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+                for (int c = 0; c < 8; ++c) {
+                    const int chunk = c ^ (r & 7);
+                    *(uint4*)(prow + chunk * 16) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+                }
             }
             // P and O are ready for the second product
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -401,14 +420,20 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(p_full));
         }
-        // ---- epilogue: O / l ----
+        // ---- epilogue: O / l, this thread's half of the columns; l is the sum of both halves ----
         if (!mbar_wait(smem_u32(pv_done), (n_tiles - 1) & 1, abort_flag)) goto done;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        {
+            float* xch = sm_x + (n_tiles & 1) * 2 * BQ;
+            xch[half * BQ + r] = l;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            l += xch[(half ^ 1) * BQ + r];
+        }
         const float inv = l > 0.f ? 1.f / l : 0.f;
         const bool store = r_begin + r < r_end;
         __nv_bfloat16* orow = p.out + ((long long)(row0 + r_begin + r) * p.nq + h) * D;
 #pragma unroll 1
-        for (int c0 = 0; c0 < D; c0 += 32) {
+        for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
             uint32_t v[32];
             tmem_ld32(tmem_o + lane_addr + c0, v);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -492,7 +517,7 @@ CRANE_API int crane_prefill_attention_tc(const void* q, void* out, const void* k
     p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.kv_len = kv_len; p.block_table = block_table;
     p.max_blocks = max_blocks; p.num_pages = num_pages; p.page_size = page_size; p.n_entries = n_entries;
     p.nq = nq; p.nkv = nkv; p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.err = err;
-    constexpr size_t smem = 6 * TILE_BYTES + 16 * 8 + 16 + 1024;
+    constexpr size_t smem = 6 * TILE_BYTES + 16 * 8 + 2 * 2 * BQ * 4 + 16 + 1024;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(prefill_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
