@@ -31,7 +31,8 @@ namespace {
 constexpr int D = 128;            // head size
 constexpr int BQ = 128;           // query rows per CTA = MMA M
 constexpr int BKV = 128;          // keys per tile
-constexpr int NUM_THREADS = 320;      // warp 0: TMA, warp 1: MMA, warps 2..9: softmax, two threads per query row
+constexpr int NUM_THREADS = 352;      // warp 0: TMA, warp 1: first product, warps 2..9: softmax (two threads
+                                      // per query row), warp 10: second product
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 constexpr uint32_t HALF_BYTES = 128 * 128;          // 128 rows x 64 bf16: one swizzled half tile
 constexpr uint32_t TILE_BYTES = 2 * HALF_BYTES;     // 128 x 128 bf16
@@ -105,6 +106,17 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, 
         "}\n" ::"r"(tmem_d), "l"(da), "l"(db), "r"(id), "r"(acc)
         : "memory");
 }
+// the same with the A operand in tensor memory (16-bit elements, two per column)
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t id, uint32_t acc) {
+    const uint32_t z = 0;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n"
+        "}\n" ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(id), "r"(acc), "r"(z)
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                  : "memory");
@@ -158,8 +170,7 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint8_t* sm_q = smem;                          // [2 halves][128][128 B]
     uint8_t* sm_k = sm_q + TILE_BYTES;             // [2 stages][2 halves][128][128 B]
     uint8_t* sm_v = sm_k + 2 * TILE_BYTES;         // [2 stages][2 halves (of d)][128 keys][128 B]
-    uint8_t* sm_p = sm_v + 2 * TILE_BYTES;         // [2 halves (of keys)][128 rows][128 B]
-    uint64_t* bars = (uint64_t*)(sm_p + TILE_BYTES);
+    uint64_t* bars = (uint64_t*)(sm_v + 2 * TILE_BYTES);
     uint64_t* q_full = bars;            // Q has landed
     uint64_t* k_full = bars + 1;        // [2]
     uint64_t* v_full = bars + 3;        // [2]
@@ -167,11 +178,11 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint64_t* v_empty = bars + 7;       // [2] the O product that read the stage is done
     uint64_t* s_full = bars + 9;        // [2] S is complete in tensor memory
     uint64_t* s_empty = bars + 11;      // [2] the softmax threads have read S out
-    uint64_t* p_full = bars + 13;       // P is in shared memory (and O rescaled if need be)
-    uint64_t* pv_done = bars + 14;      // the O product of a tile is done
-    uint32_t* tmem_slot = (uint32_t*)(bars + 15);
+    uint64_t* p_full = bars + 13;       // [2] P is in its tensor-memory buffer (and O rescaled if need be)
+    uint64_t* pv_done = bars + 15;      // [2] the O product that read the P buffer is done
+    uint32_t* tmem_slot = (uint32_t*)(bars + 17);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-    float* sm_x = (float*)(bars + 16);             // [2 tiles in turn][2 halves][128 rows]: what the two
+    float* sm_x = (float*)(bars + 18);             // [2 tiles in turn][2 halves][128 rows]: what the two
                                                    // threads of a row tell each other (maximum, sum)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -208,8 +219,10 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_init(smem_u32(&s_full[s]), 1);
             mbar_init(smem_u32(&s_empty[s]), 8);
         }
-        mbar_init(smem_u32(p_full), 8);
-        mbar_init(smem_u32(pv_done), 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&p_full[b]), 8);
+            mbar_init(smem_u32(&pv_done[b]), 1);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -225,7 +238,10 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_o = tmem_base + 256;          // S buffers at columns 0 and 128, O at 256
+    // S buffers at columns 0 and 128, O at 256, two P buffers (bf16 pairs: 64 columns each) at 384 and 448.
+    // P stays in tensor memory and is the A operand of the second product from there: it never goes
+    // through shared memory, whose bandwidth the products' operand reads and the copies already fill.
+    const uint32_t tmem_o = tmem_base + 256, tmem_p = tmem_base + 384;
     pdl_launch_dependents();
 
     if (warp == 0 && n_tiles > 0) {
@@ -273,44 +289,48 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
         }
     } else if (warp == 1 && lane == 0 && n_tiles > 0) {
-        // ---------------- MMA ----------------
-        const uint32_t id_s = idesc(false), id_o = idesc(true);
+        // ---------------- first product: S_j = Q K_j^T into S buffer j & 1 ----------------
+        // The two products are issued by a thread each: one thread's waits and issue slots for
+        // both were the longest chain of a tile; tcgen05.commit counts the issuing thread's MMAs.
+        const uint32_t id_s = idesc(false);
+        // Operand descriptors are made once; a step along the tile only adds to the address field
+        // (16-byte units, the whole of shared memory fits its 14 bits).
+        const uint64_t dq = desc_kmajor(smem_u32(sm_q)), dk = desc_kmajor(smem_u32(sm_k));
         if (!mbar_wait(smem_u32(q_full), 0, abort_flag)) goto done;
-        // S_j = Q K_j^T into S buffer j & 1
-        auto issue_s = [&](int j) -> bool {
+        for (int j = 0; j < n_tiles; ++j) {
             const int s = j & 1;
-            if (!mbar_wait(smem_u32(&k_full[s]), (j >> 1) & 1, abort_flag)) return false;
-            if (!mbar_wait(smem_u32(&s_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag)) return false;
+            if (!mbar_wait(smem_u32(&k_full[s]), (j >> 1) & 1, abort_flag)) goto done;
+            if (!mbar_wait(smem_u32(&s_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag)) goto done;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t qa = smem_u32(sm_q), kb = smem_u32(sm_k + s * TILE_BYTES);
+            const uint64_t dks = dk + (uint64_t)(s * (TILE_BYTES >> 4));
+            const uint32_t ts = tmem_base + s * 128;
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
-                const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-                umma(tmem_base + s * 128, desc_kmajor(qa + off), desc_kmajor(kb + off), id_s, kk > 0);
+                const uint64_t off = (uint64_t)(((kk >> 2) * HALF_BYTES + (kk & 3) * 32) >> 4);
+                umma(ts, dq + off, dks + off, id_s, kk > 0);
             }
             umma_commit(smem_u32(&s_full[s]));
             umma_commit(smem_u32(&k_empty[s]));
-            return true;
-        };
-        if (!issue_s(0)) goto done;
+        }
+    } else if (warp == 10 && lane == 0 && n_tiles > 0) {
+        // ---------------- second product: O += P_j V_j, P from tensor memory ----------------
+        const uint32_t id_o = idesc(true);
+        const uint64_t dv = desc_mnmajor(smem_u32(sm_v));
         for (int j = 0; j < n_tiles; ++j) {
-            if (j + 1 < n_tiles && !issue_s(j + 1)) goto done;
             const int s = j & 1;
             if (!mbar_wait(smem_u32(&v_full[s]), (j >> 1) & 1, abort_flag)) goto done;
-            if (!mbar_wait(smem_u32(p_full), j & 1, abort_flag)) goto done;
+            if (!mbar_wait(smem_u32(&p_full[s]), (j >> 1) & 1, abort_flag)) goto done;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t pa = smem_u32(sm_p), vb = smem_u32(sm_v + s * TILE_BYTES);
+            const uint64_t dvs = dv + (uint64_t)(s * (TILE_BYTES >> 4));
 #pragma unroll
             for (int kk = 0; kk < BKV / 16; ++kk) {
-                // P: 16 keys further along K = 32 bytes within a row, the second 64 keys one half on;
-                // V: 16 keys further = 16 rows = 2048 bytes
-                const uint32_t poff = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-                umma(tmem_o, desc_kmajor(pa + poff), desc_mnmajor(vb + kk * 2048), id_o, (j > 0 || kk > 0));
+                // P: 16 keys further along K = 8 columns; V: 16 keys further = 16 rows = 2048 bytes
+                umma_ts(tmem_o, tmem_p + s * 64 + kk * 8, dvs + (uint64_t)(kk * (2048 >> 4)), id_o, (j > 0 || kk > 0));
             }
-            umma_commit(smem_u32(pv_done));
+            umma_commit(smem_u32(&pv_done[s]));
             umma_commit(smem_u32(&v_empty[s]));
         }
-    } else if (warp >= 2 && n_tiles > 0) {
+    } else if (warp >= 2 && warp < 10 && n_tiles > 0) {
         // ---------------- softmax, correction, epilogue: two threads per query row ----------------
         // Warps w and w + 4 own the same 32 rows (a warp reaches the lanes of tensor memory given by
         // its index modulo 4); the first takes keys 0..63 of every tile and columns 0..63 of O, the
@@ -388,10 +408,14 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 v[(i >> 1) + 1] = *(uint32_t*)&b1;
             }
             l = l * factor + ((s0 + s1) + (s2 + s3));
-            // the O product of the tile before must be done before P is overwritten or O rescaled
-            if (j > 0 && !mbar_wait(smem_u32(pv_done), (j - 1) & 1, abort_flag)) goto done;
+            // P has two buffers: this tile's P may be written while the O product of the tile before
+            // still reads the other one; only the product two tiles back must be done.  O can be
+            // rescaled only when the product of the tile before is done, which is waited for just then.
+            if (j > 1 && !mbar_wait(smem_u32(&pv_done[s]), ((j >> 1) & 1) ^ 1, abort_flag)) goto done;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (warp_far && j > 0) {
+                if (!mbar_wait(smem_u32(&pv_done[s ^ 1]), ((j - 1) >> 1) & 1, abort_flag)) goto done;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 // this thread's half of the row of O
 #pragma unroll 1
                 for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
@@ -404,24 +428,16 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
-            // into shared memory in the swizzled K-major layout: this half's 64 keys are one half
-            // tile, 8 chunks of 16 bytes (8 keys) per row, chunk index xor-ed with row % 8
-            {
-                uint8_t* prow = sm_p + half * HALF_BYTES + r * 128;
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const int chunk = c ^ (r & 7);
-                    *(uint4*)(prow + chunk * 16) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
-                }
-            }
+            // this half's 64 keys, two to a column, into the tile's P buffer in tensor memory
+            tmem_st32(tmem_p + lane_addr + s * 64 + half * 32, v);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             // P and O are ready for the second product
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(p_full));
+            if (lane == 0) mbar_arrive(smem_u32(&p_full[s]));
         }
         // ---- epilogue: O / l, this thread's half of the columns; l is the sum of both halves ----
-        if (!mbar_wait(smem_u32(pv_done), (n_tiles - 1) & 1, abort_flag)) goto done;
+        if (!mbar_wait(smem_u32(&pv_done[(n_tiles - 1) & 1]), ((n_tiles - 1) >> 1) & 1, abort_flag)) goto done;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         {
             float* xch = sm_x + (n_tiles & 1) * 2 * BQ;
@@ -517,7 +533,7 @@ CRANE_API int crane_prefill_attention_tc(const void* q, void* out, const void* k
     p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.kv_len = kv_len; p.block_table = block_table;
     p.max_blocks = max_blocks; p.num_pages = num_pages; p.page_size = page_size; p.n_entries = n_entries;
     p.nq = nq; p.nkv = nkv; p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.err = err;
-    constexpr size_t smem = 6 * TILE_BYTES + 16 * 8 + 2 * 2 * BQ * 4 + 16 + 1024;
+    constexpr size_t smem = 5 * TILE_BYTES + 18 * 8 + 2 * 2 * BQ * 4 + 16 + 1024;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(prefill_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
