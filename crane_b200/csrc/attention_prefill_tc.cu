@@ -2,16 +2,28 @@
 // (head size 128, bf16, pages of 16..128 tokens).  One CTA owns 128 query rows
 // of one request and one query head and walks over the keys in tiles of 128:
 //
-//   warp 0 (one thread)   TMA: the Q tile once, then K and V tiles from the
+//   warp 0 (all lanes)    TMA: the Q tile once, then K and V tiles from the
 //                         paged pool, page by page through the block table,
 //                         into 128-byte-swizzled shared memory (two stages);
+//                         every lane looks one page up and issues one copy;
 //   warp 1 (one thread)   tcgen05.mma:  S = Q K^T  (float, tensor memory, two
-//                         buffers), then  O += P V  (float, tensor memory);
-//   warps 2..5            one thread per query row: read S with tcgen05.ld,
-//                         scale, mask (causal + window), running max and sum,
-//                         P = exp2(S - max) as bf16 into shared memory for the
-//                         second product; rescale O in tensor memory when the
-//                         running max has moved far; at the end O / sum -> out.
+//                         buffers);
+//   last warp (one thread) tcgen05.mma:  O += P V  (float, tensor memory), P
+//                         read from tensor memory as the A operand;
+//   the warps between     two threads per query row, each with half of the
+//                         tile's keys and half of O's columns: read S with
+//                         tcgen05.ld, scale, mask (causal + window), running
+//                         max (agreed through shared memory) and sum,
+//                         P = exp2(S - max) as bf16 pairs into one of two P
+//                         buffers in tensor memory; rescale O in tensor memory
+//                         when the running max has moved far; at the end
+//                         O / sum -> out.
+//
+// How it got this shape (per-role clock stamps of one CTA showed what a tile
+// waits for; leaving work out one piece at a time had shown nothing, because
+// several chains were about equally long): one producer lane issuing all
+// copies took longer per tile than anything else; then one thread issuing
+// both products; the softmax arithmetic was never the longest chain.
 //
 // A row keeps the maximum it uses for its exponentials until a later score
 // exceeds it by more than 2^8; until then P simply carries the factor (at most
@@ -31,8 +43,10 @@ namespace {
 constexpr int D = 128;            // head size
 constexpr int BQ = 128;           // query rows per CTA = MMA M
 constexpr int BKV = 128;          // keys per tile
-constexpr int NUM_THREADS = 352;      // warp 0: TMA, warp 1: first product, warps 2..9: softmax (two threads
-                                      // per query row), warp 10: second product
+constexpr int SPLIT = 2;              // softmax threads per query row (4 measured no faster)
+constexpr int SM_WARPS = 4 * SPLIT;   // softmax warps
+constexpr int PV_WARP = 2 + SM_WARPS; // warp 0: TMA, warp 1: first product, then the softmax warps, then the second product
+constexpr int NUM_THREADS = 32 * (PV_WARP + 1);
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 constexpr uint32_t HALF_BYTES = 128 * 128;          // 128 rows x 64 bf16: one swizzled half tile
 constexpr uint32_t TILE_BYTES = 2 * HALF_BYTES;     // 128 x 128 bf16
@@ -146,6 +160,21 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
           "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+          "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+          "r"(r[15])
+        : "memory");
+}
+template <int N>
+__device__ __forceinline__ void tmem_st_n(uint32_t taddr, const uint32_t* r) {
+    static_assert(N == 16 || N == 32, "16 or 32 columns");
+    if (N == 32) tmem_st32(taddr, r);
+    else tmem_st16(taddr, r);
+}
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -182,8 +211,8 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint64_t* pv_done = bars + 15;      // [2] the O product that read the P buffer is done
     uint32_t* tmem_slot = (uint32_t*)(bars + 17);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-    float* sm_x = (float*)(bars + 18);             // [2 tiles in turn][2 halves][128 rows]: what the two
-                                                   // threads of a row tell each other (maximum, sum)
+    float* sm_x = (float*)(bars + 18);             // [2 tiles in turn][SPLIT][128 rows]: what the threads
+                                                   // of a row tell each other (maximum, sum)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -217,10 +246,10 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_init(smem_u32(&k_empty[s]), 1);
             mbar_init(smem_u32(&v_empty[s]), 1);
             mbar_init(smem_u32(&s_full[s]), 1);
-            mbar_init(smem_u32(&s_empty[s]), 8);
+            mbar_init(smem_u32(&s_empty[s]), SM_WARPS);
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(smem_u32(&p_full[b]), 8);
+            mbar_init(smem_u32(&p_full[b]), SM_WARPS);
             mbar_init(smem_u32(&pv_done[b]), 1);
         }
         *abort_flag = 0;
@@ -312,7 +341,7 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             umma_commit(smem_u32(&s_full[s]));
             umma_commit(smem_u32(&k_empty[s]));
         }
-    } else if (warp == 10 && lane == 0 && n_tiles > 0) {
+    } else if (warp == PV_WARP && lane == 0 && n_tiles > 0) {
         // ---------------- second product: O += P_j V_j, P from tensor memory ----------------
         const uint32_t id_o = idesc(true);
         const uint64_t dv = desc_mnmajor(smem_u32(sm_v));
@@ -330,20 +359,20 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             umma_commit(smem_u32(&pv_done[s]));
             umma_commit(smem_u32(&v_empty[s]));
         }
-    } else if (warp >= 2 && warp < 10 && n_tiles > 0) {
-        // ---------------- softmax, correction, epilogue: two threads per query row ----------------
-        // Warps w and w + 4 own the same 32 rows (a warp reaches the lanes of tensor memory given by
-        // its index modulo 4); the first takes keys 0..63 of every tile and columns 0..63 of O, the
-        // second the other halves.  They agree on the row's maximum through shared memory once per
-        // tile and keep a partial sum each.  Eight softmax warps give every scheduler two warps to
-        // alternate between and halve the chain of exponentials and conversions per tile.
-        constexpr int HK = BKV / 2;
+    } else if (warp >= 2 && warp < PV_WARP && n_tiles > 0) {
+        // ---------------- softmax, correction, epilogue: SPLIT threads per query row ----------------
+        // Warps w, w + 4, w + 8, ... own the same 32 rows (a warp reaches the lanes of tensor memory
+        // given by its index modulo 4); each takes its share of every tile's keys and of O's columns.
+        // They agree on the row's maximum through shared memory once per tile and keep a partial sum
+        // each.  That gives every scheduler several softmax warps to alternate between and shortens
+        // the chain of exponentials and conversions per tile.
+        constexpr int HK = BKV / SPLIT;
         const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;
+        const int half = (warp - 2) >> 2;                   // which share: 0 .. SPLIT - 1
         const int r = quarter * 32 + lane;                  // row of the tile = lane of tensor memory
         const int pos = pos0 + r_begin + r;                 // this row's position
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        const int pair_bar = 1 + quarter;                   // named barrier of the two warps of these rows
+        const int pair_bar = 1 + quarter;                   // named barrier of the warps of these rows
         float m_ref = -INFINITY, l = 0.f;                   // maximum in use, running sum of this half
         for (int j = 0; j < n_tiles; ++j) {
             const int s = j & 1;
@@ -355,6 +384,7 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             uint32_t v[HK];
 #pragma unroll
             for (int c0 = 0; c0 < HK; c0 += 32) tmem_ld32(tmem_base + lane_addr + s * 128 + half * HK + c0, v + c0);
+            static_assert(HK % 32 == 0, "a softmax thread reads its scores 32 columns at a time");
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -379,11 +409,13 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 mx3 = fmaxf(mx3, __uint_as_float(v[i + 3]));
             }
             // the row's maximum over both halves
-            float* xch = sm_x + (j & 1) * 2 * BQ;
-            const float mine = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            float* xch = sm_x + (j & 1) * SPLIT * BQ;
+            float mine = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
             xch[half * BQ + r] = mine;
-            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-            const float mx = fmaxf(mine, xch[(half ^ 1) * BQ + r]) * p.scale_log2;   // scale > 0
+            asm volatile("bar.sync %0, %1;" ::"r"(pair_bar), "n"(32 * SPLIT) : "memory");
+#pragma unroll
+            for (int o = 0; o < SPLIT; ++o) mine = fmaxf(mine, xch[o * BQ + r]);
+            const float mx = mine * p.scale_log2;           // scale > 0
             // keep the maximum in use unless the row moved far above it (decided per warp, because
             // the tensor-memory accesses below are warp-wide; both warps of a row decide alike)
             const bool far = mx > m_ref + RESCALE_THRESHOLD;
@@ -404,7 +436,7 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 const float p3 = fast_exp2(fmaf(__uint_as_float(v[i + 3]), p.scale_log2, nbase));
                 s0 += p0; s1 += p1; s2 += p2; s3 += p3;
                 __nv_bfloat162 b0 = __floats2bfloat162_rn(p0, p1), b1 = __floats2bfloat162_rn(p2, p3);
-                v[i >> 1] = *(uint32_t*)&b0;                 // v[0..31] now hold the packed pairs
+                v[i >> 1] = *(uint32_t*)&b0;                 // the first half of v now holds the packed pairs
                 v[(i >> 1) + 1] = *(uint32_t*)&b1;
             }
             l = l * factor + ((s0 + s1) + (s2 + s3));
@@ -418,7 +450,7 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 // this thread's half of the row of O
 #pragma unroll 1
-                for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
+                for (int c0 = half * (D / SPLIT); c0 < (half + 1) * (D / SPLIT); c0 += 32) {
                     uint32_t o[32];
                     tmem_ld32(tmem_o + lane_addr + c0, o);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -429,7 +461,7 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
             // this half's 64 keys, two to a column, into the tile's P buffer in tensor memory
-            tmem_st32(tmem_p + lane_addr + s * 64 + half * 32, v);
+            tmem_st_n<HK / 2>(tmem_p + lane_addr + s * 64 + half * (HK / 2), v);
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             // P and O are ready for the second product
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -440,16 +472,18 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (!mbar_wait(smem_u32(&pv_done[(n_tiles - 1) & 1]), ((n_tiles - 1) >> 1) & 1, abort_flag)) goto done;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         {
-            float* xch = sm_x + (n_tiles & 1) * 2 * BQ;
+            float* xch = sm_x + (n_tiles & 1) * SPLIT * BQ;
             xch[half * BQ + r] = l;
-            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-            l += xch[(half ^ 1) * BQ + r];
+            asm volatile("bar.sync %0, %1;" ::"r"(pair_bar), "n"(32 * SPLIT) : "memory");
+            l = 0.f;
+#pragma unroll
+            for (int o = 0; o < SPLIT; ++o) l += xch[o * BQ + r];            // the same order for every thread
         }
         const float inv = l > 0.f ? 1.f / l : 0.f;
         const bool store = r_begin + r < r_end;
         __nv_bfloat16* orow = p.out + ((long long)(row0 + r_begin + r) * p.nq + h) * D;
 #pragma unroll 1
-        for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
+        for (int c0 = half * (D / SPLIT); c0 < (half + 1) * (D / SPLIT); c0 += 32) {
             uint32_t v[32];
             tmem_ld32(tmem_o + lane_addr + c0, v);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -533,7 +567,7 @@ CRANE_API int crane_prefill_attention_tc(const void* q, void* out, const void* k
     p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.kv_len = kv_len; p.block_table = block_table;
     p.max_blocks = max_blocks; p.num_pages = num_pages; p.page_size = page_size; p.n_entries = n_entries;
     p.nq = nq; p.nkv = nkv; p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.err = err;
-    constexpr size_t smem = 5 * TILE_BYTES + 18 * 8 + 2 * 2 * BQ * 4 + 16 + 1024;
+    constexpr size_t smem = 5 * TILE_BYTES + 18 * 8 + 2 * SPLIT * BQ * 4 + 16 + 1024;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(prefill_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
