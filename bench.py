@@ -222,7 +222,7 @@ def time_prefill(model, tokens, vocab, reps=3, mark=False):
     from crane_b200.engine import StepEntry
     runner = model.runner
     prompt = [(13 * i + 1) % vocab for i in range(tokens)]
-    best = None
+    times = []
     for r in range(reps + 1):
         rid = 5000 + r
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -236,9 +236,9 @@ def time_prefill(model, tokens, vocab, reps=3, mark=False):
             torch.cuda.profiler.stop()
         runner.end(rid)
         if r > 0:                                 # the first run warms up
-            ms = start.elapsed_time(stop)
-            best = ms if best is None else min(best, ms)
-    return best
+            times.append(start.elapsed_time(stop))
+    times.sort()
+    return times[len(times) // 2]                 # the median
 
 
 def reference_arm():
@@ -344,17 +344,19 @@ def main():
                      "peaks": pk["source"]},
     }
     if not args.no_points:
+        # the prefill first: right after the batch-64 point the power cap holds the SM clock down
+        # for a moment, which says nothing about the prefill
+        tokens = 2048
+        pms = time_prefill(model, tokens, vocab, reps=5)
+        flops = prefill_flops(cfg, layers, tokens)
+        out["prefill"] = {"value": round(tokens * 1000.0 / pms, 1), "tokens": tokens,
+                          "ms": round(pms, 3),
+                          "frac": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
         points = {}
         for b in (1, 64):
             pms, _ = decode_point(b)
             points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
         out["points"] = points
-        tokens = 2048
-        pms = time_prefill(model, tokens, vocab)
-        flops = prefill_flops(cfg, layers, tokens)
-        out["prefill"] = {"value": round(tokens * 1000.0 / pms, 1), "tokens": tokens,
-                          "ms": round(pms, 3),
-                          "frac": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
     print(json.dumps(out))
     return 0
 
