@@ -348,7 +348,9 @@ __device__ __forceinline__ void store_chunk32(const GemmParams& p, const uint32_
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const float g = __uint_as_float(r[j]), u = __uint_as_float(r[16 + j]);
-            v[j] = g / (1.f + expf(-g)) * u;
+            // the result is rounded to bf16: the approximate exp and division (each good to a
+            // few units in the last place of a float) are far inside that, and a third as long
+            v[j] = __fdividef(g, 1.f + __expf(-g)) * u;
         }
 #pragma unroll
         for (int j = 0; j < 16; j += 8) {
