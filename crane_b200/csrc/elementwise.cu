@@ -195,6 +195,33 @@ __global__ void __launch_bounds__(PER <= 2 ? 512 : 1024) add_rmsnorm2_kernel(flo
     }
 }
 
+// 8 neighbouring elements at once (16-byte aligned): 32 bytes of float or 16 bytes of bf16
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+    const float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 q = *(const uint4*)p;
+    const __nv_bfloat162* h = (const __nv_bfloat162*)&q;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        v[2 * j] = f.x;
+        v[2 * j + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+    *(float4*)p = make_float4(v[0], v[1], v[2], v[3]);
+    *(float4*)(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 q;
+    __nv_bfloat162* h = (__nv_bfloat162*)&q;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+    *(uint4*)p = q;
+}
+
 // Many rows: a warp per row and no block-wide barrier.  A lane owns CH pieces of 8
 // neighbouring elements (piece c at column (c * 32 + lane) * 8), all of whose loads are in
 // flight together; the sum of squares goes around the warp by shuffles.  For a delta that is
@@ -222,12 +249,10 @@ __global__ void __launch_bounds__(256) add_rmsnorm_warp_kernel(float* __restrict
 #pragma unroll
         for (int c = 0; c < CH; ++c) {
             const int col = (c * 32 + lane) * 8;
+            float d[8];
+            load8(dr + col, d);
 #pragma unroll
-            for (int j = 0; j < 8; j += 2) {
-                const float2 d = ld2(dr + col + j);
-                v[c][j] += d.x;
-                v[c][j + 1] += d.y;
-            }
+            for (int j = 0; j < 8; ++j) v[c][j] += d[j];
         }
 #pragma unroll
         for (int c = 0; c < CH; ++c) {
@@ -246,11 +271,11 @@ __global__ void __launch_bounds__(256) add_rmsnorm_warp_kernel(float* __restrict
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
         const int col = (c * 32 + lane) * 8;
-        const float4 wa = *(const float4*)(w + col), wb = *(const float4*)(w + col + 4);
-        st2(o + col, v[c][0] * rstd * wa.x, v[c][1] * rstd * wa.y);
-        st2(o + col + 2, v[c][2] * rstd * wa.z, v[c][3] * rstd * wa.w);
-        st2(o + col + 4, v[c][4] * rstd * wb.x, v[c][5] * rstd * wb.y);
-        st2(o + col + 6, v[c][6] * rstd * wb.z, v[c][7] * rstd * wb.w);
+        float wv[8], y[8];
+        load8(w + col, wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) y[j] = v[c][j] * rstd * wv[j];
+        store8(o + col, y);
     }
 }
 
