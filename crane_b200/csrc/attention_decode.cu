@@ -52,7 +52,6 @@ struct FusedArgs {
     float eps;
     __nv_bfloat16* k_pool_w;        // the pools again, writable
     __nv_bfloat16* v_pool_w;
-    int* counters;                  // [entries * kv heads], zero between launches: slices done per group
 };
 
 __device__ __forceinline__ float2 raw2(const FusedArgs& a, long long idx) {
@@ -442,60 +441,6 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
             const long long pi = ((long long)e * nq + h) * n_splits + split;
             part_o[pi * D + c] = O;
             if (c == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
-        }
-    }
-    if (FUSED && n_splits > 1 && fa.counters != nullptr) {
-        // the CTA that finishes its group's last slice merges all of them, in slice order
-        __shared__ int ticket;
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) ticket = atomicAdd(fa.counters + e * nkv + g, 1);
-        __syncthreads();
-        if (ticket == n_splits - 1) {
-            __threadfence();
-            // weights of the slices, per head: exp2(m_s - max m) / sum, in shared memory
-            float* wgt = (float*)smem;                           // [n_rep][n_splits], tiles are done with
-            const int pairs = n_rep * n_splits;
-            for (int i = threadIdx.x; i < pairs; i += WARPS * 32) {
-                const int r = i / n_splits, sp = i % n_splits;
-                const long long pi = ((long long)e * nq + g * n_rep + r) * n_splits + sp;
-                wgt[i] = __ldcg(part_ml + pi * 2);               // m for now
-                wgt[pairs + i] = __ldcg(part_ml + pi * 2 + 1);   // l
-            }
-            __syncthreads();
-            if (threadIdx.x < n_rep) {
-                const int r = threadIdx.x;
-                float M = -INFINITY;
-                for (int sp = 0; sp < n_splits; ++sp) M = fmaxf(M, wgt[r * n_splits + sp]);
-                const float mb = (M == -INFINITY) ? 0.f : M;
-                float L = 0.f;
-                for (int sp = 0; sp < n_splits; ++sp) {
-                    const float f = exp2f(wgt[r * n_splits + sp] - mb);
-                    L += f * wgt[pairs + r * n_splits + sp];
-                    wgt[r * n_splits + sp] = f;
-                }
-                const float inv = L > 0.f ? 1.f / L : 0.f;
-                for (int sp = 0; sp < n_splits; ++sp) wgt[r * n_splits + sp] *= inv;
-            }
-            __syncthreads();
-            for (int idx = threadIdx.x; idx < n_rep * D; idx += WARPS * 32) {
-                const int r = idx / D, c = idx % D;
-                const int h = g * n_rep + r;
-                const float* po = part_o + ((long long)e * nq + h) * n_splits * D + c;
-                float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
-                int sp = 0;
-                for (; sp + 4 <= n_splits; sp += 4) {            // four loads in flight at a time
-                    const float v0 = __ldcg(po + (long long)sp * D), v1 = __ldcg(po + (long long)(sp + 1) * D);
-                    const float v2 = __ldcg(po + (long long)(sp + 2) * D), v3 = __ldcg(po + (long long)(sp + 3) * D);
-                    acc0 += wgt[r * n_splits + sp] * v0;
-                    acc1 += wgt[r * n_splits + sp + 1] * v1;
-                    acc2 += wgt[r * n_splits + sp + 2] * v2;
-                    acc3 += wgt[r * n_splits + sp + 3] * v3;
-                }
-                for (; sp < n_splits; ++sp) acc0 += wgt[r * n_splits + sp] * __ldcg(po + (long long)sp * D);
-                out[((long long)t * nq + h) * D + c] = __float2bfloat16_rn((acc0 + acc1) + (acc2 + acc3));
-            }
-            if (threadIdx.x == 0) fa.counters[e * nkv + g] = 0;      // ready for the next launch
         }
     }
 }
@@ -1056,8 +1001,7 @@ int launch_decode(const void* q, void* out, float* part_o, float* part_ml, const
         configured = true;
     }
     dim3 grid(n_splits, nkv, n_entries);
-    const bool merged_in_kernel = FUSED && fa.counters != nullptr;
-    if (D == D128 && !merged_in_kernel && page_size % TILE == 0 && tma_path_enabled()) {
+    if (D == D128 && page_size % TILE == 0 && tma_path_enabled()) {
         const int rc = launch_decode_tma<FUSED>(q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len,
                                                 block_table, max_blocks, num_pages, page_size, nq, nkv,
                                                 window, scale, n_splits, err, fa, grid, st);
@@ -1072,8 +1016,7 @@ int launch_decode(const void* q, void* out, float* part_o, float* part_ml, const
                           (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)k_pool,
                           (const __nv_bfloat16*)v_pool, cu_q, kv_len, block_table, max_blocks, num_pages,
                           page_size, nq, nkv, window, scale * 1.4426950408889634f, n_splits, err, fa);
-    const bool merged_inside = FUSED && fa.counters != nullptr;
-    if (rc == 0 && n_splits > 1 && !merged_inside)
+    if (rc == 0 && n_splits > 1)
         rc = crane_launch(decode_merge_kernel, dim3(n_entries, nq), dim3(D >= 128 ? 128 : 64), 0, st,
                           (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, cu_q, nq, D,
                           n_splits);
@@ -1115,14 +1058,13 @@ CRANE_API int crane_paged_decode_attention(const void* q, void* out, float* part
 // The fused form: q, k and v of the step's tokens come raw from the product
 // (`qkv` whole, or `qkv_parts` as n_parts float partial sums), one row of
 // [q | k | v] (q alone when has_kv == 0) per token.  The kernel encodes and
-// normalises them, writes the new key and value into their pages, attends, and
-// merges the slices itself if `counters` is given (entries * kv heads ints, zero
-// before the first launch; the kernel leaves them zero), else in a second kernel.  Head sizes must be multiples of 4.
+// normalises them, writes the new key and value into their pages and attends; a
+// second kernel merges the slices.  Head sizes must be multiples of 4.
 CRANE_API int crane_paged_decode_attention_fused(
     const void* qkv, const float* qkv_parts, int n_parts, long long part_stride, int qkv_stride,
     int has_kv, int rotary, const float* cos_tab, const float* sin_tab, int table_len,
     const float* q_norm_w, const float* k_norm_w, float eps, void* out, float* part_o, float* part_ml,
-    int* counters, void* k_pool, void* v_pool, const int* cu_q, const int* kv_len,
+    void* k_pool, void* v_pool, const int* cu_q, const int* kv_len,
     const int* block_table, int max_blocks, int num_pages, int page_size, int n_entries, int nq, int nkv,
     int d, int window, float scale, int n_splits, int* err, cudaStream_t st) {
     if (n_entries <= 0) return 0;
@@ -1134,7 +1076,7 @@ CRANE_API int crane_paged_decode_attention_fused(
     fa.part_stride = part_stride; fa.qkv_stride = qkv_stride; fa.has_kv = has_kv; fa.rotary = rotary;
     fa.cos_tab = cos_tab; fa.sin_tab = sin_tab; fa.table_len = table_len; fa.q_norm_w = q_norm_w;
     fa.k_norm_w = k_norm_w; fa.eps = eps; fa.k_pool_w = (__nv_bfloat16*)k_pool;
-    fa.v_pool_w = (__nv_bfloat16*)v_pool; fa.counters = counters;
+    fa.v_pool_w = (__nv_bfloat16*)v_pool;
 #define CASE(DD)                                                                                  \
     case DD:                                                                                      \
         return launch_decode<DD, true>(nullptr, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len,  \

@@ -34,7 +34,7 @@ _SIGNATURES = {
     "crane_paged_prefill_attention_supports": [I, I, I],
     "crane_paged_prefill_attention": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P],
     "crane_paged_decode_attention_fused": [P, P, I, L, I, I, I, P, P, I, P, P, F, P, P, P, P, P, P, P, P,
-                                           P, I, I, I, I, I, I, I, I, F, I, P, P],
+                                           I, I, I, I, I, I, I, I, F, I, P, P],
     "crane_prefill_attention_tc_supports": [I, I, I, I],
     "crane_prefill_attention_tc": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, P],
     "crane_repetition_penalty": [P, L, I, I, P, I, P, P, P],
@@ -323,17 +323,16 @@ class Kernels:
 
     def paged_decode_attention_fused(self, qkv: Act, qkv_cols, has_kv, cos, sin, q_norm_w, k_norm_w,
                                      eps, out, k_pool, v_pool, cu_q, kv_len, block_table, page_size,
-                                     nq, nkv, d, window, scale, n_splits, part_o, part_ml, counters,
-                                     err) -> None:
+                                     nq, nkv, d, window, scale, n_splits, part_o, part_ml, err) -> None:
         """One token per entry, straight from the q/k/v product: rotary encoding,
-        per-head norm, cache write, attention and the merge of the key slices in
-        one kernel.  ``counters``: int32 zeros [entries * nkv], left zero."""
+        per-head norm, cache write and attention in one kernel, then the merge of
+        the key slices."""
         whole, parts, n_parts, stride = _split(qkv)
         n_entries = kv_len.shape[0]
         self._check(self.lib.crane_paged_decode_attention_fused(
             whole, parts, n_parts, stride, qkv_cols, 1 if has_kv else 0, 1 if cos is not None else 0,
             _ptr(cos), _ptr(sin), cos.shape[0] if cos is not None else 0, _ptr(q_norm_w),
-            _ptr(k_norm_w), float(eps), out.data_ptr(), _ptr(part_o), _ptr(part_ml), _ptr(counters),
+            _ptr(k_norm_w), float(eps), out.data_ptr(), _ptr(part_o), _ptr(part_ml),
             k_pool.data_ptr(), v_pool.data_ptr(), cu_q.data_ptr(), kv_len.data_ptr(),
             block_table.data_ptr(), block_table.shape[1], k_pool.shape[0], page_size, n_entries, nq,
             nkv, d, int(window), float(scale), int(n_splits), err.data_ptr(), self._stream(out)),

@@ -98,20 +98,17 @@ class GqaAttention(Part):
                   and k.decode_attention_supports(self.d, self.nq, self.nkv))
         if decode and self.d % 4 == 0:
             # single decoded tokens: rotary encoding, head norms, the cache write, attention over
-            # key slices (enough of them to fill the device) and their merge, all in one kernel
+            # key slices (enough of them to fill the device) in one kernel, their merge in a second
             splits = max(1, min(self.max_splits, (2 * rt.num_sms) // max(1, ctx.n_entries * self.nkv)))
             rows = rt.max_decode_rows * self.nq * min(self.max_splits, 32) + self.nq * self.max_splits
             part_o = rt.ws.get("attn_part_o", rows, self.d, torch.float32, cap=rows)
             part_ml = rt.ws.get("attn_part_ml", rows, 2, torch.float32, cap=rows)
-            counters = None
-            if os.environ.get("CRANE_MERGE_IN_ATTENTION", "0") == "1":
-                counters = rt.ws.zeros("attn_counters", rt.max_decode_rows * self.nkv, 1, torch.int32)
             k.paged_decode_attention_fused(qkv, self.qkv_cols, self.own_kv, cos, sin, self.q_norm,
                                            self.k_norm, self.eps, o, cache.k, cache.v, ctx.cu_q,
                                            ctx.kv_len, table, cache.page_size, self.nq, self.nkv,
                                            self.d, self.window, self.scale, splits, part_o, part_ml,
-                                           counters, rt.err)
-            rt.launches += 1 if (counters is not None or splits == 1) else 2
+                                           rt.err)
+            rt.launches += 1 if splits == 1 else 2
             return rt.linear(o, self.o_w, self.o_b, "attn_out")
         q = rt.ws.get("attn_q", n, self.nq * self.d, rt.dtype)
         k.rope_norm_cache(qkv, self.qkv_cols, rt.dtype, ctx.positions, ctx.tok_entry, table, cos,

@@ -581,16 +581,13 @@ def test_fused_decode_attention_equals_the_separate_kernels(K, err, d, nq, nkv, 
     part_ml = torch.empty(n * nq * splits * 2, device=DEV)
     K.paged_decode_attention(q, want, k1, v1, cu, kvl, table, page_size, nq, nkv, d, window, d ** -0.5,
                              splits, part_o, part_ml, err)
-    # one kernel, twice (the counters must be back at zero after the first call)
-    counters = torch.zeros(n * nkv, dtype=torch.int32, device=DEV)
     for _ in range(2):
         k2, v2 = k_pool.clone(), v_pool.clone()
         got = torch.full_like(q, 9.0)
         K.paged_decode_attention_fused(src, cols, True, cos, sin, qw, kw, 1e-5, got, k2, v2, cu, kvl, table,
-                                       page_size, nq, nkv, d, window, d ** -0.5, splits, part_o, part_ml,
-                                       counters, err)
+                                       page_size, nq, nkv, d, window, d ** -0.5, splits, part_o, part_ml, err)
         torch.cuda.synchronize()
-        assert int(err.item()) == 0 and int(counters.abs().sum()) == 0
+        assert int(err.item()) == 0
         assert torch.equal(k2, k1) and torch.equal(v2, v1)
         assert rel_err(got, want.double()) < 4e-3
 
