@@ -126,6 +126,40 @@ __device__ __forceinline__ void rope_norm_row(const FusedArgs& a, long long src,
     }
 }
 
+// Up to four pairs of neighbours of the raw product at once: from partial sums, the loads of
+// all four places and of up to eight slices are in flight together (one round trip instead of
+// one per place), added in slice order and rounded once as in raw2.
+__device__ __forceinline__ void raw2x4(const FusedArgs& a, const long long (&idx)[4], int n, float2 (&out)[4]) {
+    if (a.qkv_parts == nullptr) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            out[q] = q < n ? __bfloat1622float2(*(const __nv_bfloat162*)(a.qkv + idx[q])) : make_float2(0.f, 0.f);
+        return;
+    }
+    float2 acc[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) acc[q] = make_float2(0.f, 0.f);
+    for (int i = 0; i < a.n_parts; i += 8) {
+        float2 p[4][8];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                p[q][j] = (q < n && i + j < a.n_parts)
+                              ? *(const float2*)(a.qkv_parts + (long long)(i + j) * a.part_stride + idx[q])
+                              : make_float2(0.f, 0.f);
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                acc[q].x += p[q][j].x;
+                acc[q].y += p[q][j].y;
+            }
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) out[q] = __bfloat1622float2(__floats2bfloat162_rn(acc[q].x, acc[q].y));
+}
+
 // The same in two phases, so that the loads of several rows (and of the tables,
 // which are the same for all rows of a position) are in flight together.
 template <int D>
@@ -509,8 +543,8 @@ paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     __nv_bfloat16* q_s = (__nv_bfloat16*)(smem + WARPS * NSTAGE * STAGE_BYTES);           // [16][D]
-    __nv_bfloat16* row_s = q_s + 16 * D;                                                  // [WARPS][D]
-    uint64_t* full = (uint64_t*)(row_s + WARPS * D);                                      // [WARPS][NSTAGE]
+    __nv_bfloat16* row_s = q_s + 16 * D;                                                  // [WARPS][2][D]
+    uint64_t* full = (uint64_t*)(row_s + WARPS * 2 * D);                                  // [WARPS][NSTAGE]
 
     pdl_launch_dependents();
     const bool early = FUSED && fa.has_kv != 0;
@@ -592,20 +626,61 @@ paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
             w1[0] = *(const float2*)(fa.q_norm_w + j);
             w2[0] = *(const float2*)(fa.q_norm_w + j + D / 2);
         }
-        const long long q_src = (long long)t * fa.qkv_stride + (long long)(g * n_rep) * D;
+        const long long row_src = (long long)t * fa.qkv_stride;
+        const long long q_src = row_src + (long long)(g * n_rep) * D;
+        auto load_two = [&](int r, RowRegs<D>& ra, RowRegs<D>& rb) {
+            // rows r and r + WARPS of the group: four places, one round of loads
+            const bool two = r + WARPS < n_rep;
+            const long long at[4] = {q_src + (long long)r * D + j, q_src + (long long)r * D + j + D / 2,
+                                     q_src + (long long)(r + WARPS) * D + j,
+                                     q_src + (long long)(r + WARPS) * D + j + D / 2};
+            float2 got[4];
+            raw2x4(fa, at, two ? 4 : 2, got);
+            ra.u[0] = got[0]; ra.v[0] = got[1];
+            rb.u[0] = got[2]; rb.v[0] = got[3];
+        };
         RowRegs<D> ra, rb;
-        row_load<D>(fa, q_src + (long long)warp * D, lane, ra);
-        if (warp + WARPS < n_rep) row_load<D>(fa, q_src + (long long)(warp + WARPS) * D, lane, rb);
+        if (warp < n_rep) load_two(warp, ra, rb);
         for (int i = threadIdx.x; i < 16 * D / 2; i += WARPS * 32) ((uint32_t*)q_s)[i] = 0u;
         __syncthreads();
         for (int r = warp; r < n_rep; r += 2 * WARPS) {
-            if (r != warp) {
-                row_load<D>(fa, q_src + (long long)r * D, lane, ra);
-                if (r + WARPS < n_rep) row_load<D>(fa, q_src + (long long)(r + WARPS) * D, lane, rb);
-            }
+            if (r != warp) load_two(r, ra, rb);
             row_finish<D>(ra, rotate, cs, sn, norm, w1, w2, fa.eps, lane, q_s + r * D, nullptr);
             if (r + WARPS < n_rep)
                 row_finish<D>(rb, rotate, cs, sn, norm, w1, w2, fa.eps, lane, q_s + (r + WARPS) * D, nullptr);
+        }
+        // The warp whose tiles include the new position makes that position's key (encoded,
+        // normalised) and value now, for the page and, kept in shared memory, for its tile later:
+        // at the end of the loop these loads and the arithmetic would lengthen the whole kernel.
+        if (makes_kv && pos / TILE >= tile_begin && pos / TILE < tile_end &&
+            (pos / TILE - tile_begin) % WARPS == warp) {
+            const int page = table[pos / page_size];
+            if (page < 0 || page >= num_pages) {
+                bad_page = true;
+            } else {
+                const long long prow = (((long long)page * nkv + g) * page_size + pos % page_size) * D;
+                const long long k_src = row_src + (long long)(nq + g) * D, v_src = row_src + (long long)(nq + nkv + g) * D;
+                const long long at[4] = {k_src + j, k_src + j + D / 2, v_src + j, v_src + j + D / 2};
+                float2 got[4];
+                raw2x4(fa, at, 4, got);
+                RowRegs<D> rk;
+                rk.u[0] = got[0]; rk.v[0] = got[1];
+                float2 kw1[1], kw2[1];
+                kw1[0] = kw2[0] = make_float2(0.f, 0.f);
+                const bool knorm = fa.k_norm_w != nullptr;
+                if (knorm) {
+                    kw1[0] = *(const float2*)(fa.k_norm_w + j);
+                    kw2[0] = *(const float2*)(fa.k_norm_w + j + D / 2);
+                }
+                __nv_bfloat16* kv_lin = row_s + warp * 2 * D;              // [key row | value row]
+                row_finish<D>(rk, rotate, cs, sn, knorm, kw1, kw2, fa.eps, lane, kv_lin, fa.k_pool_w + prow);
+                const __nv_bfloat162 va = __floats2bfloat162_rn(got[2].x, got[2].y);
+                const __nv_bfloat162 vb = __floats2bfloat162_rn(got[3].x, got[3].y);
+                *(__nv_bfloat162*)(kv_lin + D + j) = va;
+                *(__nv_bfloat162*)(kv_lin + D + j + D / 2) = vb;
+                *(__nv_bfloat162*)(fa.v_pool_w + prow + j) = va;
+                *(__nv_bfloat162*)(fa.v_pool_w + prow + j + D / 2) = vb;
+            }
         }
         __syncthreads();
         const int r0 = lane >> 2, c0 = (lane & 3) * 2;
@@ -668,27 +743,12 @@ paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
             }
             __syncwarp();
             if (makes_kv && ti == pos / TILE) {
-                // this tile holds the new position: its key (encoded, normalised) and value are
-                // made here, for the tile in shared memory and for the page
-                const int page = table[pos / page_size];
-                if (page < 0 || page >= num_pages) {
-                    bad_page = true;
-                } else {
-                    const long long prow = (((long long)page * nkv + g) * page_size + pos % page_size) * D;
-                    const long long row_src = (long long)t * fa.qkv_stride;
-                    __nv_bfloat16* k_lin = row_s + warp * D;
-                    rope_norm_row<D>(fa, row_src + (long long)(nq + g) * D, pos, rotate, fa.k_norm_w, lane,
-                                     k_lin, fa.k_pool_w + prow);
-                    __syncwarp();
-                    const int r = pos % TILE;
-                    if (lane < 16) *(uint4*)(stage + sw_off(r, lane)) = *(const uint4*)(k_lin + lane * 8);
-                    for (int c = 2 * lane; c < D; c += 64) {
-                        const float2 x = raw2(fa, row_src + (long long)(nq + nkv + g) * D + c);
-                        const __nv_bfloat162 b = __floats2bfloat162_rn(x.x, x.y);
-                        *(__nv_bfloat162*)(stage + TILE128_BYTES + sw_off(r, c >> 3) + (c & 7) * 2) = b;
-                        *(__nv_bfloat162*)(fa.v_pool_w + prow + c) = b;
-                    }
-                }
+                // this tile holds the new position: its key and value, made before the loop, go
+                // into the tile in shared memory
+                const __nv_bfloat16* kv_lin = row_s + warp * 2 * D;
+                const int r = pos % TILE;
+                if (lane < 16) *(uint4*)(stage + sw_off(r, lane)) = *(const uint4*)(kv_lin + lane * 8);
+                else *(uint4*)(stage + TILE128_BYTES + sw_off(r, lane - 16)) = *(const uint4*)(kv_lin + D + (lane - 16) * 8);
                 __syncwarp();
             }
         }
@@ -965,7 +1025,7 @@ int launch_decode_tma(const void* q, void* out, float* part_o, float* part_ml, c
                       int max_blocks, int num_pages, int page_size, int nq, int nkv, int window,
                       float scale, int n_splits, int* err, const FusedArgs& fa, dim3 grid,
                       cudaStream_t st) {
-    constexpr int tiles = WARPS * NSTAGE * 2 * TILE128_BYTES + 16 * D128 * 2 + WARPS * D128 * 2 +
+    constexpr int tiles = WARPS * NSTAGE * 2 * TILE128_BYTES + 16 * D128 * 2 + WARPS * 2 * D128 * 2 +
                           WARPS * NSTAGE * 8;
     constexpr int merge = WARPS * 16 * (D128 + 2) * 4;
     constexpr int smem = (tiles > merge ? tiles : merge) + 1024;
