@@ -527,7 +527,13 @@ __device__ __forceinline__ uint32_t sw_off(int row, int chunk) {
     return (uint32_t)((chunk >> 3) * HALF_TILE_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
-template <bool FUSED>
+// CLUSTER: the CTAs of the slices of one (request, kv head) form a thread-block cluster (at most
+// 8 slices) and merge their results themselves through distributed shared memory: every CTA
+// leaves (max, sum, unnormalised output) of its slice in its own shared memory, and after a
+// cluster barrier each CTA works out its share of the output columns from all slices, in slice
+// order.  No scratch memory, no second kernel (a kernel of its own costs its place in the chain
+// of dependent launches, about 3 us per layer here, whatever little it does).
+template <bool FUSED, bool CLUSTER>
 __global__ void __launch_bounds__(WARPS * 32)
 paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
                              const __grid_constant__ CUtensorMap v_map,
@@ -853,6 +859,8 @@ paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
     __syncthreads();                                 // every warp is done with its tiles
     float* sm_o = (float*)smem;                      // [WARPS][16][D]
     float* sm_ml = sm_o + WARPS * 16 * D;            // [WARPS][16][2]
+    float* cl_ml = sm_ml + WARPS * 16 * 2;           // [16][2]  this slice's (max, sum), for the cluster's merge
+    float* cl_o = cl_ml + 16 * 2;                    // [16][D]  and its unnormalised output
     {
         const int r0 = lane >> 2, c0 = (lane & 3) * 2;
 #pragma unroll
@@ -884,11 +892,55 @@ paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
         const int h = g * n_rep + r;
         if (n_splits == 1) {
             out[((long long)t * nq + h) * D + c] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        } else if (CLUSTER) {
+            cl_o[r * D + c] = O;
+            if (c == 0) { cl_ml[r * 2] = M; cl_ml[r * 2 + 1] = L; }
         } else {
             const long long pi = ((long long)e * nq + h) * n_splits + split;
             part_o[pi * D + c] = O;
             if (c == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
         }
+    }
+    if (CLUSTER && n_splits > 1) {
+        // every slice's result is in its CTA's shared memory; this CTA takes its share of the
+        // n_rep x D outputs and reads that element of every slice (slice s = cluster rank s)
+        asm volatile("barrier.cluster.arrive.release.aligned;\n"
+                     "barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        const int total = n_rep * D;
+        const int begin = (int)((long long)split * total / n_splits), end = (int)((long long)(split + 1) * total / n_splits);
+        const uint32_t o_addr = smem_u32(cl_o), ml_addr = smem_u32(cl_ml);
+        for (int idx = begin + (int)threadIdx.x; idx < end; idx += WARPS * 32) {
+            const int r = idx / D;
+            float2 ml[8];
+            float ov[8];
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) {
+                ml[sp] = make_float2(-INFINITY, 0.f);
+                ov[sp] = 0.f;
+                if (sp < n_splits) {
+                    uint32_t ra, rb;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(ml_addr + (uint32_t)(r * 8)), "r"(sp));
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rb) : "r"(o_addr + (uint32_t)(idx * 4)), "r"(sp));
+                    asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(ml[sp].x), "=f"(ml[sp].y) : "r"(ra) : "memory");
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ov[sp]) : "r"(rb) : "memory");
+                }
+            }
+            float M = -INFINITY;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) M = fmaxf(M, ml[sp].x);
+            const float mb = (M == -INFINITY) ? 0.f : M;
+            float L = 0.f, acc = 0.f;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) {
+                const float f = exp2f(ml[sp].x - mb);        // 0 beyond n_splits
+                L += f * ml[sp].y;
+                acc += f * ov[sp];
+            }
+            out[((long long)t * nq + g * n_rep + r) * D + (idx % D)] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        }
+        // nobody leaves while a CTA of the cluster may still read its shared memory
+        asm volatile("barrier.cluster.arrive.release.aligned;\n"
+                     "barrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
 }
 
@@ -1006,6 +1058,15 @@ bool tma_path_enabled() {
     }
     return on == 1;
 }
+// CRANE_DECODE_CLUSTER=0: the slices always go through scratch memory and the merge kernel.
+bool cluster_merge_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* v = getenv("CRANE_DECODE_CLUSTER");
+        on = (v == nullptr || v[0] != '0') ? 1 : 0;
+    }
+    return on == 1;
+}
 // The pool as [rows, 128] bf16; box of 64 elements x TILE rows, 128-byte swizzle.
 bool pool_map(CUtensorMap* map, const void* pool, long long rows) {
     EncodeTiledFn fn = encode_fn();
@@ -1023,16 +1084,29 @@ template <bool FUSED>
 int launch_decode_tma(const void* q, void* out, float* part_o, float* part_ml, const void* k_pool,
                       const void* v_pool, const int* cu_q, const int* kv_len, const int* block_table,
                       int max_blocks, int num_pages, int page_size, int nq, int nkv, int window,
-                      float scale, int n_splits, int* err, const FusedArgs& fa, dim3 grid,
+                      float scale, int n_splits, int* err, const FusedArgs& fa, dim3 grid, bool cluster,
                       cudaStream_t st) {
     constexpr int tiles = WARPS * NSTAGE * 2 * TILE128_BYTES + 16 * D128 * 2 + WARPS * 2 * D128 * 2 +
                           WARPS * NSTAGE * 8;
-    constexpr int merge = WARPS * 16 * (D128 + 2) * 4;
+    constexpr int merge = (WARPS + 1) * 16 * (D128 + 2) * 4;
     constexpr int smem = (tiles > merge ? tiles : merge) + 1024;
     CUtensorMap km, vm;
     const long long rows = (long long)num_pages * nkv * page_size;
     if (!pool_map(&km, k_pool, rows) || !pool_map(&vm, v_pool, rows)) return (int)cudaErrorInvalidValue;
-    auto kern = paged_decode_attn_tma_kernel<FUSED>;
+    if (cluster) {
+        auto kern = paged_decode_attn_tma_kernel<FUSED, true>;
+        static bool configured = false;
+        if (!configured) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+                return (int)cudaGetLastError();
+            configured = true;
+        }
+        return crane_launch_cluster(kern, grid, dim3(WARPS * 32), smem, dim3(grid.x, 1, 1), st, km, vm,
+                                    (const __nv_bfloat16*)q, (__nv_bfloat16*)out, part_o, part_ml, cu_q, kv_len,
+                                    block_table, max_blocks, num_pages, page_size, nq, nkv, window,
+                                    scale * 1.4426950408889634f, n_splits, err, fa);
+    }
+    auto kern = paged_decode_attn_tma_kernel<FUSED, false>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
@@ -1062,11 +1136,13 @@ int launch_decode(const void* q, void* out, float* part_o, float* part_ml, const
     }
     dim3 grid(n_splits, nkv, n_entries);
     if (D == D128 && page_size % TILE == 0 && tma_path_enabled()) {
+        // 2 to 8 slices merge themselves in a cluster; more go through scratch memory and a second kernel
+        const bool cluster = n_splits > 1 && n_splits <= 8 && cluster_merge_enabled();
         const int rc = launch_decode_tma<FUSED>(q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len,
                                                 block_table, max_blocks, num_pages, page_size, nq, nkv,
-                                                window, scale, n_splits, err, fa, grid, st);
+                                                window, scale, n_splits, err, fa, grid, cluster, st);
         if (rc != 0) return rc;
-        if (n_splits > 1)
+        if (n_splits > 1 && !cluster)
             return crane_launch(decode_merge_kernel, dim3(n_entries, nq), dim3(D >= 128 ? 128 : 64), 0, st,
                                 (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, cu_q, nq,
                                 D, n_splits);

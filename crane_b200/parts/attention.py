@@ -100,6 +100,8 @@ class GqaAttention(Part):
             # single decoded tokens: rotary encoding, head norms, the cache write, attention over
             # key slices (enough of them to fill the device) in one kernel, their merge in a second
             splits = max(1, min(self.max_splits, (2 * rt.num_sms) // max(1, ctx.n_entries * self.nkv)))
+            if 8 < splits <= 11:
+                splits = 8          # up to 8 slices merge themselves in a cluster, without a second kernel
             rows = rt.max_decode_rows * self.nq * min(self.max_splits, 32) + self.nq * self.max_splits
             part_o = rt.ws.get("attn_part_o", rows, self.d, torch.float32, cap=rows)
             part_ml = rt.ws.get("attn_part_ml", rows, 2, torch.float32, cap=rows)
