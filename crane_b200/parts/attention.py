@@ -110,7 +110,7 @@ class GqaAttention(Part):
                                            ctx.kv_len, table, cache.page_size, self.nq, self.nkv,
                                            self.d, self.window, self.scale, splits, part_o, part_ml,
                                            rt.err)
-            rt.launches += 1 if splits == 1 else 2
+            rt.launches += 1 if splits <= 8 else 2     # the merge is a launch of its own above 8 slices
             return rt.linear(o, self.o_w, self.o_b, "attn_out")
         q = rt.ws.get("attn_q", n, self.nq * self.d, rt.dtype)
         k.rope_norm_cache(qkv, self.qkv_cols, rt.dtype, ctx.positions, ctx.tok_entry, table, cos,

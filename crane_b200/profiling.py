@@ -128,12 +128,14 @@ def decode_attention(a):
     w = torch.ones(d, device=DEV)
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     splits = a.splits or max(1, min(32, (2 * sms) // (B * nkv)))
+    if not a.splits and 8 < splits <= 11:
+        splits = 8              # what the attention part chooses: up to 8 slices merge in a cluster
     o = torch.empty(B, nq * d, device=DEV, dtype=BF)
     po = torch.empty(B * nq * splits * d, device=DEV); pml = torch.empty(B * nq * splits * 2, device=DEV)
 
     def fn():
         K.paged_decode_attention_fused(qkv, cols, True, cos, sin, w, w, 1e-5, o, kp, vp, cu, kvl, table, ps,
-                                       nq, nkv, d, 0, d ** -0.5, splits, po, pml, None, err)
+                                       nq, nkv, d, 0, d ** -0.5, splits, po, pml, err)
     t = _time(fn, a.warmup, a.reps)
     assert int(err.item()) == 0
     nbytes = B * T * nkv * d * 2 * 2
