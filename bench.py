@@ -260,6 +260,8 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
     ap.add_argument("--only-prefill", action="store_true",
                     help="measure the 2,048-token prefill alone (for profiling); prints its record only")
+    ap.add_argument("--prefill-tokens", type=int, default=2048,
+                    help="with --only-prefill: another prompt length than the contract's 2,048 (one step)")
     ap.add_argument("--sizes", default="1.8b", choices=["1.8b", "4b", "7b"],
                     help="layer sizes: Hunyuan 1.8B (the default, the headline configuration), 4B or 7B")
     ap.add_argument("--only-decode", action="store_true",
@@ -277,6 +279,9 @@ def main():
     cfg = dict(MODEL)
     cfg.update(OTHER_SIZES.get(args.sizes, {}))
     full_layers = cfg["num_hidden_layers"]
+    # a context beyond the configuration's limit: the same layer sizes with a longer position table
+    cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], args.context + 2048,
+                                         args.prefill_tokens + 2048)
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
     layers, vocab = cfg["num_hidden_layers"], cfg["vocab_size"]
@@ -288,15 +293,17 @@ def main():
     opts = dict(page_size=page, num_pages=need_tokens // page + 64, max_concurrent=max(64, args.batch),
                 max_seq_len=args.context + 1024, max_batched_tokens=2048, chunk_size=2048)
     if args.only_prefill:
-        opts.update(num_pages=2048 // page + 8, max_concurrent=4)
+        pt = args.prefill_tokens
+        opts.update(num_pages=pt // page + 8, max_concurrent=4, max_seq_len=pt + 1024,
+                    max_batched_tokens=max(2048, pt), chunk_size=max(2048, pt))
     if args.only_decode:
         opts.update(num_pages=args.batch * (args.context + args.steps + args.warmup + 64) // page + 64)
     model = build_model(cfg, opts)
     runner = model.runner
     if args.only_prefill:
-        pms = time_prefill(model, 2048, vocab, reps=max(1, args.steps), mark=True)
-        flops = prefill_flops(cfg, layers, 2048)
-        print(json.dumps({"prefill": {"value": round(2048 * 1000.0 / pms, 1), "tokens": 2048,
+        pms = time_prefill(model, pt, vocab, reps=max(1, args.steps), mark=True)
+        flops = prefill_flops(cfg, layers, pt)
+        print(json.dumps({"prefill": {"value": round(pt * 1000.0 / pms, 1), "tokens": pt,
                                       "ms": round(pms, 3), "layers": layers,
                                       "frac": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}}))
         return 0

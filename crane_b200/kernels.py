@@ -281,6 +281,19 @@ class Kernels:
             block_table.shape[1], k_pool.shape[0], page_size, q.shape[0], nq, nkv, d, int(window),
             float(scale), err.data_ptr(), self._stream(q)), "paged_attention_simt")
 
+    @staticmethod
+    def decode_splits(entries: int, nkv: int, sms: int, cap: int = 64) -> int:
+        """Key slices per (request, kv head) of the fused decode attention: enough CTAs to fill
+        the device twice over (two fit on an SM), at most ``cap`` (the merge kernel takes 64).
+        Measured in whole decode steps: 9 to 11 slices lose to 8, which merge themselves in a
+        cluster without a second kernel; 33 to 40 lose to 32."""
+        splits = max(1, min(cap, 64, (2 * sms) // max(1, entries * nkv)))
+        if 8 < splits <= 11:
+            return 8
+        if 32 < splits <= 40:
+            return 32
+        return splits
+
     def decode_attention_supports(self, d: int, nq: int, nkv: int) -> bool:
         return bool(self.lib.crane_paged_decode_attention_supports(d, nq, nkv))
 

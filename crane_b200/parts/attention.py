@@ -78,7 +78,7 @@ class GqaAttention(Part):
         if self.position is not None:
             self.position.load(weights, rt)          # a position encoding may have tensors of its own
         self.qkv_cols = self.qkv_w.shape[0]
-        self.max_splits = int(os.environ.get("CRANE_DECODE_SPLITS", "32"))
+        self.max_splits = int(os.environ.get("CRANE_DECODE_SPLITS", "64"))
 
     def cache_need(self) -> CacheNeed:
         if not self.own_kv:
@@ -99,10 +99,9 @@ class GqaAttention(Part):
         if decode and self.d % 4 == 0:
             # single decoded tokens: rotary encoding, head norms, the cache write, attention over
             # key slices (enough of them to fill the device) in one kernel, their merge in a second
-            splits = max(1, min(self.max_splits, (2 * rt.num_sms) // max(1, ctx.n_entries * self.nkv)))
-            if 8 < splits <= 11:
-                splits = 8          # up to 8 slices merge themselves in a cluster, without a second kernel
-            rows = rt.max_decode_rows * self.nq * min(self.max_splits, 32) + self.nq * self.max_splits
+            splits = k.decode_splits(ctx.n_entries, self.nkv, rt.num_sms, self.max_splits)
+            # slices x entries never exceed two CTAs per SM: that bounds the slices' scratch rows
+            rows = self.nq * (2 * rt.num_sms // self.nkv + 1)
             part_o = rt.ws.get("attn_part_o", rows, self.d, torch.float32, cap=rows)
             part_ml = rt.ws.get("attn_part_ml", rows, 2, torch.float32, cap=rows)
             k.paged_decode_attention_fused(qkv, self.qkv_cols, self.own_kv, cos, sin, self.q_norm,

@@ -127,9 +127,7 @@ def decode_attention(a):
     cos = torch.randn(T + 8, d // 2, device=DEV); sin = torch.randn(T + 8, d // 2, device=DEV)
     w = torch.ones(d, device=DEV)
     sms = torch.cuda.get_device_properties(0).multi_processor_count
-    splits = a.splits or max(1, min(32, (2 * sms) // (B * nkv)))
-    if not a.splits and 8 < splits <= 11:
-        splits = 8              # what the attention part chooses: up to 8 slices merge in a cluster
+    splits = a.splits or K.decode_splits(B, nkv, sms)       # what the attention part chooses
     o = torch.empty(B, nq * d, device=DEV, dtype=BF)
     po = torch.empty(B * nq * splits * d, device=DEV); pml = torch.empty(B * nq * splits * 2, device=DEV)
 

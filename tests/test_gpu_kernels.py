@@ -541,7 +541,10 @@ def test_paged_prefill_attention_mixed_batch(K, err, d, nq, nkv, page_size, wind
 
 @pytest.mark.parametrize("d,nq,nkv,page_size,window,splits,qk_norm,parts", [
     (128, 16, 4, 64, 0, 9, True, 0), (128, 16, 4, 64, 0, 1, True, 3), (64, 8, 8, 16, 0, 3, False, 0),
-    (16, 4, 2, 8, 0, 2, True, 2), (32, 8, 2, 16, 50, 4, True, 0), (48, 6, 3, 32, 0, 32, False, 5)])
+    (16, 4, 2, 8, 0, 2, True, 2), (32, 8, 2, 16, 50, 4, True, 0), (48, 6, 3, 32, 0, 32, False, 5),
+    # head size 128, 2 to 8 slices: the slices merge in a thread-block cluster; 64: the most slices
+    (128, 16, 4, 64, 0, 8, True, 6), (128, 8, 8, 32, 0, 2, False, 0), (128, 12, 4, 64, 100, 5, True, 0),
+    (128, 16, 4, 64, 0, 64, True, 0)])
 def test_fused_decode_attention_equals_the_separate_kernels(K, err, d, nq, nkv, page_size, window,
                                                             splits, qk_norm, parts):
     """Rotary encoding, head norms, cache write, attention and merge in one
@@ -560,7 +563,10 @@ def test_fused_decode_attention_equals_the_separate_kernels(K, err, d, nq, nkv, 
     if parts:
         p = torch.randn(parts, n, cols, device=DEV)
         p[0] += qkv - p.sum(0)
-        src, whole = Partials(p), p.sum(0).bfloat16()
+        whole = p[0].clone()
+        for i in range(1, parts):
+            whole += p[i]                       # in slice order, as the kernel adds them
+        src, whole = Partials(p), whole.bfloat16()
     else:
         src = whole = qkv.bfloat16()
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
