@@ -358,6 +358,7 @@ __global__ void rope_norm_cache_kernel(GemmOut<T> qkv, int qkv_stride,
         nw = q_norm_w;
     } else {
         const int e = tok_entry[t];
+        if (e < 0) return;                         // a row that pads the step: it has no place in a cache
         const int page = block_table[(long long)e * max_blocks + pos / page_size];
         if (page < 0 || page >= num_pages) {
             if (lane == 0) atomicOr(err, CRANE_ERR_PAGE_RANGE);
@@ -501,10 +502,12 @@ __global__ void rope_norm_cache_d128_kernel(const __nv_bfloat16* __restrict__ qk
             dst = q_out + ((long long)t * nq + h) * D;
             nw = q_norm_w;
         } else {
-            const int page = block_table[(long long)tok_entry[t] * max_blocks + pos / page_size];
-            if (page < 0 || page >= num_pages) {
+            // a negative entry: a row that pads the step; it has no place in a cache, dst stays null
+            const int e = tok_entry[t];
+            const int page = e < 0 ? -1 : block_table[(long long)e * max_blocks + pos / page_size];
+            if (e >= 0 && (page < 0 || page >= num_pages)) {
                 if (sub == 0) atomicOr(err, CRANE_ERR_PAGE_RANGE);
-            } else {
+            } else if (e >= 0) {
                 is_v = h >= nq + nkv;
                 const int g = is_v ? h - nq - nkv : h - nq;
                 dst = (is_v ? v_pool : k_pool) + (((long long)page * nkv + g) * page_size + pos % page_size) * D;

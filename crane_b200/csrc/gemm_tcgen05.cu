@@ -766,16 +766,41 @@ EncodeTiledFn encode_fn() {
 }
 
 // [rows, k] bf16, k contiguous, `ld` elements between rows; box of 64 x box_rows.
+// A descriptor depends on nothing but these arguments, and a model asks for the same few
+// hundred (every weight, a handful of activation buffers) step after step: the last ones are
+// kept per thread and found again by their arguments, which saves the driver call.
+struct MapSlot {
+    const void* ptr;
+    long long ld;
+    int rows, k, box_rows;
+    bool used;
+    CUtensorMap map;
+};
+constexpr int MAP_SLOTS = 1024;                      // a power of two
+
 bool make_map(CUtensorMap* map, const void* ptr, int rows, int k, long long ld, int box_rows) {
+    static thread_local MapSlot* slots = nullptr;
+    if (!slots) slots = new MapSlot[MAP_SLOTS]();
+    uint64_t h = (uint64_t)(uintptr_t)ptr >> 4;
+    h ^= ((uint64_t)(uint32_t)rows << 20) ^ ((uint64_t)(uint32_t)box_rows << 44) ^ ((uint64_t)(uint32_t)k << 8);
+    h *= 0x9E3779B97F4A7C15ull;
+    MapSlot& sl = slots[(h >> 40) & (MAP_SLOTS - 1)];
+    if (sl.used && sl.ptr == ptr && sl.rows == rows && sl.k == k && sl.ld == ld && sl.box_rows == box_rows) {
+        *map = sl.map;
+        return true;
+    }
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
     cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
-              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    if (fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
+           estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    sl.ptr = ptr; sl.ld = ld; sl.rows = rows; sl.k = k; sl.box_rows = box_rows; sl.map = *map; sl.used = true;
+    return true;
 }
 
 template <int BN, int STAGES, bool OUT_F32, bool TRANSPOSED>

@@ -63,6 +63,9 @@ class StepContext:
                                        # a token id <= -2 in ``tokens`` is read from row -id - 2
     graph_bucket: int = 0       # > 0: a decode step padded to this many entries
     real_entries: int = 0
+    graph_key: Optional[tuple] = None   # a step with prompt portions whose rows are padded to a
+                                        # multiple of 64 so that a captured graph fits it; the
+                                        # padding rows have tok_entry -1 and belong to no entry
 
 
 class _MetaBuffers:
@@ -130,7 +133,8 @@ class ModelRunner:
         self.deferred_tokens = torch.zeros(self.cap_entries, dtype=torch.int32, device=self.rt.device)
         self.steps = 0
         # decode steps (one token per entry) of the bfloat16 path replay a captured graph
-        self._graphs: Dict[int, tuple] = {}
+        self._graphs: Dict[object, tuple] = {}
+        self._shape_seen: Dict[tuple, int] = {}      # how often a shape of small step has come
         self._graph_generation = -1
         self._graphs_ok = (self.cfg.use_cuda_graphs and not self.rt.exact
                            and all(n.kind != "state" for n in self.model.cache_needs()))
@@ -236,6 +240,16 @@ class ModelRunner:
         pad_to = 0
         if (self._graphs_ok and max(counts) == 1 and all(len(e.want) == 1 for e in entries)):
             pad_to = self._bucket(n_entries)
+        # a small step with prompt portions: its rows are padded to a multiple of 64, and from the
+        # second step of the same (rows, entries, wanted) on a captured graph is replayed
+        key = None
+        if (not pad_to and self._graphs_ok and 0 < n_tokens <= self.cfg.graph_max_tokens):
+            rows = min(-(-n_tokens // 64) * 64, self.cap_tokens)
+            shape = ("rows", rows, n_entries, sum(len(e.want) for e in entries))
+            seen = self._shape_seen.get(shape, 0) + 1
+            self._shape_seen[shape] = seen
+            if seen >= 2 and shape[3] > 0:
+                key = shape
         m = self.meta
         m.copied.synchronize()                      # the last step's copy has left the host block
         real_entries = n_entries
@@ -252,6 +266,11 @@ class ModelRunner:
                                         m.off["cu_q"], m.off["kv_len"], m.off["slots"], m.bt_off_arr,
                                         m.max_blocks_arr)
         m.view("tokens", n_tokens, False)[:] = arrays[0] if len(arrays) == 1 else np.concatenate(arrays)
+        if key is not None and key[1] > n_tokens:
+            m.view("tokens", key[1], False)[n_tokens:] = 0
+            m.view("positions", key[1], False)[n_tokens:] = 0
+            m.view("tok_entry", key[1], False)[n_tokens:] = -1
+            n_tokens = key[1]
         cu = m.view("cu_q", n_entries + 1, False)
         kvl = m.view("kv_len", n_entries, False)
         slots = m.view("slots", n_entries, False)
@@ -268,6 +287,7 @@ class ModelRunner:
 
         ctx = StepContext()
         ctx.graph_bucket, ctx.real_entries = pad_to, real_entries
+        ctx.graph_key = key
         ctx.n_tokens, ctx.n_entries, ctx.n_want = n_tokens, n_entries, n_want
         ctx.max_q_len = int(cnt.max())
         ctx.max_kv_len = int(kvl.max())
@@ -293,7 +313,9 @@ class ModelRunner:
         ctx = self.prepare(entries, reserved)
         self.steps += 1
         if ctx.graph_bucket:
-            return self._replay(ctx)[:ctx.real_entries]
+            return self._replay(ctx, ctx.graph_bucket)[:ctx.real_entries]
+        if ctx.graph_key is not None:
+            return self._replay(ctx, ctx.graph_key)
         return self.model.forward(ctx, self.pools.layers)
 
     # ---- captured decode steps -----------------------------------------
@@ -303,11 +325,17 @@ class ModelRunner:
             b *= 2
         return min(b, self.cap_entries) if b <= self.cap_entries else 0
 
-    def _replay(self, ctx: StepContext) -> torch.Tensor:
+    MAX_SHAPE_GRAPHS = 48       # graphs of small steps kept; the least recently used one goes first
+
+    def _replay(self, ctx: StepContext, key) -> torch.Tensor:
         if self._graph_generation != self.rt.ws.generation:
             self._graphs.clear()                    # a buffer moved: captured addresses are stale
             self._graph_generation = self.rt.ws.generation
-        entry = self._graphs.get(ctx.graph_bucket)
+        entry = self._graphs.pop(key, None)
+        if entry is None and isinstance(key, tuple):
+            shapes = [k for k in self._graphs if isinstance(k, tuple)]
+            if len(shapes) >= self.MAX_SHAPE_GRAPHS:
+                del self._graphs[shapes[0]]
         if entry is None:
             # once eagerly, so that every buffer exists; then the same step again under capture
             # (it rewrites the same cache rows with the same values)
@@ -321,7 +349,7 @@ class ModelRunner:
             with torch.cuda.graph(graph):
                 logits = self.model.forward(ctx, self.pools.layers)
             entry = (graph, logits, self.rt.launches - before)
-            self._graphs[ctx.graph_bucket] = entry
+        self._graphs[key] = entry                   # (back) at the end: the most recently used
         graph, logits, launches = entry
         graph.replay()
         self.rt.launches += launches

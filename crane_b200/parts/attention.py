@@ -17,7 +17,7 @@ import os
 import torch
 
 from ..weights.loader import TensorSpec
-from .base import CacheNeed, Part, build_part, register_part
+from .base import CacheNeed, Part, build_part, query_tiles, register_part
 
 
 @register_part("mixer", "gqa_attention")
@@ -129,14 +129,12 @@ class GqaAttention(Part):
             rt.launches += 3 if splits > 1 else 2
         elif (not rt.exact and rt.use_tc_attention
               and k.prefill_attention_tc_supports(self.d, self.nq, self.nkv, cache.page_size)):
-            q_lens = ctx.h_cu_q[1:ctx.n_entries + 1] - ctx.h_cu_q[:ctx.n_entries]
-            tiles = int(((q_lens + 127) // 128).sum())
+            tiles = query_tiles(ctx, 128)
             k.prefill_attention_tc(q, o, cache.k, cache.v, ctx.cu_q, ctx.kv_len, table, cache.page_size,
                                    tiles, self.nq, self.nkv, self.d, self.window, self.scale, rt.err)
             rt.launches += 2
         elif not rt.exact and k.prefill_attention_supports(self.d, self.nq, self.nkv):
-            q_lens = ctx.h_cu_q[1:ctx.n_entries + 1] - ctx.h_cu_q[:ctx.n_entries]
-            tiles = int(((q_lens + 63) // 64).sum())
+            tiles = query_tiles(ctx, 64)
             k.paged_prefill_attention(q, o, cache.k, cache.v, ctx.cu_q, ctx.kv_len, table,
                                       cache.page_size, tiles, self.nq, self.nkv, self.d, self.window,
                                       self.scale, rt.err)

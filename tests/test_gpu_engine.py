@@ -190,6 +190,49 @@ def test_overlapped_steps_change_no_token(dtype, model_folders):
     assert runs[False] == runs[True]
 
 
+@pytest.mark.parametrize("name", ["B", "C", "S18"])
+def test_small_steps_replay_graphs_with_the_same_logits(name, model_folders):
+    """Steps with prompt portions of up to graph_max_tokens tokens are padded to
+    a multiple of 64 rows and, from the second step of a shape on, replay a
+    captured graph: prompts of different lengths under one shape, then a
+    portion beside decoded tokens, then decoding, give the logits of an engine
+    that launches every step kernel by kernel; the padding rows write nothing
+    into the cache (the decoded tokens that follow read it)."""
+    from crane_b200.engine import StepEntry
+    folder = model_folders(name, "bfloat16")
+    rng = np.random.default_rng(3)
+    vocab = tiny_configs.TINY[name]["config"]["vocab_size"]
+    prompts = [rng.integers(0, vocab, n).tolist() for n in (70, 100, 128, 65, 90, 101)]
+    runs = {}
+    for graphs in (0, 1024):
+        m = load(folder, "bf16", page_size=tiny_configs.TINY[name]["page_size"], num_pages=64,
+                 max_concurrent=16, max_batched_tokens=256, chunk_size=256, graph_max_tokens=graphs)
+        r = m.runner
+        out = []
+        for i, p in enumerate(prompts):                         # one shape: 128 rows, 1 entry, 2 wanted
+            out.append(r.step([StepEntry(i, p, [0, len(p) - 1])]).float().cpu())
+        for t in range(3):                                      # 4 single tokens beside a portion of 30
+            fresh = rng.integers(0, vocab, 30).tolist()
+            entries = [StepEntry(i, [int(rng.integers(0, vocab))], [0]) for i in range(4)]
+            entries.append(StepEntry(10 + t, fresh, [29]))
+            out.append(r.step(entries).float().cpu())
+        for t in range(3):                                      # all nine decode (the decode graphs)
+            ids = list(range(4)) + [4, 5] + [10, 11, 12]
+            out.append(r.step([StepEntry(i, [int(rng.integers(0, vocab))], [0]) for i in ids]).float().cpu())
+        r.rt.check_errors()
+        runs[graphs] = (out, r.graph_replays)
+        for i in list(range(6)) + [10, 11, 12]:
+            r.end(i)
+        r.table.check()
+        rng = np.random.default_rng(3)
+        prompts = [rng.integers(0, vocab, n).tolist() for n in (70, 100, 128, 65, 90, 101)]
+    assert runs[0][1] == 3                                      # only the decode steps
+    assert runs[1024][1] == 3 + 5 + 2                           # prompts 2..6, mixed steps 2 and 3
+    for a, b in zip(runs[0][0], runs[1024][0]):
+        assert a.shape == b.shape
+        assert (a - b).abs().max() <= 2e-3 * a.abs().max()
+
+
 def test_refusals(model_folders):
     folder = model_folders("A", "float32")
     m = load(folder, "fp32", page_size=16, num_pages=16, max_concurrent=2, max_batched_tokens=64)
