@@ -248,7 +248,7 @@ class ModelRunner:
             shape = ("rows", rows, n_entries, sum(len(e.want) for e in entries))
             seen = self._shape_seen.get(shape, 0) + 1
             self._shape_seen[shape] = seen
-            if seen >= 2 and shape[3] > 0:
+            if seen >= 2:
                 key = shape
         m = self.meta
         m.copied.synchronize()                      # the last step's copy has left the host block

@@ -211,6 +211,11 @@ def test_small_steps_replay_graphs_with_the_same_logits(name, model_folders):
         out = []
         for i, p in enumerate(prompts):                         # one shape: 128 rows, 1 entry, 2 wanted
             out.append(r.step([StepEntry(i, p, [0, len(p) - 1])]).float().cpu())
+        for i in (20, 21, 22):                                  # portions of which nothing is wanted
+            p = rng.integers(0, vocab, 150).tolist()
+            assert r.step([StepEntry(i, p[:100], [])]).shape[0] == 0
+            out.append(r.step([StepEntry(i, p[100:], [49])]).float().cpu())
+            r.end(i)
         for t in range(3):                                      # 4 single tokens beside a portion of 30
             fresh = rng.integers(0, vocab, 30).tolist()
             entries = [StepEntry(i, [int(rng.integers(0, vocab))], [0]) for i in range(4)]
@@ -227,7 +232,7 @@ def test_small_steps_replay_graphs_with_the_same_logits(name, model_folders):
         rng = np.random.default_rng(3)
         prompts = [rng.integers(0, vocab, n).tolist() for n in (70, 100, 128, 65, 90, 101)]
     assert runs[0][1] == 3                                      # only the decode steps
-    assert runs[1024][1] == 3 + 5 + 2                           # prompts 2..6, mixed steps 2 and 3
+    assert runs[1024][1] == 3 + 5 + 2 + 4                       # prompts 2..6, mixed steps 2 and 3, 4 portions
     for a, b in zip(runs[0][0], runs[1024][0]):
         assert a.shape == b.shape
         assert (a - b).abs().max() <= 2e-3 * a.abs().max()
