@@ -336,6 +336,9 @@ class ModelRunner:
             shapes = [k for k in self._graphs if isinstance(k, tuple)]
             if len(shapes) >= self.MAX_SHAPE_GRAPHS:
                 del self._graphs[shapes[0]]
+                # a capture costs more than two steps launched kernel by kernel: a shape that was
+                # dropped has to come ten times more before it is captured again
+                self._shape_seen[shapes[0]] = -8
         if entry is None:
             # once eagerly, so that every buffer exists; then the same step again under capture
             # (it rewrites the same cache rows with the same values)
