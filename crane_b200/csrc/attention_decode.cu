@@ -1160,10 +1160,53 @@ int launch_decode(const void* q, void* out, float* part_o, float* part_ml, const
 }
 }  // namespace
 
+// Every head size is compiled as an object of its own from this file (the build passes
+// CRANE_HEAD_SIZE), in parallel: such an object holds nothing but that size's kernels and the
+// launcher below.  The object without CRANE_HEAD_SIZE holds the entry points, which pick a launcher.
+#define CRANE_CAT2(a, b) a##b
+#define CRANE_CAT(a, b) CRANE_CAT2(a, b)
+#define CRANE_DECODE_LAUNCHER_ARGS                                                                   \
+    int fused, const void *q, void *out, float *part_o, float *part_ml, const void *k_pool,           \
+        const void *v_pool, const int *cu_q, const int *kv_len, const int *block_table, int max_blocks, \
+        int num_pages, int page_size, int n_entries, int nq, int nkv, int window, float scale,         \
+        int n_splits, int *err, const void *fused_args, cudaStream_t st
+#ifdef CRANE_HEAD_SIZE
+extern "C" int CRANE_CAT(crane_decode_launch_d, CRANE_HEAD_SIZE)(CRANE_DECODE_LAUNCHER_ARGS) {
+    const FusedArgs& fa = *(const FusedArgs*)fused_args;
+    if (fused)
+        return launch_decode<CRANE_HEAD_SIZE, true>(q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len,
+                                                    block_table, max_blocks, num_pages, page_size,
+                                                    n_entries, nq, nkv, window, scale, n_splits, err, fa, st);
+    return launch_decode<CRANE_HEAD_SIZE, false>(q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len,
+                                                 block_table, max_blocks, num_pages, page_size, n_entries,
+                                                 nq, nkv, window, scale, n_splits, err, fa, st);
+}
+#else
+#define CRANE_DECODE_HEAD_SIZES(X) X(16) X(32) X(48) X(64) X(80) X(96) X(112) X(128) X(160) X(192) X(256)
+#define DECLARE(DD) extern "C" int crane_decode_launch_d##DD(CRANE_DECODE_LAUNCHER_ARGS);
+CRANE_DECODE_HEAD_SIZES(DECLARE)
+#undef DECLARE
+
+namespace {
+int launch_for_head_size(int d, CRANE_DECODE_LAUNCHER_ARGS) {
+#define CASE(DD)                                                                                     \
+    case DD:                                                                                         \
+        return crane_decode_launch_d##DD(fused, q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len, \
+                                         block_table, max_blocks, num_pages, page_size, n_entries, nq, \
+                                         nkv, window, scale, n_splits, err, fused_args, st);
+    switch (d) { CRANE_DECODE_HEAD_SIZES(CASE) }
+#undef CASE
+    return (int)cudaErrorInvalidValue;
+}
+}  // namespace
+
 // 1 if the kernel is built for this head size and group size, else 0.
 CRANE_API int crane_paged_decode_attention_supports(int d, int nq, int nkv) {
     if (nkv <= 0 || nq % nkv != 0 || nq / nkv > 16) return 0;
-    return d == 16 || d == 32 || d == 48 || d == 64 || d == 128;
+#define IS(DD) if (d == DD) return 1;
+    CRANE_DECODE_HEAD_SIZES(IS)
+#undef IS
+    return 0;
 }
 
 // One token per entry (row cu_q[e] of q and out).  part_o needs
@@ -1179,16 +1222,9 @@ CRANE_API int crane_paged_decode_attention(const void* q, void* out, float* part
     if (!crane_paged_decode_attention_supports(d, nq, nkv) || n_splits < 1 || n_splits > 64)
         return (int)cudaErrorInvalidValue;
     const FusedArgs none = {};
-#define CASE(DD)                                                                                  \
-    case DD:                                                                                      \
-        return launch_decode<DD, false>(q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len,       \
-                                        block_table, max_blocks, num_pages, page_size, n_entries, nq, \
-                                        nkv, window, scale, n_splits, err, none, st);
-    switch (d) {
-        CASE(16) CASE(32) CASE(48) CASE(64) CASE(128)
-    }
-#undef CASE
-    return (int)cudaErrorInvalidValue;
+    return launch_for_head_size(d, 0, q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len, block_table,
+                                max_blocks, num_pages, page_size, n_entries, nq, nkv, window, scale,
+                                n_splits, err, &none, st);
 }
 
 // The fused form: q, k and v of the step's tokens come raw from the product
@@ -1213,16 +1249,9 @@ CRANE_API int crane_paged_decode_attention_fused(
     fa.cos_tab = cos_tab; fa.sin_tab = sin_tab; fa.table_len = table_len; fa.q_norm_w = q_norm_w;
     fa.k_norm_w = k_norm_w; fa.eps = eps; fa.k_pool_w = (__nv_bfloat16*)k_pool;
     fa.v_pool_w = (__nv_bfloat16*)v_pool;
-#define CASE(DD)                                                                                  \
-    case DD:                                                                                      \
-        return launch_decode<DD, true>(nullptr, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len,  \
-                                       block_table, max_blocks, num_pages, page_size, n_entries, nq,  \
-                                       nkv, window, scale, n_splits, err, fa, st);
-    switch (d) {
-        CASE(16) CASE(32) CASE(48) CASE(64) CASE(128)
-    }
-#undef CASE
-    return (int)cudaErrorInvalidValue;
+    return launch_for_head_size(d, 1, nullptr, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len,
+                                block_table, max_blocks, num_pages, page_size, n_entries, nq, nkv, window,
+                                scale, n_splits, err, &fa, st);
 }
 
 // ------------------------------------------------------------------------
@@ -1294,3 +1323,4 @@ CRANE_API int crane_paged_decode_attention_noalloc(const void* q, void* out, con
                                         block_table, max_blocks, num_pages, page_size, n_entries, nq,
                                         nkv, d, window, scale, n_splits, err, stream);
 }
+#endif  // CRANE_HEAD_SIZE

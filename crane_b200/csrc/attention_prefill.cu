@@ -218,9 +218,32 @@ int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_p
 }
 }  // namespace
 
+// Every head size is compiled as an object of its own from this file (the build passes
+// CRANE_HEAD_SIZE), in parallel; the object without it holds the entry points.
+#define CRANE_CAT2(a, b) a##b
+#define CRANE_CAT(a, b) CRANE_CAT2(a, b)
+#define CRANE_PREFILL_LAUNCHER_ARGS                                                                    \
+    const void *q, void *out, const void *k_pool, const void *v_pool, const int *cu_q, const int *kv_len, \
+        const int *block_table, int max_blocks, int num_pages, int page_size, int n_entries,            \
+        int total_q_tiles, int nq, int nkv, int window, float scale, int *err, cudaStream_t st
+#ifdef CRANE_HEAD_SIZE
+extern "C" int CRANE_CAT(crane_prefill_launch_d, CRANE_HEAD_SIZE)(CRANE_PREFILL_LAUNCHER_ARGS) {
+    return launch_prefill<CRANE_HEAD_SIZE>(q, out, k_pool, v_pool, cu_q, kv_len, block_table, max_blocks,
+                                           num_pages, page_size, n_entries, total_q_tiles, nq, nkv, window,
+                                           scale, err, st);
+}
+#else
+#define CRANE_PREFILL_HEAD_SIZES(X) X(16) X(32) X(48) X(64) X(80) X(96) X(112) X(128) X(160) X(192) X(256)
+#define DECLARE(DD) extern "C" int crane_prefill_launch_d##DD(CRANE_PREFILL_LAUNCHER_ARGS);
+CRANE_PREFILL_HEAD_SIZES(DECLARE)
+#undef DECLARE
+
 CRANE_API int crane_paged_prefill_attention_supports(int d, int nq, int nkv) {
     if (nkv <= 0 || nq % nkv != 0) return 0;
-    return d == 16 || d == 32 || d == 48 || d == 64 || d == 128;
+#define IS(DD) if (d == DD) return 1;
+    CRANE_PREFILL_HEAD_SIZES(IS)
+#undef IS
+    return 0;
 }
 
 // total_q_tiles: sum over the entries of ceil(q_len / 64).
@@ -232,14 +255,13 @@ CRANE_API int crane_paged_prefill_attention(const void* q, void* out, const void
                                             cudaStream_t st) {
     if (n_entries <= 0 || total_q_tiles <= 0) return 0;
     if (!crane_paged_prefill_attention_supports(d, nq, nkv)) return (int)cudaErrorInvalidValue;
-#define CASE(DD)                                                                                   \
-    case DD:                                                                                       \
-        return launch_prefill<DD>(q, out, k_pool, v_pool, cu_q, kv_len, block_table, max_blocks,    \
-                                  num_pages, page_size, n_entries, total_q_tiles, nq, nkv, window,  \
-                                  scale, err, st);
-    switch (d) {
-        CASE(16) CASE(32) CASE(48) CASE(64) CASE(128)
-    }
+#define CASE(DD)                                                                                      \
+    case DD:                                                                                          \
+        return crane_prefill_launch_d##DD(q, out, k_pool, v_pool, cu_q, kv_len, block_table, max_blocks, \
+                                          num_pages, page_size, n_entries, total_q_tiles, nq, nkv,      \
+                                          window, scale, err, st);
+    switch (d) { CRANE_PREFILL_HEAD_SIZES(CASE) }
 #undef CASE
     return (int)cudaErrorInvalidValue;
 }
+#endif  // CRANE_HEAD_SIZE

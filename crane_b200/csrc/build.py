@@ -23,9 +23,15 @@ from typing import Dict, List, Optional, Sequence
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
-KERNEL_SOURCES = ["elementwise.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "attention_simt.cu",
-                  "attention_decode.cu", "attention_prefill.cu", "attention_prefill_tc.cu",
-                  "sampling.cu"]
+# "file@NAME=VALUE": the file compiled once more with -DNAME=VALUE into an object of its own.  The
+# warp-level attention kernels are compiled per head size this way, side by side.
+ATTENTION_HEAD_SIZES = (16, 32, 48, 64, 80, 96, 112, 128, 160, 192, 256)
+KERNEL_SOURCES = (["elementwise.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "attention_simt.cu",
+                   "attention_decode.cu", "attention_prefill.cu", "attention_prefill_tc.cu",
+                   "sampling.cu"]
+                  # the slowest to compile first
+                  + [f"attention_decode.cu@CRANE_HEAD_SIZE={d}" for d in reversed(ATTENTION_HEAD_SIZES)]
+                  + [f"attention_prefill.cu@CRANE_HEAD_SIZE={d}" for d in reversed(ATTENTION_HEAD_SIZES)])
 HOST_SOURCES = ["host/cache_manager.cpp", "host/scheduler.cpp"]
 
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
@@ -86,7 +92,7 @@ def _digest(paths: Sequence[str], flags: Sequence[str]) -> str:
     host_headers = sorted(os.path.join("host", f) for f in os.listdir(os.path.join(HERE, "host"))
                           if f.endswith((".h", ".hpp")))
     for rel in list(paths) + headers + host_headers:
-        with open(os.path.join(HERE, rel), "rb") as f:
+        with open(os.path.join(HERE, rel.split("@")[0]), "rb") as f:
             h.update(rel.encode())
             h.update(f.read())
     return h.hexdigest()[:16]
@@ -123,14 +129,17 @@ def _build(lib: str, sources: Sequence[str], compiler: str, flags: Sequence[str]
     objs = []
 
     def one(rel: str) -> str:
-        obj = os.path.join(bdir, f"{lib}_{tag}_{os.path.basename(rel)}.o")
-        cmd = [compiler, *flags, "-I", HERE, "-c", os.path.join(HERE, rel), "-o", obj]
+        path, _, define = rel.partition("@")
+        obj = os.path.join(bdir, f"{lib}_{tag}_{os.path.basename(path)}{'_' + define.replace('=', '_') if define else ''}.o")
+        cmd = [compiler, *flags, "-I", HERE, "-c", os.path.join(HERE, path), "-o", obj]
+        if define:
+            cmd.insert(1, "-D" + define)
         if verbose_ptxas:
             cmd.insert(1, "-Xptxas=-v")
         _run(cmd, rel)
         _say(f"compiled {rel} ({time.time() - t0:.0f} s)")
         return obj
-    with ThreadPoolExecutor(max_workers=min(8, len(sources))) as pool:
+    with ThreadPoolExecutor(max_workers=min(os.cpu_count() or 8, 16, len(sources))) as pool:
         objs = list(pool.map(one, sources))
     tmp = so + f".tmp{os.getpid()}"
     _run([compiler, "-shared", "-o", tmp, *objs, *link_flags], lib)

@@ -52,11 +52,12 @@ def test_greedy_generation_float32_equals_plain(name, model_folders):
     assert m.runner.table.live() == 0
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D80", "D192"])
 def test_greedy_generation_bfloat16(name, model_folders):
     folder = model_folders(name, "bfloat16")
     pc, pw = ph.load_folder(folder)
-    m = load(folder, "bf16", page_size=16, num_pages=32, max_concurrent=4, max_batched_tokens=64)
+    m = load(folder, "bf16", page_size=tiny_configs.TINY[name]["page_size"] if name.startswith("D") else 16,
+             num_pages=32, max_concurrent=4, max_batched_tokens=64)
     prompt = np.random.default_rng(4).integers(0, pc.vocab_size, 12).tolist()
     got = m.generate(prompt, greedy_cfg(12, eos_token_id=-1))
     assert len(got) == 24 and got[:12] == prompt

@@ -469,7 +469,9 @@ def test_gemm_tcgen05_refuses_what_it_cannot_take(K, err):
 
 @pytest.mark.parametrize("d,nq,nkv,page_size,window,splits", [
     (128, 16, 4, 64, 0, 1), (128, 16, 4, 64, 0, 7), (64, 8, 8, 16, 0, 3), (16, 4, 2, 8, 0, 2),
-    (32, 8, 2, 16, 50, 4), (48, 6, 3, 32, 0, 32), (128, 32, 2, 128, 300, 5)])
+    (32, 8, 2, 16, 50, 4), (48, 6, 3, 32, 0, 32), (128, 32, 2, 128, 300, 5),
+    (80, 10, 5, 16, 0, 3), (96, 6, 2, 32, 0, 1), (112, 4, 4, 16, 90, 4), (160, 4, 2, 16, 0, 2),
+    (192, 6, 1, 32, 0, 5), (256, 8, 2, 64, 0, 6)])
 def test_paged_decode_attention(K, err, d, nq, nkv, page_size, window, splits):
     """Single tokens of requests of very different lengths, one of them with a
     far key that must dominate; every slicing of the keys gives the same."""
@@ -506,7 +508,9 @@ def test_paged_decode_attention(K, err, d, nq, nkv, page_size, window, splits):
 
 @pytest.mark.parametrize("d,nq,nkv,page_size,window", [(128, 8, 2, 64, 0), (64, 4, 4, 16, 0),
                                                         (16, 4, 2, 8, 0), (32, 4, 1, 16, 37),
-                                                        (48, 6, 3, 32, 0), (128, 4, 1, 128, 100)])
+                                                        (48, 6, 3, 32, 0), (128, 4, 1, 128, 100),
+                                                        (80, 10, 5, 16, 0), (96, 6, 2, 32, 41), (112, 4, 4, 16, 0),
+                                                        (160, 4, 2, 16, 0), (192, 6, 1, 32, 0), (256, 8, 2, 64, 70)])
 def test_paged_prefill_attention_mixed_batch(K, err, d, nq, nkv, page_size, window):
     """A portion that starts in the middle of a page after 105 cached positions, a
     single decoded token far into a long context, a whole prompt of 200, a
@@ -544,7 +548,9 @@ def test_paged_prefill_attention_mixed_batch(K, err, d, nq, nkv, page_size, wind
     (16, 4, 2, 8, 0, 2, True, 2), (32, 8, 2, 16, 50, 4, True, 0), (48, 6, 3, 32, 0, 32, False, 5),
     # head size 128, 2 to 8 slices: the slices merge in a thread-block cluster; 64: the most slices
     (128, 16, 4, 64, 0, 8, True, 6), (128, 8, 8, 32, 0, 2, False, 0), (128, 12, 4, 64, 100, 5, True, 0),
-    (128, 16, 4, 64, 0, 64, True, 0)])
+    (128, 16, 4, 64, 0, 64, True, 0),
+    (80, 10, 5, 16, 0, 3, True, 0), (96, 6, 2, 32, 0, 1, False, 4), (112, 8, 4, 16, 90, 4, True, 2),
+    (160, 4, 2, 16, 0, 2, True, 0), (192, 6, 1, 32, 0, 5, False, 0), (256, 8, 2, 64, 0, 6, True, 3)])
 def test_fused_decode_attention_equals_the_separate_kernels(K, err, d, nq, nkv, page_size, window,
                                                             splits, qk_norm, parts):
     """Rotary encoding, head norms, cache write, attention and merge in one

@@ -31,6 +31,17 @@ C = {
     "use_cla": True, "cla_share_factor": 2,
 }
 
+# head sizes between the powers of two: 80 (five 16-wide steps of the MMA), and 192
+D80 = {
+    "architectures": ["HunYuanDenseV1ForCausalLM"], "model_type": "hunyuan_v1_dense",
+    "vocab_size": 211, "hidden_size": 144, "intermediate_size": 272, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 80, "hidden_act": "silu",
+    "max_position_embeddings": 256, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+    "use_qk_norm": True, "tie_word_embeddings": True, "attention_bias": False,
+}
+D192 = dict(D80, head_dim=192, num_attention_heads=3, num_key_value_heads=1, use_qk_norm=False)
+
+
 def _layer_sizes(hidden, heads, kv_heads, inter, layers, tied, vocab=1000):
     """One or two layers with the layer sizes of a Hunyuan model (a small vocabulary keeps the
     folder small): the sizes at which the serving kernels' tensor-core paths are taken."""
@@ -52,6 +63,8 @@ TINY = {
     "A": {"config": A, "seed": 0, "std": 0.08, "norm_std": 0.05, "page_size": 64},
     "B": {"config": B, "seed": 1, "std": 0.08, "norm_std": 0.05, "page_size": 16},
     "C": {"config": C, "seed": 2, "std": 0.08, "norm_std": 0.05, "page_size": 32},
+    "D80": {"config": D80, "seed": 6, "std": 0.08, "norm_std": 0.05, "page_size": 16},
+    "D192": {"config": D192, "seed": 7, "std": 0.08, "norm_std": 0.05, "page_size": 32},
     "S18": {"config": S18, "seed": 3, "std": 0.02, "norm_std": 0.05, "page_size": 64},
     "S4": {"config": S4, "seed": 4, "std": 0.02, "norm_std": 0.05, "page_size": 16},
     "S7": {"config": S7, "seed": 5, "std": 0.015, "norm_std": 0.05, "page_size": 128},
