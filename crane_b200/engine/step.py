@@ -65,7 +65,10 @@ class StepContext:
     real_entries: int = 0
     graph_key: Optional[tuple] = None   # a step with prompt portions whose rows are padded to a
                                         # multiple of 64 so that a captured graph fits it; the
-                                        # padding rows have tok_entry -1 and belong to no entry
+                                        # padding rows have tok_entry -1 and belong to no entry,
+                                        # padding entries have no rows and no cached length, and
+                                        # the wanted rows beyond ``real_want`` repeat row 0
+    real_want: int = 0
 
 
 class _MetaBuffers:
@@ -240,12 +243,15 @@ class ModelRunner:
         pad_to = 0
         if (self._graphs_ok and max(counts) == 1 and all(len(e.want) == 1 for e in entries)):
             pad_to = self._bucket(n_entries)
-        # a small step with prompt portions: its rows are padded to a multiple of 64, and from the
-        # second step of the same (rows, entries, wanted) on a captured graph is replayed
+        # a small step with prompt portions: its rows are padded to a multiple of 64, its entries
+        # and wanted places to a power of two, and from the second step of the same (rows,
+        # entries, wanted) on a captured graph is replayed
         key = None
         if (not pad_to and self._graphs_ok and 0 < n_tokens <= self.cfg.graph_max_tokens):
             rows = min(-(-n_tokens // 64) * 64, self.cap_tokens)
-            shape = ("rows", rows, n_entries, sum(len(e.want) for e in entries))
+            wanted = sum(len(e.want) for e in entries)
+            shape = ("rows", rows, self._power_of_two(n_entries, self.cap_entries),
+                     self._power_of_two(wanted, rows) if wanted else 0)
             seen = self._shape_seen.get(shape, 0) + 1
             self._shape_seen[shape] = seen
             if seen >= 2:
@@ -274,12 +280,25 @@ class ModelRunner:
         cu = m.view("cu_q", n_entries + 1, False)
         kvl = m.view("kv_len", n_entries, False)
         slots = m.view("slots", n_entries, False)
+        if key is not None and key[2] > n_entries:
+            # entries without tokens and without a cache fill the shape up: no kernel has work for them
+            last = int(cu[n_entries])
+            cu = m.view("cu_q", key[2] + 1, False)
+            kvl = m.view("kv_len", key[2], False)
+            slots = m.view("slots", key[2], False)
+            cu[n_entries + 1:] = last
+            kvl[n_entries:] = 0
+            slots[n_entries:] = 0
+            n_entries = key[2]
         if pad_to:
             n_want = pad_to
             m.view("want_rows", n_want, False)[:] = np.arange(n_want, dtype=np.int32)
         else:
             want_rows = [int(cu[i]) + w for i, e in enumerate(entries) for w in e.want]
-            n_want = len(want_rows)
+            n_want = real_want = len(want_rows)
+            if key is not None and key[3] > n_want:
+                want_rows += [0] * (key[3] - n_want)        # more rows of logits than are wanted
+                n_want = key[3]
             if n_want:
                 m.view("want_rows", n_want, False)[:] = np.asarray(want_rows, dtype=np.int32)
         m.dev.copy_(m.host, non_blocking=True)
@@ -288,8 +307,10 @@ class ModelRunner:
         ctx = StepContext()
         ctx.graph_bucket, ctx.real_entries = pad_to, real_entries
         ctx.graph_key = key
+        ctx.real_want = n_want if key is None else real_want
         ctx.n_tokens, ctx.n_entries, ctx.n_want = n_tokens, n_entries, n_want
-        ctx.max_q_len = int(cnt.max())
+        # a padded step never counts as one of single tokens only: its filling entries have none
+        ctx.max_q_len = int(cnt.max()) if key is None else max(2, int(cnt.max()))
         ctx.max_kv_len = int(kvl.max())
         ctx.max_positions = self.max_seq_len
         ctx.deferred_tokens = self.deferred_tokens
@@ -315,7 +336,7 @@ class ModelRunner:
         if ctx.graph_bucket:
             return self._replay(ctx, ctx.graph_bucket)[:ctx.real_entries]
         if ctx.graph_key is not None:
-            return self._replay(ctx, ctx.graph_key)
+            return self._replay(ctx, ctx.graph_key)[:ctx.real_want]
         return self.model.forward(ctx, self.pools.layers)
 
     # ---- captured decode steps -----------------------------------------
@@ -326,6 +347,13 @@ class ModelRunner:
         return min(b, self.cap_entries) if b <= self.cap_entries else 0
 
     MAX_SHAPE_GRAPHS = 48       # graphs of small steps kept; the least recently used one goes first
+
+    @staticmethod
+    def _power_of_two(n: int, cap: int) -> int:
+        b = 1
+        while b < n:
+            b *= 2
+        return min(b, cap)
 
     def _replay(self, ctx: StepContext, key) -> torch.Tensor:
         if self._graph_generation != self.rt.ws.generation:

@@ -217,23 +217,24 @@ def test_small_steps_replay_graphs_with_the_same_logits(name, model_folders):
             assert r.step([StepEntry(i, p[:100], [])]).shape[0] == 0
             out.append(r.step([StepEntry(i, p[100:], [49])]).float().cpu())
             r.end(i)
-        for t in range(3):                                      # 4 single tokens beside a portion of 30
-            fresh = rng.integers(0, vocab, 30).tolist()
-            entries = [StepEntry(i, [int(rng.integers(0, vocab))], [0]) for i in range(4)]
+        for t, n_single in enumerate((4, 3, 2, 4)):             # single tokens beside a portion of 30:
+            fresh = rng.integers(0, vocab, 30).tolist()         # 5, 4, 3, 5 entries fill shapes of 8, 4, 4, 8
+            entries = [StepEntry(i, [int(rng.integers(0, vocab))], [0]) for i in range(n_single)]
             entries.append(StepEntry(10 + t, fresh, [29]))
             out.append(r.step(entries).float().cpu())
-        for t in range(3):                                      # all nine decode (the decode graphs)
-            ids = list(range(4)) + [4, 5] + [10, 11, 12]
+            assert out[-1].shape[0] == n_single + 1
+        for t in range(3):                                      # all ten decode (the decode graphs)
+            ids = list(range(4)) + [4, 5] + [10, 11, 12, 13]
             out.append(r.step([StepEntry(i, [int(rng.integers(0, vocab))], [0]) for i in ids]).float().cpu())
         r.rt.check_errors()
         runs[graphs] = (out, r.graph_replays)
-        for i in list(range(6)) + [10, 11, 12]:
+        for i in list(range(6)) + [10, 11, 12, 13]:
             r.end(i)
         r.table.check()
         rng = np.random.default_rng(3)
         prompts = [rng.integers(0, vocab, n).tolist() for n in (70, 100, 128, 65, 90, 101)]
     assert runs[0][1] == 3                                      # only the decode steps
-    assert runs[1024][1] == 3 + 5 + 2 + 4                       # prompts 2..6, mixed steps 2 and 3, 4 portions
+    assert runs[1024][1] == 3 + 5 + 2 + 4                       # prompts 2..6, mixed steps 3 and 4, 4 portions
     for a, b in zip(runs[0][0], runs[1024][0]):
         assert a.shape == b.shape
         assert (a - b).abs().max() <= 2e-3 * a.abs().max()
