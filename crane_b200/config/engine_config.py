@@ -49,7 +49,7 @@ class EngineConfig:
     chunk_size: int = 2048             # longest prompt portion of one request in a step
     workspace_rows: int = 0            # rows activations are first allocated for; 0: max_batched_tokens
     use_cuda_graphs: bool = True       # decode steps replay a captured graph (bfloat16 only)
-    graph_max_tokens: int = 1024       # steps with prompt portions replay graphs too, up to this many tokens (0: never)
+    graph_max_tokens: int = 2048       # steps with prompt portions replay graphs too, up to this many tokens (0: never)
     async_scheduling: bool = True      # plan and launch a step before the last one's tokens are read
     device: str = "cuda:0"
 

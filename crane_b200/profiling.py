@@ -84,8 +84,8 @@ def gemm(a):
     ws = [(torch.randn(a.n, a.k, device=DEV) / a.k ** 0.5).to(BF) for _ in range(a.sets)]
     state = {"i": 0}
     sms = torch.cuda.get_device_properties(0).multi_processor_count
-    if a.m <= 64:
-        bn = 16 if a.m <= 16 else 32 if a.m <= 32 else 64
+    if a.m <= 64 or a.swap:
+        bn = a.bn or (16 if a.m <= 16 else 32 if a.m <= 32 else 64 if a.m <= 64 else 128 if a.m <= 128 else 256)
         slices = a.slices or K.slices_for((a.n + 127) // 128, a.k, sms)
         out = torch.empty(slices, a.m, a.n, device=DEV) if slices > 1 else torch.empty(a.m, a.n, device=DEV, dtype=BF)
 
@@ -93,6 +93,14 @@ def gemm(a):
             w = ws[state["i"] % a.sets]; state["i"] += 1
             K.gemm_tcgen05(x, w, None, out, err, split_k=slices, swap=True, bn=bn)
         extra = {"mode": "swap-AB", "bn": bn, "slices": slices}
+    elif a.slices > 1:
+        bn = a.bn or 128
+        out = torch.empty(a.slices, a.m, a.n, device=DEV)
+
+        def fn():
+            w = ws[state["i"] % a.sets]; state["i"] += 1
+            K.gemm_tcgen05(x, w, None, out, err, split_k=a.slices, bn=bn)
+        extra = {"mode": "tiles in slices", "bn": bn, "slices": a.slices}
     else:
         bn = a.bn or (256 if a.n >= 2048 else 128)
         cols = a.n // 2 if a.silu_mul else a.n
@@ -186,6 +194,7 @@ def main(argv=None) -> int:
     g.add_argument("--k", type=int, required=True); g.add_argument("--bn", type=int, default=0)
     g.add_argument("--slices", type=int, default=0); g.add_argument("--sets", type=int, default=1)
     g.add_argument("--silu-mul", action="store_true")
+    g.add_argument("--swap", action="store_true", help="weights on the 128-row side also for more than 64 tokens")
     g.add_argument("--pair", action="store_true", help="many tokens: the kernel in which two SMs share a tile")
     for name in ("decode-attention", "prefill-attention"):
         p = sub.add_parser(name)

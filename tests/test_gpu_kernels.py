@@ -458,6 +458,25 @@ def test_gemm_tcgen05_few_tokens_swapped_and_split(K, err, M, bn, N, K_, split):
     assert int(err.item()) == 0
 
 
+@pytest.mark.parametrize("M,N,K_,slices", [(300, 384, 3072, 2), (512, 2048, 6144, 4), (1000, 260, 4608, 3)])
+def test_gemm_tcgen05_hundreds_of_tokens_in_wide_slices(K, err, M, N, K_, slices):
+    """A few hundred tokens, a long inner dimension: tiles of 128 features x 256
+    tokens (several tiles of tokens) over slices, and the norm that adds them up."""
+    from crane_b200.kernels import Partials
+    a = torch.randn(M, K_, device=DEV).bfloat16()
+    w = torch.randn(N, K_, device=DEV).bfloat16()
+    want = a.double() @ w.double().T
+    parts = torch.full((slices, M, N), 7.0, device=DEV)
+    K.gemm_tcgen05(a, w, None, parts, err, split_k=slices, swap=True, bn=256)
+    assert rel_err(parts.sum(0), want) < acc_tol(K_)
+    x = torch.zeros(M, N, device=DEV)
+    normed = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    K.add_rmsnorm(x, Partials(parts), torch.ones(N, device=DEV), 1e-6, normed)
+    assert rel_err(x, want) < 4e-3
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+
+
 def test_gemm_tcgen05_refuses_what_it_cannot_take(K, err):
     from crane_b200.kernels import KernelError
     a = torch.randn(4, 100, device=DEV).bfloat16()        # inner dimension not a multiple of 8
