@@ -29,6 +29,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, T* __restrict__ out,
     const int t = (int)(warp / nq), h = (int)(warp % nq);
     const int g = h / (nq / nkv);
     const int pos = positions[t];
+    if (tok_entry[t] < 0) return;                 // a row that pads the step: it attends to nothing
     const int* table = block_table + (long long)tok_entry[t] * max_blocks;
     const T* qp = q + ((long long)t * nq + h) * d;
     for (int c = lane; c < d; c += 32) q_s[wib][c] = to_f32(qp[c]);

@@ -52,7 +52,7 @@ def test_greedy_generation_float32_equals_plain(name, model_folders):
     assert m.runner.table.live() == 0
 
 
-@pytest.mark.parametrize("name", ["A", "B", "D80", "D192"])
+@pytest.mark.parametrize("name", ["A", "B", "D80", "D192", "D144"])
 def test_greedy_generation_bfloat16(name, model_folders):
     folder = model_folders(name, "bfloat16")
     pc, pw = ph.load_folder(folder)
@@ -191,7 +191,7 @@ def test_overlapped_steps_change_no_token(dtype, model_folders):
     assert runs[False] == runs[True]
 
 
-@pytest.mark.parametrize("name", ["B", "C", "S18"])
+@pytest.mark.parametrize("name", ["B", "C", "S18", "D144"])
 def test_small_steps_replay_graphs_with_the_same_logits(name, model_folders):
     """Steps with prompt portions of up to graph_max_tokens tokens are padded to
     a multiple of 64 rows and, from the second step of a shape on, replay a

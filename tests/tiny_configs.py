@@ -40,6 +40,8 @@ D80 = {
     "use_qk_norm": True, "tie_word_embeddings": True, "attention_bias": False,
 }
 D192 = dict(D80, head_dim=192, num_attention_heads=3, num_key_value_heads=1, use_qk_norm=False)
+# a head size for which no tensor-core attention is built: the bfloat16 path takes the plain kernel
+D144 = dict(D80, head_dim=144, num_attention_heads=2, num_key_value_heads=1)
 
 
 def _layer_sizes(hidden, heads, kv_heads, inter, layers, tied, vocab=1000):
@@ -65,6 +67,7 @@ TINY = {
     "C": {"config": C, "seed": 2, "std": 0.08, "norm_std": 0.05, "page_size": 32},
     "D80": {"config": D80, "seed": 6, "std": 0.08, "norm_std": 0.05, "page_size": 16},
     "D192": {"config": D192, "seed": 7, "std": 0.08, "norm_std": 0.05, "page_size": 32},
+    "D144": {"config": D144, "seed": 8, "std": 0.08, "norm_std": 0.05, "page_size": 16},
     "S18": {"config": S18, "seed": 3, "std": 0.02, "norm_std": 0.05, "page_size": 64},
     "S4": {"config": S4, "seed": 4, "std": 0.02, "norm_std": 0.05, "page_size": 16},
     "S7": {"config": S7, "seed": 5, "std": 0.015, "norm_std": 0.05, "page_size": 128},
