@@ -344,13 +344,21 @@ __global__ void rope_norm_cache_kernel(GemmOut<T> qkv, int qkv_stride,
                                        int n_tokens, int nq, int nkv, int d, int has_kv,
                                        int rotary, int* err) {
     pdl_launch_dependents();
-    pdl_wait();
     const int heads = nq + (has_kv ? 2 * nkv : 0);
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
-    if (warp >= n_tokens * heads) return;
-    const int t = warp / heads, h = warp % heads;
+    const bool in = warp < n_tokens * heads;
+    const int t = in ? warp / heads : 0, h = in ? warp % heads : 0;
+    // the step's positions and block tables were written before the step began: they are looked up
+    // before the wait for the product that makes q, k and v
     const int pos = positions[t];
+    int e = -1, page = -1;
+    if (in && h >= nq) {
+        e = tok_entry[t];
+        if (e >= 0) page = block_table[(long long)e * max_blocks + pos / page_size];
+    }
+    pdl_wait();
+    if (!in) return;
     const int half = d >> 1;
     const long long src = (long long)t * qkv_stride + (long long)h * d;   // q,k,v are consecutive
 
@@ -361,9 +369,7 @@ __global__ void rope_norm_cache_kernel(GemmOut<T> qkv, int qkv_stride,
         dst = q_out + ((long long)t * nq + h) * d;
         nw = q_norm_w;
     } else {
-        const int e = tok_entry[t];
         if (e < 0) return;                         // a row that pads the step: it has no place in a cache
-        const int page = block_table[(long long)e * max_blocks + pos / page_size];
         if (page < 0 || page >= num_pages) {
             if (lane == 0) atomicOr(err, CRANE_ERR_PAGE_RANGE);
             return;
@@ -490,7 +496,9 @@ __global__ void rope_norm_cache_d128_kernel(const __nv_bfloat16* __restrict__ qk
                                             int rotary, int* err) {
     constexpr int D = 128, HALF = 64;
     pdl_launch_dependents();
-    pdl_wait();
+    // Positions, block tables, the cosine and sine tables and the norm weights were written before
+    // the step began: they are fetched before the wait for the product that makes q, k and v, so
+    // that after it only the rows themselves are on the way.
     const int heads = nq + (has_kv ? 2 * nkv : 0);
     const long long item = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;
     const int sub = threadIdx.x & 7;                         // which eighth of a half
@@ -524,6 +532,24 @@ __global__ void rope_norm_cache_d128_kernel(const __nv_bfloat16* __restrict__ qk
         if (sub == 0) atomicOr(err, CRANE_ERR_POSITION_RANGE);
         rotate = false;
     }
+    float c[8], sn[8], wa[8], wb[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) c[i] = sn[i] = wa[i] = wb[i] = 0.f;
+    if (live && rotate) {
+        const float4* c4 = (const float4*)(cos_tab + (long long)pos * HALF + 8 * sub);
+        const float4* s4 = (const float4*)(sin_tab + (long long)pos * HALF + 8 * sub);
+        const float4 c0 = c4[0], c1 = c4[1], s0 = s4[0], s1 = s4[1];
+        c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w; c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
+        sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+    }
+    if (nw != nullptr) {
+        const float4* w4 = (const float4*)(nw + 8 * sub);
+        const float4* v4 = (const float4*)(nw + HALF + 8 * sub);
+        const float4 w0 = w4[0], w1 = w4[1], v0 = v4[0], v1 = v4[1];
+        wa[0] = w0.x; wa[1] = w0.y; wa[2] = w0.z; wa[3] = w0.w; wa[4] = w1.x; wa[5] = w1.y; wa[6] = w1.z; wa[7] = w1.w;
+        wb[0] = v0.x; wb[1] = v0.y; wb[2] = v0.z; wb[3] = v0.w; wb[4] = v1.x; wb[5] = v1.y; wb[6] = v1.z; wb[7] = v1.w;
+    }
+    pdl_wait();
     float a[8], b[8];
     {
         uint4 ra = make_uint4(0, 0, 0, 0), rb = ra;
@@ -541,11 +567,6 @@ __global__ void rope_norm_cache_d128_kernel(const __nv_bfloat16* __restrict__ qk
         }
     }
     if (live && rotate) {
-        const float4* c4 = (const float4*)(cos_tab + (long long)pos * HALF + 8 * sub);
-        const float4* s4 = (const float4*)(sin_tab + (long long)pos * HALF + 8 * sub);
-        const float4 c0 = c4[0], c1 = c4[1], s0 = s4[0], s1 = s4[1];
-        const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-        const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const float x1 = a[i], x2 = b[i];
@@ -563,11 +584,6 @@ __global__ void rope_norm_cache_d128_kernel(const __nv_bfloat16* __restrict__ qk
         ss += __shfl_xor_sync(0xffffffffu, ss, 4);
         if (nw != nullptr) {
             const float rstd = rsqrtf(ss / (float)D + eps);
-            const float4* w4 = (const float4*)(nw + 8 * sub);
-            const float4* v4 = (const float4*)(nw + HALF + 8 * sub);
-            const float4 w0 = w4[0], w1 = w4[1], v0 = v4[0], v1 = v4[1];
-            const float wa[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-            const float wb[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 a[i] = a[i] * rstd * wa[i];
