@@ -69,6 +69,7 @@ class StepContext:
                                         # padding entries have no rows and no cached length, and
                                         # the wanted rows beyond ``real_want`` repeat row 0
     real_want: int = 0
+    replay: bool = False        # a step with a graph_key: replay its graph (else launch its kernels)
 
 
 class _MetaBuffers:
@@ -142,6 +143,8 @@ class ModelRunner:
         self._graphs_ok = (self.cfg.use_cuda_graphs and not self.rt.exact
                            and all(n.kind != "state" for n in self.model.cache_needs()))
         self.graph_replays = 0
+        self._step_done = torch.cuda.Event()       # recorded behind every step's kernels
+        self._step_done.record()
 
     # ---- cache geometry -------------------------------------------------
     def _build_cache(self) -> None:
@@ -247,7 +250,11 @@ class ModelRunner:
         # and wanted places to a power of two, and from the second step of the same (rows,
         # entries, wanted) on a captured graph is replayed
         key = None
-        if (not pad_to and self._graphs_ok and 0 < n_tokens <= self.cfg.graph_max_tokens):
+        # (a prompt portion alone or beside one other entry has few shapes, so all of them up to
+        # graph_max_tokens are worth a graph; mixes of many entries come in many shapes, and only the
+        # small ones, which the host could not launch as fast as the device runs them, get one)
+        limit = self.cfg.graph_max_tokens if n_entries <= 2 else self.cfg.graph_max_tokens // 4
+        if (not pad_to and self._graphs_ok and 0 < n_tokens <= limit):
             rows = min(-(-n_tokens // 64) * 64, self.cap_tokens)
             wanted = sum(len(e.want) for e in entries)
             shape = ("rows", rows, self._power_of_two(n_entries, self.cap_entries),
@@ -307,6 +314,12 @@ class ModelRunner:
         ctx = StepContext()
         ctx.graph_bucket, ctx.real_entries = pad_to, real_entries
         ctx.graph_key = key
+        # While the device still runs the step before, the host launches this step's kernels
+        # behind it at no cost, and launched one by one they ran a little faster than replayed
+        # (a serving mix: 5 % per step): a graph pays when the device waits for the host.  The
+        # step is padded to its shape either way, so that both ways run the same kernels on the
+        # same rows and give the same bits.
+        ctx.replay = key is not None and self._step_done.query()
         ctx.real_want = n_want if key is None else real_want
         ctx.n_tokens, ctx.n_entries, ctx.n_want = n_tokens, n_entries, n_want
         # a padded step never counts as one of single tokens only: its filling entries have none
@@ -333,11 +346,14 @@ class ModelRunner:
         entries and of their ``want``."""
         ctx = self.prepare(entries, reserved)
         self.steps += 1
-        if ctx.graph_bucket:
-            return self._replay(ctx, ctx.graph_bucket)[:ctx.real_entries]
-        if ctx.graph_key is not None:
-            return self._replay(ctx, ctx.graph_key)[:ctx.real_want]
-        return self.model.forward(ctx, self.pools.layers)
+        try:
+            if ctx.graph_bucket:
+                return self._replay(ctx, ctx.graph_bucket)[:ctx.real_entries]
+            if ctx.graph_key is not None and ctx.replay:
+                return self._replay(ctx, ctx.graph_key)[:ctx.real_want]
+            return self.model.forward(ctx, self.pools.layers)[:ctx.real_want]
+        finally:
+            self._step_done.record()
 
     # ---- captured decode steps -----------------------------------------
     def _bucket(self, n: int) -> int:
@@ -346,7 +362,7 @@ class ModelRunner:
             b *= 2
         return min(b, self.cap_entries) if b <= self.cap_entries else 0
 
-    MAX_SHAPE_GRAPHS = 48       # graphs of small steps kept; the least recently used one goes first
+    MAX_SHAPE_GRAPHS = 256      # graphs of small steps kept; the least recently used one goes first
 
     @staticmethod
     def _power_of_two(n: int, cap: int) -> int:

@@ -198,7 +198,9 @@ def test_small_steps_replay_graphs_with_the_same_logits(name, model_folders):
     captured graph: prompts of different lengths under one shape, then a
     portion beside decoded tokens, then decoding, give the logits of an engine
     that launches every step kernel by kernel; the padding rows write nothing
-    into the cache (the decoded tokens that follow read it)."""
+    into the cache (the decoded tokens that follow read it).  Every step here
+    finds the device idle (its results are read each time): only then does a
+    step take a graph."""
     from crane_b200.engine import StepEntry
     folder = model_folders(name, "bfloat16")
     rng = np.random.default_rng(3)
@@ -215,6 +217,7 @@ def test_small_steps_replay_graphs_with_the_same_logits(name, model_folders):
         for i in (20, 21, 22):                                  # portions of which nothing is wanted
             p = rng.integers(0, vocab, 150).tolist()
             assert r.step([StepEntry(i, p[:100], [])]).shape[0] == 0
+            torch.cuda.synchronize()                            # a graph is taken only while the device idles
             out.append(r.step([StepEntry(i, p[100:], [49])]).float().cpu())
             r.end(i)
         for t, n_single in enumerate((4, 3, 2, 4)):             # single tokens beside a portion of 30:
