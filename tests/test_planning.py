@@ -1,0 +1,68 @@
+"""The host-side choices of shapes: how many key slices a decode step's attention takes, how many
+slices and which tile widths the products take, how many query tiles a step has.  Pure
+arithmetic, no device."""
+import numpy as np
+import pytest
+
+from crane_b200.kernels import Kernels
+from crane_b200.parts.base import query_tiles
+
+SMS = 148
+
+
+@pytest.mark.parametrize("nkv", [1, 2, 4, 8, 32])
+def test_decode_splits_fill_the_device_and_fit_the_scratch(nkv):
+    for entries in range(1, 300):
+        s = Kernels.decode_splits(entries, nkv, SMS)
+        assert 1 <= s <= 64
+        if s > 1:
+            # never more CTAs than two per SM, which is also what the slices' scratch is sized for
+            assert entries * nkv * s <= 2 * SMS
+        assert not 8 < s <= 11 and not 32 < s <= 40      # ranges that measured slower than 8 / 32
+    assert Kernels.decode_splits(8, 4, SMS) == 8           # the headline shape: one cluster per (request, kv head)
+    assert Kernels.decode_splits(1, 4, SMS) == 64
+    assert Kernels.decode_splits(64, 4, SMS) == 1
+    assert Kernels.decode_splits(1, 4, SMS, cap=16) == 16
+
+
+def test_slices_for_fills_the_last_wave():
+    for tiles in (1, 3, 16, 24, 96, 148, 200, 944):
+        for k in (64, 256, 2048, 6144):
+            s = Kernels.slices_for(tiles, k, SMS)
+            assert 1 <= s <= max(1, (k + 63) // 64)
+            assert tiles * s <= max(tiles, 3 * SMS)
+    assert Kernels.slices_for(944, 2048, SMS) == 1         # the head: tiles enough without slices
+    assert Kernels.slices_for(16, 6144, SMS) == 9          # 144 CTAs for 148 SMs
+    assert Kernels.split_plan(2048, 6) == (5, 6)
+    assert Kernels.split_plan(64, 6) == (1, 1)
+
+
+def test_tile_widths():
+    for m in (65, 128, 300, 2048, 8192):
+        for n in (256, 2048, 3072, 12288):
+            assert Kernels.tile_width_for(m, n, SMS) in Kernels.WIDE_TILES
+            p = Kernels.pair_width_for(m, n, 2048, SMS)
+            assert p == 0 or p in Kernels.PAIR_TILES
+    assert Kernels.pair_width_for(255, 12288, 2048, SMS) == 0          # fewer than 256 rows
+    assert Kernels.pair_width_for(2048, 2048, 2048, SMS) == 0          # a small product
+    assert Kernels.pair_width_for(2048, 12288, 2048, SMS) > 0
+    assert Kernels.tile_width_for(2048, 3072, SMS) == 192              # 256 tiles: two rounds, the narrowest that does it
+
+
+class _Ctx:
+    pass
+
+
+def test_query_tiles_exact_and_bound():
+    c = _Ctx()
+    c.n_entries, c.n_tokens, c.graph_key = 3, 300, None
+    c.h_cu_q = np.array([0, 1, 130, 300], dtype=np.int32)
+    assert query_tiles(c, 128) == 1 + 2 + 2
+    assert query_tiles(c, 64) == 1 + 3 + 3
+    # a step that replays a graph: the most tiles any step of its shape can have
+    c.graph_key = ("rows", 320, 4, 4)
+    c.n_entries, c.n_tokens = 4, 320
+    assert query_tiles(c, 128) == 4 + 2
+    for lens in ([320, 0, 0, 0], [1, 1, 1, 317], [127, 129, 63, 1], [80, 80, 80, 80]):
+        exact = sum(-(-q // 128) for q in lens)
+        assert exact <= query_tiles(c, 128)
