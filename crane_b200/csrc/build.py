@@ -108,10 +108,12 @@ def _run(cmd: List[str], what: str) -> None:
             out.append(line)
     th = threading.Thread(target=pump, daemon=True)
     th.start()
-    while proc.poll() is None:
-        th.join(timeout=10.0)
-        if proc.poll() is None:
-            _say(f"still compiling {what} ({time.time() - t0:.0f} s)")
+    while True:
+        try:
+            proc.wait(timeout=10.0)
+            break
+        except subprocess.TimeoutExpired:
+            _say(f"still compiling {what} ({time.time() - t0:.0f} s)")     # a line now and then
     th.join()
     if proc.returncode != 0:
         raise BuildError(f"compiling {what} failed:\n$ {' '.join(cmd)}\n{''.join(out)}")
