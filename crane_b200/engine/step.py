@@ -140,7 +140,7 @@ class ModelRunner:
         self._graphs: Dict[object, tuple] = {}
         self._shape_seen: Dict[tuple, int] = {}      # how often a shape of small step has come
         self._graph_generation = -1
-        self._graphs_ok = (self.cfg.use_cuda_graphs and not self.rt.exact
+        self._graphs_ok = (self.cfg.use_cuda_graphs and not self.rt.exact and self.model.capturable()
                            and all(n.kind != "state" for n in self.model.cache_needs()))
         self.graph_replays = 0
         self._step_done = torch.cuda.Event()       # recorded behind every step's kernels
@@ -386,15 +386,23 @@ class ModelRunner:
         if entry is None:
             # once eagerly, so that every buffer exists; then the same step again under capture
             # (it rewrites the same cache rows with the same values)
-            self.model.forward(ctx, self.pools.layers)
+            eager = self.model.forward(ctx, self.pools.layers)
             if self._graph_generation != self.rt.ws.generation:
                 self._graphs.clear()
                 self._graph_generation = self.rt.ws.generation
             before = self.rt.launches
             torch.cuda.synchronize(self.rt.device)
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                logits = self.model.forward(ctx, self.pools.layers)
+            try:
+                with torch.cuda.graph(graph):
+                    logits = self.model.forward(ctx, self.pools.layers)
+            except Exception as exc:
+                # the step itself has run (kernel by kernel, above); what is lost is the process's
+                # further use of captures, which an aborted one leaves in an undefined state
+                raise RuntimeError(
+                    "a step could not be recorded as a CUDA graph; a part that reads results on the "
+                    "host in its forward must set `capturable = False` (or run the engine with "
+                    "use_cuda_graphs=False)") from exc
             entry = (graph, logits, self.rt.launches - before)
         self._graphs[key] = entry                   # (back) at the end: the most recently used
         graph, logits, launches = entry

@@ -97,6 +97,11 @@ class LayerCache:
 
 class Part:
     kind = "part"
+    # Whether the part's forward can be recorded in a CUDA graph: it launches kernels and tensor
+    # operations only and reads nothing of their results on the host.  A part that does read
+    # (``.item()``, ``.cpu()``, ``nonzero()``, a data-dependent Python branch) sets this to False;
+    # the engine then launches every step of the model kernel by kernel.
+    capturable = True
 
     def __init__(self, spec: PartSpec):
         self.spec = spec

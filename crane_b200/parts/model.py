@@ -65,6 +65,13 @@ class DecoderModel:
         return [self.blocks[s.layer].mixer.cache_need() if s.cache_of is None else CacheNeed("none")
                 for s in self.spec.schedule]
 
+    def capturable(self) -> bool:
+        """Whether every part says that its forward can be recorded in a CUDA graph."""
+        parts = [self.embed, self.final_norm, self.head]
+        for b in self.blocks:
+            parts += list(b.parts())
+        return all(getattr(p, "capturable", True) for p in parts)
+
     def forward(self, ctx, caches: List[LayerCache]) -> torch.Tensor:
         """Runs the step's tokens through the schedule (``caches``: one entry
         per step of the schedule) and returns float logits

@@ -22,6 +22,7 @@ def register_toys():
     class Routed(Part):
         """y = scale * gelu(h W1[e]^T) W2[e]^T with e = argmax of the float router logits."""
         kind = "ffn"
+        capturable = False          # it reads its routing on the host: no CUDA graph can hold that
 
         @classmethod
         def manifest(cls, spec):
@@ -156,6 +157,16 @@ def test_toy_model_in_bfloat16_follows_the_float_one():
         pytest.fail("no prompt with wide routing margins among 40")
     got = r16.step([StepEntry(1, tokens, list(range(30)))]).cpu()
     assert rel_err(got, want) < 3e-2
+    # The toy feed-forward reads its routing on the host and says so (capturable = False): steps of
+    # the same shape, which the engine would otherwise capture and replay, are launched kernel by
+    # kernel every time and give the same bits.
+    r16.end(1)
+    again = r16.step([StepEntry(2, tokens, list(range(30)))]).cpu()
+    assert torch.equal(again, got)
+    r16.end(2)
+    third = r16.step([StepEntry(3, tokens, list(range(30)))]).cpu()
+    assert torch.equal(third, got) and r16.graph_replays == 0
+    r16.rt.check_errors()
 
 
 def test_toy_routed_feed_forward_alone():
