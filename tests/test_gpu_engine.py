@@ -162,6 +162,41 @@ def test_sampling_with_a_seed_is_reproducible(model_folders):
     assert len(rep) == 17
 
 
+@pytest.mark.parametrize("opts", [dict(temperature=0.8, top_k=12), dict(temperature=1.2, top_p=0.85),
+                                  dict(temperature=0.9, top_k=20, top_p=0.9, repetition_penalty=1.3, repeat_last_n=8),
+                                  dict(temperature=None, repetition_penalty=1.7, repeat_last_n=5)])
+def test_sampling_options_through_the_engine_follow_the_plain_rules(opts, model_folders):
+    """Every token that ``generate`` returns is the one the plain rules pick from
+    the plain logits of its prefix: the repetition penalty over the last
+    ``repeat_last_n`` tokens of prompt ++ generated, the top-k / top-p set, and
+    the request's own random stream keyed by seed and the count of tokens it has
+    sampled before."""
+    from crane_b200.generation import GenerationConfig
+    folder = model_folders("B", "float32")
+    pc, pw = ph.load_folder(folder)
+    m = load(folder, "fp32", page_size=16, num_pages=32, max_concurrent=3, max_batched_tokens=128)
+    prompt = [7, 7, 7, 300, 12, 5, 7, 19, 300, 2, 44]
+    n_new, seed = 14, 77
+    got = m.generate(prompt, GenerationConfig(max_new_tokens=n_new, eos_token_id=-1, seed=seed, **opts))
+    assert got[:len(prompt)] == prompt and len(got) == len(prompt) + n_new
+    logits = ph.logits_all(pc, pw, got[:-1])
+    temp = opts.get("temperature")
+    for i in range(len(prompt), len(got)):
+        row = logits[i - 1]
+        pen = opts.get("repetition_penalty", 1.0)
+        if pen != 1.0:
+            row = ph.apply_repetition_penalty(row, pen, got[max(0, i - opts["repeat_last_n"]):i])
+        if temp is None:
+            assert row[got[i]] >= row.max() - 1e-4 * np.abs(row).max(), (i, got[i], int(row.argmax()))
+            continue
+        top_p = opts.get("top_p", 1.0)
+        top_k = opts.get("top_k", 0) or (64 if top_p < 1.0 else 0)       # top-p works inside the best 64
+        keep = ph.top_k_top_p_keep(row, temp, top_k, top_p)
+        assert got[i] in set(int(j) for j in keep), (i, got[i], keep[:8])
+        score = ph.gumbel_scores(row, temp, ph.uniform_noise(seed, i - len(prompt), pc.vocab_size))
+        assert score[got[i]] >= score[keep].max() - 1e-3, (i, got[i], int(keep[np.argmax(score[keep])]))
+
+
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
 def test_overlapped_steps_change_no_token(dtype, model_folders):
     """The engine that launches a step before it has read the last one's tokens
@@ -189,6 +224,60 @@ def test_overlapped_steps_change_no_token(dtype, model_folders):
         assert m.runner.table.free_pages() == 12
         assert not m.engine.has_work()
     assert runs[False] == runs[True]
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_overlapped_steps_on_a_lagging_device_change_no_token(dtype, model_folders):
+    """The same comparison while the device is far behind the host, as it is at
+    real model sizes: every forward pass of the model is preceded on the stream
+    by tens of milliseconds of ordinary finite work (large products), so that a
+    step's sampler runs long after the host has planned and launched the step
+    after it.  Rows carry their own temperature, top-k, top-p and seed; requests end
+    at different times and one is added late, so the rows of the batch shift.
+    Whatever the host stages for a step's sampler must still be that step's
+    when the device gets to it."""
+    from crane_b200.engine import LLMEngine, ModelRunner
+    from crane_b200.config import EngineConfig
+    from crane_b200.sampling import SamplingParams
+    folder = model_folders("B", "float32" if dtype == "fp32" else "bfloat16")
+    rng = np.random.default_rng(21)
+    prompts = [rng.integers(0, 300, n).tolist() for n in (9, 14, 3, 11, 6)]
+    options = [(dict(temperature=0.7, seed=11), 5), (dict(temperature=None), 14),
+               (dict(temperature=1.3, top_k=20, seed=12), 9), (dict(temperature=0.9, top_p=0.8, seed=13), 14),
+               (dict(temperature=1.1, seed=14), 8)]
+    a = torch.randn(4096, 4096, device="cuda:0")
+    w = torch.randn(4096, 4096, device="cuda:0")
+    c = torch.empty(4096, 4096, device="cuda:0")
+    runs = {}
+    for overlap in (False, True):
+        runner = ModelRunner(folder, EngineConfig(dtype=dtype, page_size=16, num_pages=32, max_concurrent=4,
+                                                  max_batched_tokens=64, chunk_size=32,
+                                                  async_scheduling=overlap))
+        eng = LLMEngine(runner)
+        forward = runner.model.forward
+
+        def slow_forward(ctx, layers, forward=forward, runner=runner):
+            for _ in range(3):                               # behind the step's metadata, before its sampler
+                runner.rt.kernels.gemm_simt(a, w, None, c)
+            return forward(ctx, layers)
+        runner.model.forward = slow_forward
+        ids = [eng.add_request(p, SamplingParams(**o), n, [-1]) for p, (o, n) in zip(prompts[:4], options[:4])]
+        steps = behind = 0
+        while eng.has_work():
+            if steps == 6:
+                ids.append(eng.add_request(prompts[4], SamplingParams(**options[4][0]), options[4][1], [-1]))
+            eng.step()
+            steps += 1
+            if eng._inflight is not None and not eng._inflight.event.query():
+                behind += 1
+        runner.rt.check_errors()
+        runs[overlap] = [eng.finished[i].tokens for i in ids]
+        if overlap:
+            assert behind >= steps // 2, (behind, steps)      # the device did lag behind the host
+        runner.table.check()
+    assert runs[False] == runs[True]
+    for toks, p, (o, n) in zip(runs[True], prompts, options):
+        assert len(toks) == len(p) + n
 
 
 @pytest.mark.parametrize("name", ["B", "C", "S18", "D144"])
