@@ -51,6 +51,8 @@ class EngineConfig:
     use_cuda_graphs: bool = True       # decode steps replay a captured graph (bfloat16 only)
     graph_max_tokens: int = 2048       # steps with prompt portions replay graphs too, up to this many tokens (0: never)
     async_scheduling: bool = True      # plan and launch a step before the last one's tokens are read
+    mixed_decode_min_keys: int = 2048  # decoded tokens beside prompt portions take the split-KV decode
+                                       # kernel when together they read at least this many cached keys
     device: str = "cuda:0"
 
     def __post_init__(self) -> None:

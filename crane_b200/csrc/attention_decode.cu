@@ -246,6 +246,9 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_rep = nq / nkv;
     const int t = cu_q[e];
+    // an entry with a prompt portion (or a padding entry without rows) is another kernel's: all
+    // CTAs of the entry, which are all CTAs of its cluster, leave here
+    if (cu_q[e + 1] - t != 1) return;
     const int pos = kv_len[e] - 1;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int* table = block_table + (long long)e * max_blocks;
@@ -559,6 +562,9 @@ paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_rep = nq / nkv;
     const int t = cu_q[e];
+    // an entry with a prompt portion (or a padding entry without rows) is another kernel's: all
+    // CTAs of the entry, which are all CTAs of its cluster, leave here
+    if (cu_q[e + 1] - t != 1) return;
     const int pos = kv_len[e] - 1;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int* table = block_table + (long long)e * max_blocks;
@@ -989,6 +995,7 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
     const int e = blockIdx.x, h = blockIdx.y;
     const long long base = ((long long)e * nq + h) * n_splits;
     const int t = cu_q[e];
+    if (cu_q[e + 1] - t != 1) return;
     if (n_splits <= 64) {
         // all loads of a thread go out together; 16 slices' worth of registers when that is enough
         if (n_splits <= 16) merge_column<16>(part_o, part_ml, out, base, t, nq, h, d, n_splits);
@@ -1209,7 +1216,9 @@ CRANE_API int crane_paged_decode_attention_supports(int d, int nq, int nkv) {
     return 0;
 }
 
-// One token per entry (row cu_q[e] of q and out).  part_o needs
+// The entries with exactly one token (row cu_q[e] of q and out); entries with
+// more or no rows are skipped, so that a step's prompt portions can go to the
+// prefill kernel and its decoded tokens here.  part_o needs
 // n_entries * nq * n_splits * d floats and part_ml n_entries * nq * n_splits * 2
 // when n_splits > 1.
 CRANE_API int crane_paged_decode_attention(const void* q, void* out, float* part_o, float* part_ml,
@@ -1291,7 +1300,7 @@ CRANE_API const char* crane_noalloc_strerror(int code) {
                    "entries per call, or the entry point that takes the caller's scratch buffers";
         case CRANE_NOALLOC_BAD_ARGUMENT:
             return "an argument is out of range (head size or head grouping without a kernel, "
-                   "n_splits < 1, or a device ordinal beyond 63)";
+                   "n_splits outside 1..64, or a device ordinal beyond 63)";
         case CRANE_NOALLOC_NO_SYMBOL:
             return "the device address of the built-in scratch array could not be found";
     }
@@ -1306,7 +1315,7 @@ CRANE_API int crane_paged_decode_attention_noalloc(const void* q, void* out, con
                                                    float scale, int n_splits, int* err,
                                                    cudaStream_t stream) {
     if (n_entries <= 0) return 0;
-    if (!crane_paged_decode_attention_supports(d, nq, nkv) || n_splits < 1)
+    if (!crane_paged_decode_attention_supports(d, nq, nkv) || n_splits < 1 || n_splits > 64)
         return CRANE_NOALLOC_BAD_ARGUMENT;
     float* part_o = nullptr;
     float* part_ml = nullptr;

@@ -28,7 +28,7 @@ paged_prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __
                           const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ cu_q,
                           const int* __restrict__ kv_len, const int* __restrict__ block_table,
                           int max_blocks, int num_pages, int page_size, int n_entries, int nq, int nkv,
-                          int window, float scale_log2, int* err) {
+                          int window, float scale_log2, int skip_single, int* err) {
     constexpr int RB = Tile<D>::ROW_BYTES;
     constexpr int TILE_BYTES = BKV * RB;
     constexpr int KS = D / 16, DN = D / 8;
@@ -38,7 +38,9 @@ paged_prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __
     // read the most keys) come first, so that the long CTAs start early
     int e = 0, tile = blockIdx.x;
     for (; e < n_entries; ++e) {
-        const int tiles = (cu_q[e + 1] - cu_q[e] + BQ - 1) / BQ;
+        const int rows = cu_q[e + 1] - cu_q[e];
+        // skip_single: entries of one token have no tile here (the decode kernel takes them)
+        const int tiles = (skip_single && rows == 1) ? 0 : (rows + BQ - 1) / BQ;
         if (tile < tiles) {
             tile = tiles - 1 - tile;
             break;
@@ -200,7 +202,7 @@ template <int D>
 int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_pool, const int* cu_q,
                    const int* kv_len, const int* block_table, int max_blocks, int num_pages,
                    int page_size, int n_entries, int total_q_tiles, int nq, int nkv, int window,
-                   float scale, int* err, cudaStream_t st) {
+                   float scale, int skip_single, int* err, cudaStream_t st) {
     constexpr int smem = 4 * BKV * Tile<D>::ROW_BYTES;
     auto kern = paged_prefill_attn_kernel<D>;
     static bool configured = false;
@@ -213,7 +215,7 @@ int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_p
     kern<<<grid, THREADS, smem, st>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out,
                                       (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, cu_q,
                                       kv_len, block_table, max_blocks, num_pages, page_size, n_entries,
-                                      nq, nkv, window, scale * 1.4426950408889634f, err);
+                                      nq, nkv, window, scale * 1.4426950408889634f, skip_single, err);
     return crane_launch_status();
 }
 }  // namespace
@@ -225,12 +227,13 @@ int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_p
 #define CRANE_PREFILL_LAUNCHER_ARGS                                                                    \
     const void *q, void *out, const void *k_pool, const void *v_pool, const int *cu_q, const int *kv_len, \
         const int *block_table, int max_blocks, int num_pages, int page_size, int n_entries,            \
-        int total_q_tiles, int nq, int nkv, int window, float scale, int *err, cudaStream_t st
+        int total_q_tiles, int nq, int nkv, int window, float scale, int skip_single, int *err,         \
+        cudaStream_t st
 #ifdef CRANE_HEAD_SIZE
 extern "C" int CRANE_CAT(crane_prefill_launch_d, CRANE_HEAD_SIZE)(CRANE_PREFILL_LAUNCHER_ARGS) {
     return launch_prefill<CRANE_HEAD_SIZE>(q, out, k_pool, v_pool, cu_q, kv_len, block_table, max_blocks,
                                            num_pages, page_size, n_entries, total_q_tiles, nq, nkv, window,
-                                           scale, err, st);
+                                           scale, skip_single, err, st);
 }
 #else
 #define CRANE_PREFILL_HEAD_SIZES(X) X(16) X(32) X(48) X(64) X(80) X(96) X(112) X(128) X(160) X(192) X(256)
@@ -246,20 +249,22 @@ CRANE_API int crane_paged_prefill_attention_supports(int d, int nq, int nkv) {
     return 0;
 }
 
-// total_q_tiles: sum over the entries of ceil(q_len / 64).
+// total_q_tiles: sum over the entries of ceil(q_len / 64) (an upper bound will do: tiles beyond
+// the real ones do nothing).  skip_single != 0: entries of exactly one token are left out (they
+// count no tile either); their rows of `out` are for the decode kernel to write.
 CRANE_API int crane_paged_prefill_attention(const void* q, void* out, const void* k_pool,
                                             const void* v_pool, const int* cu_q, const int* kv_len,
                                             const int* block_table, int max_blocks, int num_pages,
                                             int page_size, int n_entries, int total_q_tiles, int nq,
-                                            int nkv, int d, int window, float scale, int* err,
-                                            cudaStream_t st) {
+                                            int nkv, int d, int window, float scale, int skip_single,
+                                            int* err, cudaStream_t st) {
     if (n_entries <= 0 || total_q_tiles <= 0) return 0;
     if (!crane_paged_prefill_attention_supports(d, nq, nkv)) return (int)cudaErrorInvalidValue;
 #define CASE(DD)                                                                                      \
     case DD:                                                                                          \
         return crane_prefill_launch_d##DD(q, out, k_pool, v_pool, cu_q, kv_len, block_table, max_blocks, \
                                           num_pages, page_size, n_entries, total_q_tiles, nq, nkv,      \
-                                          window, scale, err, st);
+                                          window, scale, skip_single, err, st);
     switch (d) { CRANE_PREFILL_HEAD_SIZES(CASE) }
 #undef CASE
     return (int)cudaErrorInvalidValue;

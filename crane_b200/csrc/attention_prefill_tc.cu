@@ -187,6 +187,7 @@ struct Params {
     const int* kv_len;
     const int* block_table;
     int max_blocks, num_pages, page_size, n_entries, nq, nkv, window;
+    int skip_single;             // entries of one token have no tile here (the decode kernel takes them)
     float scale_log2;
     int* err;
 };
@@ -220,7 +221,8 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // keys, come first)
     int e = 0, tile = blockIdx.x;
     for (; e < p.n_entries; ++e) {
-        const int tiles = (p.cu_q[e + 1] - p.cu_q[e] + BQ - 1) / BQ;
+        const int rows = p.cu_q[e + 1] - p.cu_q[e];
+        const int tiles = (p.skip_single && rows == 1) ? 0 : (rows + BQ - 1) / BQ;
         if (tile < tiles) {
             tile = tiles - 1 - tile;
             break;
@@ -550,12 +552,13 @@ CRANE_API int crane_prefill_attention_tc_supports(int d, int nq, int nkv, int pa
     return d == 128 && (page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128);
 }
 
-// total_q_tiles: sum over the entries of ceil(q_len / 128).  q is [n_tokens, nq * 128].
+// total_q_tiles: sum over the entries of ceil(q_len / 128) (or more).  q is [n_tokens, nq * 128].
+// skip_single != 0: entries of exactly one token are left out and count no tile.
 CRANE_API int crane_prefill_attention_tc(const void* q, void* out, const void* k_pool, const void* v_pool,
                                          const int* cu_q, const int* kv_len, const int* block_table,
                                          int max_blocks, int num_pages, int page_size, int n_entries,
                                          int n_tokens, int total_q_tiles, int nq, int nkv, int d, int window,
-                                         float scale, int* err, cudaStream_t st) {
+                                         float scale, int skip_single, int* err, cudaStream_t st) {
     if (n_entries <= 0 || total_q_tiles <= 0) return 0;
     if (!crane_prefill_attention_tc_supports(d, nq, nkv, page_size)) return (int)cudaErrorInvalidValue;
     CUtensorMap mq, mk, mv;
@@ -566,7 +569,7 @@ CRANE_API int crane_prefill_attention_tc(const void* q, void* out, const void* k
     Params p;
     p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.kv_len = kv_len; p.block_table = block_table;
     p.max_blocks = max_blocks; p.num_pages = num_pages; p.page_size = page_size; p.n_entries = n_entries;
-    p.nq = nq; p.nkv = nkv; p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.err = err;
+    p.nq = nq; p.nkv = nkv; p.window = window; p.skip_single = skip_single; p.scale_log2 = scale * 1.4426950408889634f; p.err = err;
     constexpr size_t smem = 5 * TILE_BYTES + 18 * 8 + 2 * SPLIT * BQ * 4 + 16 + 1024;
     static bool configured = false;
     if (!configured) {

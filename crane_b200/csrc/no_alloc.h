@@ -15,6 +15,7 @@
 //
 //  * The array is CRANE_NOALLOC_SCRATCH_FLOATS floats (4 MiB).  Every GPU that
 //    loads the library holds it from load until the process exits.
+//  * n_splits is 1..64 (anything else: CRANE_NOALLOC_BAD_ARGUMENT).
 //  * A call needs n_entries * nq * n_splits * (d + 2) floats of it.  A call
 //    that needs more is refused with CRANE_NOALLOC_TOO_LARGE and launches
 //    nothing; crane_noalloc_strerror() says so in words.  n_splits == 1 needs

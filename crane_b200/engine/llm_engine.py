@@ -71,6 +71,8 @@ class LLMEngine:
         self._next_id = 1
         self.finished: Dict[int, RequestOutput] = {}
         self.timers = {"prefill_s": 0.0, "decode_s": 0.0, "prefill_tokens": 0, "decode_tokens": 0}
+        self.last_step_kind = ""          # of the batch the last step() launched: "decode" (single tokens
+                                          # only), "prefill" (prompt portions only), "mixed", or "" (none)
 
     # ---- requests -------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -121,6 +123,7 @@ class LLMEngine:
         for rid in self.scheduler.last_failed():
             self._finish(rid)
         cur = self._launch(plan, overlap) if plan else None
+        self.last_step_kind = ""
         if self._inflight is not None:
             out += self.flush()
         if cur is not None:
@@ -129,6 +132,7 @@ class LLMEngine:
                 out += self.flush()
             n_tok = sum(len(p.tokens) for p in plan)
             kind = "decode" if all(len(p.tokens) == 1 for p in plan) else "prefill"
+            self.last_step_kind = kind if kind == "decode" or all(len(p.tokens) > 1 for p in plan) else "mixed"
             self.timers[kind + "_s"] += time.perf_counter() - t0
             self.timers[kind + "_tokens"] += n_tok
         return out

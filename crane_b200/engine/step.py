@@ -70,6 +70,10 @@ class StepContext:
                                         # the wanted rows beyond ``real_want`` repeat row 0
     real_want: int = 0
     replay: bool = False        # a step with a graph_key: replay its graph (else launch its kernels)
+    single_entries: int = 0     # > 0: a step with prompt portions whose entries of exactly one token
+                                # (decoded tokens, about this many) are worth a kernel of their own:
+                                # an attention mixer may give them to its split-KV decode kernel and
+                                # the rest to its prefill kernel
 
 
 class _MetaBuffers:
@@ -246,23 +250,6 @@ class ModelRunner:
         pad_to = 0
         if (self._graphs_ok and max(counts) == 1 and all(len(e.want) == 1 for e in entries)):
             pad_to = self._bucket(n_entries)
-        # a small step with prompt portions: its rows are padded to a multiple of 64, its entries
-        # and wanted places to a power of two, and from the second step of the same (rows,
-        # entries, wanted) on a captured graph is replayed
-        key = None
-        # (a prompt portion alone or beside one other entry has few shapes, so all of them up to
-        # graph_max_tokens are worth a graph; mixes of many entries come in many shapes, and only the
-        # small ones, which the host could not launch as fast as the device runs them, get one)
-        limit = self.cfg.graph_max_tokens if n_entries <= 2 else self.cfg.graph_max_tokens // 4
-        if (not pad_to and self._graphs_ok and 0 < n_tokens <= limit):
-            rows = min(-(-n_tokens // 64) * 64, self.cap_tokens)
-            wanted = sum(len(e.want) for e in entries)
-            shape = ("rows", rows, self._power_of_two(n_entries, self.cap_entries),
-                     self._power_of_two(wanted, rows) if wanted else 0)
-            seen = self._shape_seen.get(shape, 0) + 1
-            self._shape_seen[shape] = seen
-            if seen >= 2:
-                key = shape
         m = self.meta
         m.copied.synchronize()                      # the last step's copy has left the host block
         real_entries = n_entries
@@ -278,6 +265,33 @@ class ModelRunner:
         n_tokens = self.table.fill_step(ids, cnt, m.np, m.off["positions"], m.off["tok_entry"],
                                         m.off["cu_q"], m.off["kv_len"], m.off["slots"], m.bt_off_arr,
                                         m.max_blocks_arr)
+        # Decoded tokens beside prompt portions: when together they read enough cached keys, they are
+        # worth the split-KV decode kernel (the prefill kernel would give each a whole query tile with
+        # one live row and walk its context unsliced).
+        singles = 0
+        if not pad_to and n_tokens > n_entries and not self.rt.exact:
+            one = cnt == 1
+            if one.any() and int(m.view("kv_len", n_entries, False)[one].sum()) >= self.cfg.mixed_decode_min_keys:
+                singles = int(one.sum())
+        # a small step with prompt portions: its rows are padded to a multiple of 64, its entries
+        # and wanted places to a power of two, and from the second step of the same (rows,
+        # entries, wanted, single-token entries) on a captured graph is replayed
+        key = None
+        # (a prompt portion alone or beside one other entry has few shapes, so all of them up to
+        # graph_max_tokens are worth a graph; mixes of many entries come in many shapes, and only the
+        # small ones, which the host could not launch as fast as the device runs them, get one)
+        limit = self.cfg.graph_max_tokens if n_entries <= 2 else self.cfg.graph_max_tokens // 4
+        if (not pad_to and self._graphs_ok and 0 < n_tokens <= limit):
+            rows = min(-(-n_tokens // 64) * 64, self.cap_tokens)
+            wanted = sum(len(e.want) for e in entries)
+            shape = ("rows", rows, self._power_of_two(n_entries, self.cap_entries),
+                     self._power_of_two(wanted, rows) if wanted else 0,
+                     self._power_of_two(singles, self.cap_entries) if singles else 0)
+            seen = self._shape_seen.get(shape, 0) + 1
+            self._shape_seen[shape] = seen
+            if seen >= 2:
+                key = shape
+                singles = shape[4]
         m.view("tokens", n_tokens, False)[:] = arrays[0] if len(arrays) == 1 else np.concatenate(arrays)
         if key is not None and key[1] > n_tokens:
             m.view("tokens", key[1], False)[n_tokens:] = 0
@@ -314,6 +328,7 @@ class ModelRunner:
         ctx = StepContext()
         ctx.graph_bucket, ctx.real_entries = pad_to, real_entries
         ctx.graph_key = key
+        ctx.single_entries = singles
         # While the device still runs the step before, the host launches this step's kernels
         # behind it at no cost, and launched one by one they ran a little faster than replayed
         # (a serving mix: 5 % per step): a graph pays when the device waits for the host.  The

@@ -32,11 +32,11 @@ _SIGNATURES = {
     "crane_paged_decode_attention_supports": [I, I, I],
     "crane_paged_decode_attention": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P],
     "crane_paged_prefill_attention_supports": [I, I, I],
-    "crane_paged_prefill_attention": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P],
+    "crane_paged_prefill_attention": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
     "crane_paged_decode_attention_fused": [P, P, I, L, I, I, I, P, P, I, P, P, F, P, P, P, P, P, P, P, P,
                                            I, I, I, I, I, I, I, I, F, I, P, P],
     "crane_prefill_attention_tc_supports": [I, I, I, I],
-    "crane_prefill_attention_tc": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, P],
+    "crane_prefill_attention_tc": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
     "crane_repetition_penalty": [P, L, I, I, P, I, P, P, P],
     "crane_sample": [P, L, I, I, P, P, P, P, P, P, P],
 }
@@ -299,8 +299,9 @@ class Kernels:
 
     def paged_decode_attention(self, q, out, k_pool, v_pool, cu_q, kv_len, block_table, page_size,
                                nq, nkv, d, window, scale, n_splits, part_o, part_ml, err) -> None:
-        """One token per entry (bfloat16); ``part_o`` [entries * nq * n_splits * d]
-        and ``part_ml`` [entries * nq * n_splits * 2] floats are scratch for n_splits > 1."""
+        """The entries of exactly one token (bfloat16); entries with more or no
+        rows are skipped.  ``part_o`` [entries * nq * n_splits * d] and ``part_ml``
+        [entries * nq * n_splits * 2] floats are scratch for n_splits > 1."""
         n_entries = kv_len.shape[0]
         self._check(self.lib.crane_paged_decode_attention(
             q.data_ptr(), out.data_ptr(), _ptr(part_o), _ptr(part_ml), k_pool.data_ptr(),
@@ -312,27 +313,29 @@ class Kernels:
         return bool(self.lib.crane_paged_prefill_attention_supports(d, nq, nkv))
 
     def paged_prefill_attention(self, q, out, k_pool, v_pool, cu_q, kv_len, block_table, page_size,
-                                total_q_tiles, nq, nkv, d, window, scale, err) -> None:
+                                total_q_tiles, nq, nkv, d, window, scale, err, skip_single=False) -> None:
         """Any mix of portions and single tokens (bfloat16).  ``total_q_tiles``:
-        the sum over the entries of ceil(tokens / 64)."""
+        the sum over the entries of ceil(tokens / 64), or more.  ``skip_single``:
+        entries of exactly one token are left to the decode kernel."""
         self._check(self.lib.crane_paged_prefill_attention(
             q.data_ptr(), out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), cu_q.data_ptr(),
             kv_len.data_ptr(), block_table.data_ptr(), block_table.shape[1], k_pool.shape[0],
             page_size, kv_len.shape[0], int(total_q_tiles), nq, nkv, d, int(window), float(scale),
-            err.data_ptr(), self._stream(q)), "paged_prefill_attention")
+            1 if skip_single else 0, err.data_ptr(), self._stream(q)), "paged_prefill_attention")
 
     def prefill_attention_tc_supports(self, d: int, nq: int, nkv: int, page_size: int) -> bool:
         return bool(self.lib.crane_prefill_attention_tc_supports(d, nq, nkv, page_size))
 
     def prefill_attention_tc(self, q, out, k_pool, v_pool, cu_q, kv_len, block_table, page_size,
-                             total_q_tiles, nq, nkv, d, window, scale, err) -> None:
+                             total_q_tiles, nq, nkv, d, window, scale, err, skip_single=False) -> None:
         """Flash attention on tcgen05 (head size 128).  ``total_q_tiles``: the sum
-        over the entries of ceil(tokens / 128)."""
+        over the entries of ceil(tokens / 128), or more.  ``skip_single`` as in
+        ``paged_prefill_attention``."""
         self._check(self.lib.crane_prefill_attention_tc(
             q.data_ptr(), out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), cu_q.data_ptr(),
             kv_len.data_ptr(), block_table.data_ptr(), block_table.shape[1], k_pool.shape[0],
             page_size, kv_len.shape[0], q.shape[0], int(total_q_tiles), nq, nkv, d, int(window),
-            float(scale), err.data_ptr(), self._stream(q)), "prefill_attention_tc")
+            float(scale), 1 if skip_single else 0, err.data_ptr(), self._stream(q)), "prefill_attention_tc")
 
     def paged_decode_attention_fused(self, qkv: Act, qkv_cols, has_kv, cos, sin, q_norm_w, k_norm_w,
                                      eps, out, k_pool, v_pool, cu_q, kv_len, block_table, page_size,

@@ -116,8 +116,20 @@ class GqaAttention(Part):
                           sin, self.q_norm, self.k_norm, self.eps, q, cache.k, cache.v,
                           cache.page_size, self.nq, self.nkv, self.d, self.own_kv,
                           self.position is not None, rt.err)
-        if decode:
-            splits = max(1, min(32, (2 * rt.num_sms) // max(1, ctx.n_entries * self.nkv)))
+        use_tc = (not rt.exact and rt.use_tc_attention
+                  and k.prefill_attention_tc_supports(self.d, self.nq, self.nkv, cache.page_size))
+        use_mma = not rt.exact and k.prefill_attention_supports(self.d, self.nq, self.nkv)
+        # Decoded tokens beside prompt portions: the entries of one token go to the split-KV decode
+        # kernel (which skips the others), the prompt portions to the prefill kernel (which skips them).
+        singles = getattr(ctx, "single_entries", 0) if (use_tc or use_mma) and not decode else 0
+        if singles and not k.decode_attention_supports(self.d, self.nq, self.nkv):
+            singles = 0
+        if decode or singles:
+            if decode:
+                splits = max(1, min(32, (2 * rt.num_sms) // max(1, ctx.n_entries * self.nkv)))
+            else:
+                # at most 8 slices: at head size 128 they merge inside a cluster without scratch
+                splits = min(8, k.decode_splits(singles, self.nkv, rt.num_sms, self.max_splits))
             part_o = part_ml = None
             if splits > 1:
                 rows = rt.max_decode_rows * self.nq * 32
@@ -127,17 +139,20 @@ class GqaAttention(Part):
                                      cache.page_size, self.nq, self.nkv, self.d, self.window,
                                      self.scale, splits, part_o, part_ml, rt.err)
             rt.launches += 3 if splits > 1 else 2
-        elif (not rt.exact and rt.use_tc_attention
-              and k.prefill_attention_tc_supports(self.d, self.nq, self.nkv, cache.page_size)):
-            tiles = query_tiles(ctx, 128)
+            if decode:
+                return rt.linear(o, self.o_w, self.o_b, "attn_out")
+            rt.launches -= 1                      # the rotary kernel is counted once, below
+        if use_tc:
+            tiles = query_tiles(ctx, 128, skip_single=bool(singles))
             k.prefill_attention_tc(q, o, cache.k, cache.v, ctx.cu_q, ctx.kv_len, table, cache.page_size,
-                                   tiles, self.nq, self.nkv, self.d, self.window, self.scale, rt.err)
+                                   tiles, self.nq, self.nkv, self.d, self.window, self.scale, rt.err,
+                                   skip_single=bool(singles))
             rt.launches += 2
-        elif not rt.exact and k.prefill_attention_supports(self.d, self.nq, self.nkv):
-            tiles = query_tiles(ctx, 64)
+        elif use_mma:
+            tiles = query_tiles(ctx, 64, skip_single=bool(singles))
             k.paged_prefill_attention(q, o, cache.k, cache.v, ctx.cu_q, ctx.kv_len, table,
                                       cache.page_size, tiles, self.nq, self.nkv, self.d, self.window,
-                                      self.scale, rt.err)
+                                      self.scale, rt.err, skip_single=bool(singles))
             rt.launches += 2
         else:
             k.paged_attention_simt(q, o, cache.k, cache.v, ctx.positions, ctx.tok_entry, table,

@@ -166,12 +166,15 @@ class Workspace:
         return sum(b.numel() * b.element_size() for b in self._bufs.values())
 
 
-def query_tiles(ctx, rows_per_tile: int) -> int:
+def query_tiles(ctx, rows_per_tile: int, skip_single: bool = False) -> int:
     """How many tiles of ``rows_per_tile`` query rows the step's entries have, no
-    tile spanning two entries.  For a step that replays a captured graph
-    (``ctx.graph_key``), the most that any step of the same shape can have:
-    kernels skip the tiles beyond the real ones."""
+    tile spanning two entries (``skip_single``: not counting entries of exactly
+    one token).  For a step that replays a captured graph (``ctx.graph_key``),
+    the most that any step of the same shape can have: kernels skip the tiles
+    beyond the real ones."""
     if getattr(ctx, "graph_key", None) is not None:
         return ctx.n_entries + ctx.n_tokens // rows_per_tile
     q_lens = ctx.h_cu_q[1:ctx.n_entries + 1] - ctx.h_cu_q[:ctx.n_entries]
+    if skip_single:
+        q_lens = q_lens[q_lens != 1]
     return int(((q_lens + rows_per_tile - 1) // rows_per_tile).sum())

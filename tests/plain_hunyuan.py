@@ -163,14 +163,17 @@ def causal_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray,
     n_rep = nq // nkv
     out = np.zeros((T, nq, d), dtype=F)
     idx = np.arange(T)
-    allowed = idx[None, :] <= idx[:, None]
-    if window > 0:
-        allowed &= idx[None, :] > idx[:, None] - window
-    for h in range(nq):
-        g = h // n_rep
-        s = (q[:, h, :] @ k[:, g, :].T) * (1.0 / math.sqrt(d))
-        s = np.where(allowed, s, -np.inf)
-        out[:, h, :] = softmax_rows(s) @ v[:, g, :]
+    # (the rows in blocks of 2048 only so that a long sequence's [T, T] scores need not exist at once)
+    for r0 in range(0, T, 2048):
+        r1 = min(T, r0 + 2048)
+        allowed = idx[None, :r1] <= idx[r0:r1, None]
+        if window > 0:
+            allowed &= idx[None, :r1] > idx[r0:r1, None] - window
+        for h in range(nq):
+            g = h // n_rep
+            s = (q[r0:r1, h, :] @ k[:r1, g, :].T) * (1.0 / math.sqrt(d))
+            s = np.where(allowed, s, -np.inf)
+            out[r0:r1, h, :] = softmax_rows(s) @ v[:r1, g, :]
     return out.reshape(T, nq * d)
 
 

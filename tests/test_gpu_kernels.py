@@ -289,6 +289,111 @@ def test_window_edge(K, err, dtype):
     assert abs(float(out[0, 0]) - (n - window)) < 1.0
 
 
+def _window_edge_request(pos0, q_len, nq, nkv, d, window):
+    """Queries, keys and values of one request in which every query row has a
+    key that would swamp its softmax JUST outside its window and its heaviest
+    legitimate key JUST inside: row i (position p = pos0 + i) asks channel
+    i mod d; key j answers 30 in the channel of the row whose window it has just
+    left (j = p - window) and 5 in the channel of the row whose window starts at
+    it (j = p - window + 1).  The window is shorter than d, so inside a row's
+    window no other key answers its channel.  Channel 0 of the values is the
+    key's position (from the request's first kept one), the rest small noise: a
+    key too many pulls a row's output to p - window, a key too few to the middle
+    of its window."""
+    assert window + 2 <= d
+    n = pos0 + q_len
+    q = torch.zeros(q_len, nq, d)
+    for i in range(q_len):
+        q[i, :, i % d] = d ** 0.5                       # times 1 / sqrt(d): the key's channel value is the score
+    k = torch.zeros(n, nkv, d)
+    for j in range(n):
+        k[j, :, (j + window - pos0) % d] = 30.0
+        k[j, :, (j - 1 + window - pos0) % d] = 5.0
+    v = 0.05 * torch.randn(n, nkv, d)
+    v[:, :, 0] = (torch.arange(n).float() - max(0, pos0 - window - 2))[:, None]
+    return q.bfloat16().float(), k.bfloat16().float(), v.bfloat16().float()
+
+
+def _check_window_edge(out_rows, reqs, window, nq, d):
+    row = 0
+    for (pos0, q_len), (q, k, v) in reqs:
+        for i in range(q_len):
+            want = attention_reference(q[i], k, v, pos0 + i, window)
+            got = out_rows[row].double().cpu().view(nq, d)
+            # channel 0 is a position: a wrong edge moves it by a fifth of the window or more
+            assert (got[:, 0] - want[:, 0]).abs().max() < 0.02 * window + 0.01 * float(want[:, 0].abs().max()), \
+                (pos0, i, got[:, 0], want[:, 0])
+            assert rel_err(got, want) < 1.5e-2, (pos0, i)
+            row += 1
+
+
+WINDOW_EDGE_KERNELS = ["simt", "decode_1", "decode_3", "decode_12", "fused_1", "fused_3", "fused_12",
+                       "prefill_mma", "prefill_tc"]
+
+
+@pytest.mark.parametrize("kernel", WINDOW_EDGE_KERNELS)
+@pytest.mark.parametrize("d,page_size,window", [(128, 64, 100), (128, 32, 33), (64, 16, 50)])
+def test_window_edge_of_the_serving_kernels(K, err, kernel, d, page_size, window):
+    """Every attention kernel that serves: the key at p - window is not read, the
+    one at p - window + 1 is, for every row of a query tile (rows of one tile have
+    different window starts), with the edge at the start of a tile, of a page, in
+    their middle, and before the first key."""
+    nq, nkv = 8, 2
+    if kernel == "prefill_tc" and not K.prefill_attention_tc_supports(d, nq, nkv, page_size):
+        pytest.skip("the tcgen05 flash attention is built for head size 128")
+    torch.manual_seed(window)
+    single = kernel.startswith(("decode", "fused"))
+    if single:
+        # the window's first key: position 0, 1, a tile's first (32), 33, a page's first and last, mid-tile
+        first = [0, 1, 32, 33, page_size, 2 * page_size - 1, 4 * page_size, 77, 600, 1000]
+        shapes = [(lo + window - 1, 1) for lo in first] + [(window // 2, 1)]      # the last: no key left out yet
+    else:
+        shapes = [(211, 300), (1333 - 1, 1), (0, 150), (65, 2), (window - 1, 3)]
+    reqs = [((pos0, ql), _window_edge_request(pos0, ql, nq, nkv, d, window)) for pos0, ql in shapes]
+    lens = [pos0 + ql for pos0, ql in shapes]
+    q_lens = [ql for _, ql in shapes]
+    ks, vs = [r[1][1].clone() for r in reqs], [r[1][2].clone() for r in reqs]
+    if kernel.startswith("fused"):
+        for k_, v_ in zip(ks, vs):                       # the new position's key and value come from the step
+            k_[-1] = 77.0
+            v_[-1] = 77.0
+    k_pool, v_pool, table = paged_cache(ks, vs, page_size, torch.bfloat16, seed=window)
+    i32 = lambda x: torch.tensor(np.asarray(x), dtype=torch.int32, device=DEV)
+    cu = np.concatenate([[0], np.cumsum(q_lens)])
+    q = torch.cat([r[1][0] for r in reqs]).to(DEV).bfloat16().reshape(-1, nq * d)
+    out = torch.full_like(q, 9.0)
+    scale = d ** -0.5
+    n = len(shapes)
+    if kernel == "simt":
+        pos = np.concatenate([np.arange(p0, p0 + ql) for p0, ql in shapes])
+        ent = np.concatenate([np.full(ql, e) for e, ql in enumerate(q_lens)])
+        K.paged_attention_simt(q, out, k_pool, v_pool, i32(pos), i32(ent), table, page_size, nq, nkv, d,
+                               window, scale, err)
+    elif single:
+        splits = int(kernel.split("_")[1])
+        part_o = torch.empty(n * nq * splits * d, device=DEV)
+        part_ml = torch.empty(n * nq * splits * 2, device=DEV)
+        if kernel.startswith("decode"):
+            K.paged_decode_attention(q, out, k_pool, v_pool, i32(cu), i32(lens), table, page_size, nq, nkv, d,
+                                     window, scale, splits, part_o, part_ml, err)
+        else:
+            new_k = torch.stack([r[1][1][-1] for r in reqs]).reshape(n, nkv * d)
+            new_v = torch.stack([r[1][2][-1] for r in reqs]).reshape(n, nkv * d)
+            qkv = torch.cat([q, new_k.to(DEV).bfloat16(), new_v.to(DEV).bfloat16()], dim=1).contiguous()
+            K.paged_decode_attention_fused(qkv, qkv.shape[1], True, None, None, None, None, 0.0, out, k_pool,
+                                           v_pool, i32(cu), i32(lens), table, page_size, nq, nkv, d, window,
+                                           scale, splits, part_o, part_ml, err)
+    elif kernel == "prefill_mma":
+        K.paged_prefill_attention(q, out, k_pool, v_pool, i32(cu), i32(lens), table, page_size,
+                                  sum((x + 63) // 64 for x in q_lens), nq, nkv, d, window, scale, err)
+    else:
+        K.prefill_attention_tc(q, out, k_pool, v_pool, i32(cu), i32(lens), table, page_size,
+                               sum((x + 127) // 128 for x in q_lens), nq, nkv, d, window, scale, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    _check_window_edge(out, reqs, window, nq, d)
+
+
 def test_argmax_ties_go_to_the_lowest_index(K):
     vocab = 120818
     logits = torch.randn(3, vocab, device=DEV)
@@ -678,6 +783,56 @@ def test_prefill_attention_tcgen05_mixed_batch(K, err, nq, nkv, page_size, windo
             assert rel_err(out[row + i].cpu().view(nq, d), want) < 1.5e-2, (e, i)
         row += ql
     assert rel_err(out[300].cpu().view(nq, d)[0], vs[1][far, 0].double()) < 2e-2
+
+
+@pytest.mark.parametrize("kernel,d,nq,nkv,page_size,window,splits", [
+    ("tc", 128, 8, 2, 64, 0, 4), ("tc", 128, 16, 4, 32, 300, 8), ("mma", 128, 4, 4, 16, 0, 1),
+    ("mma", 64, 8, 2, 16, 0, 3), ("mma", 80, 10, 5, 16, 90, 2)])
+def test_single_tokens_and_portions_split_between_two_kernels(K, err, kernel, d, nq, nkv, page_size, window,
+                                                              splits):
+    """A mixed step as the attention part runs it: the entries of one token on the
+    split-KV decode kernel, the others on a prefill kernel that skips them; every
+    row is written by exactly one of the two."""
+    torch.manual_seed(d + splits)
+    lens = [511, 1333, 1000, 67, 1, 900]
+    q_lens = [300, 1, 1000, 2, 1, 1]
+    ks = [torch.randn(n, nkv, d).bfloat16().float() for n in lens]
+    vs = [torch.randn(n, nkv, d).bfloat16().float() for n in lens]
+    qs = [torch.randn(ql, nq, d).bfloat16().float() for ql in q_lens]
+    k_pool, v_pool, table = paged_cache(ks, vs, page_size, torch.bfloat16, seed=d)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    cu = np.concatenate([[0], np.cumsum(q_lens)]).tolist()
+    n = len(lens)
+    q = torch.cat(qs).to(DEV).bfloat16().reshape(-1, nq * d)
+    out = torch.full_like(q, 9.0)
+    part_o = torch.empty(n * nq * splits * d, device=DEV)
+    part_ml = torch.empty(n * nq * splits * 2, device=DEV)
+    K.paged_decode_attention(q, out, k_pool, v_pool, i32(cu), i32(lens), table, page_size, nq, nkv, d, window,
+                             d ** -0.5, splits, part_o, part_ml, err)
+    torch.cuda.synchronize()
+    untouched = [r for e in range(n) if q_lens[e] != 1 for r in range(cu[e], cu[e + 1])]
+    assert float(out[untouched].float().min()) == 9.0            # the decode kernel left the portions alone
+    tile = 128 if kernel == "tc" else 64
+    tiles = sum((x + tile - 1) // tile for x in q_lens if x != 1)
+    fn = K.prefill_attention_tc if kernel == "tc" else K.paged_prefill_attention
+    fn(q, out, k_pool, v_pool, i32(cu), i32(lens), table, page_size, tiles, nq, nkv, d, window, d ** -0.5,
+       err, skip_single=True)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    row = 0
+    for e, (m, ql) in enumerate(zip(lens, q_lens)):
+        for i in sorted({0, 1, ql // 2, ql - 1} & set(range(ql))):
+            want = attention_reference(qs[e][i], ks[e], vs[e], m - ql + i, window)
+            assert rel_err(out[row + i].cpu().view(nq, d), want) < 1.5e-2, (e, i)
+        row += ql
+    # with more tiles than there are (a step padded to a shape), nothing else is written
+    again = torch.full_like(q, 9.0)
+    fn(q, again, k_pool, v_pool, i32(cu), i32(lens), table, page_size, tiles + 5, nq, nkv, d, window,
+       d ** -0.5, err, skip_single=True)
+    torch.cuda.synchronize()
+    singles = [cu[e] for e in range(n) if q_lens[e] == 1]
+    assert float(again[singles].float().min()) == 9.0
+    assert torch.equal(again[untouched], out[untouched])
 
 
 @pytest.mark.parametrize("qk_norm", [True, False])

@@ -32,10 +32,19 @@ def test_replay_at_model_layer_sizes(name, dtype, model_folders, tmp_path):
     tt.trace_portions(tb, reqs, np.random.default_rng(7))
     got = tt.run_trace(folder, dtype, tb.steps, tb.peak_tokens, ps, str(tmp_path / "alone"))
     worst = tt.compare(got, tb, plain, dtype, f"{name} alone")
+    runs = [(got, tb)]
     # mixed, pool so small that pages are used again
     tm = tt.TraceBuilder(ps)
     tt.trace_mixed(tm, reqs, np.random.default_rng(11))
     assert tm.pages_taken > tm.peak_tokens // ps
     got = tt.run_trace(folder, dtype, tm.steps, tm.peak_tokens, ps, str(tmp_path / "mixed"))
     worst = max(worst, tt.compare(got, tm, plain, dtype, f"{name} mixed"))
+    runs.append((got, tm))
+    if dtype == "bfloat16":
+        # once more with every single token of a mixed step on the split-KV decode kernel
+        got = tt.run_trace(folder, dtype, tm.steps, tm.peak_tokens, ps, str(tmp_path / "mixed_split"),
+                           extra_args=["--mixed-decode-min-keys", "0"])
+        worst = max(worst, tt.compare(got, tm, plain, dtype, f"{name} mixed, decode kernel"))
+        runs.append((got, tm))
+    tt.compare_cuts(runs, dtype, name)
     print(f"{name} {dtype}: worst relative error {worst:.3e}")

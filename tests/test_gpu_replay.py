@@ -46,6 +46,7 @@ def test_alone_whole_tail_portions(name, dtype, cases, tmp_path):
     tt.trace_portions(tb, reqs, np.random.default_rng(7))
     got = tt.run_trace(folder, dtype, tb.steps, tb.peak_tokens, ps, str(tmp_path / "out"))
     worst = tt.compare(got, tb, plain, dtype, f"config {name}")
+    tt.compare_cuts([(got, tb)], dtype, f"config {name}")
     print(f"config {name} {dtype}: worst relative error {worst:.3e}")
 
 
@@ -62,3 +63,20 @@ def test_mixed_with_page_reuse(name, dtype, cases, tmp_path):
     got = tt.run_trace(folder, dtype, tb.steps, tb.peak_tokens, ps, str(tmp_path / "out"))
     worst = tt.compare(got, tb, plain, dtype, f"config {name} mixed")
     print(f"config {name} {dtype} mixed: worst relative error {worst:.3e}")
+
+
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_mixed_with_the_decode_kernel_for_single_tokens(name, cases, tmp_path):
+    """The same mixed traces with every single token of a mixed step sent to the
+    split-KV decode kernel and the portions to the prefill kernel (the engine
+    does this by itself once the single tokens read thousands of cached keys;
+    here from the first key on)."""
+    folder, reqs, plain = cases(name, "bfloat16")
+    ps = tiny_configs.TINY[name]["page_size"]
+    tb = tt.TraceBuilder(ps)
+    tt.trace_mixed(tb, reqs, np.random.default_rng(12))
+    assert any(len(s["entries"]) >= 3 and min(len(e["tokens"]) for e in s["entries"]) == 1
+               and max(len(e["tokens"]) for e in s["entries"]) > 1 for s in tb.steps)
+    got = tt.run_trace(folder, "bfloat16", tb.steps, tb.peak_tokens, ps, str(tmp_path / "out"),
+                       extra_args=["--mixed-decode-min-keys", "0"])
+    tt.compare(got, tb, plain, "bfloat16", f"config {name} mixed, decode kernel")

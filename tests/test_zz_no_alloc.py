@@ -53,25 +53,34 @@ def _call(lib, q, out, k_pool, v_pool, cu_q, kv_len, table, page_size, nq, nkv, 
         kv_len.shape[0], nq, nkv, d, 0, d ** -0.5, splits, err.data_ptr(), stream)
 
 
-def test_two_calls_in_a_row_match_the_allocating_entry_point(lib):
+def test_calls_in_a_row_match_the_allocating_entry_point(lib):
+    """Every call here has more than 8 key slices at head size 128, or another
+    head size, so its partial results do go through the built-in array and the
+    merge kernel (2 to 8 slices at head size 128 merge inside a cluster and
+    would never touch it).  Each call lays its slots out differently from the
+    one before and finds that call's leftovers in the array; entries shorter
+    than the number of slices have slices without keys."""
     from crane_b200.kernels import get_kernels
     K = get_kernels()
     err = torch.zeros(1, dtype=torch.int32, device=DEV)
-    # second call: other lengths, other slicing, fewer entries; the array still holds the first call's leftovers
-    for seed, lens, splits in ((1, [700, 33, 1025, 5], 6), (2, [90, 2048, 64], 3)):
-        d, nq, nkv, ps = 128, 16, 4, 64
+    cases = ((1, [700, 33, 1025, 5], 12, 128, 16, 4, 64),       # 4 x 16 x 12 x 130 = 99,840 floats
+             (2, [90, 2048, 64], 9, 128, 16, 4, 64),
+             (3, [300, 5, 77], 5, 64, 8, 2, 16),                # the kernel that copies with cp.async
+             (4, [40, 1500], 33, 128, 8, 1, 32))
+    for seed, lens, splits, d, nq, nkv, ps in cases:
         ks, vs, qs, k_pool, v_pool, table, q, cu_q, kv_len = _case(seed, lens, d, nq, nkv, ps)
+        n = len(lens)
+        assert n * nq * splits * (d + 2) <= SCRATCH_FLOATS
         got = torch.full_like(q, 9.0)
         assert _call(lib, q, got, k_pool, v_pool, cu_q, kv_len, table, ps, nq, nkv, d, splits, err) == 0
         want = torch.full_like(q, -9.0)
-        n = len(lens)
         part_o = torch.empty(n * nq * splits * d, device=DEV)
         part_ml = torch.empty(n * nq * splits * 2, device=DEV)
         K.paged_decode_attention(q, want, k_pool, v_pool, cu_q, kv_len, table, ps, nq, nkv, d, 0,
                                  d ** -0.5, splits, part_o, part_ml, err)
         torch.cuda.synchronize()
         assert int(err.item()) == 0
-        assert rel_err(got, want.double()) < TOL
+        assert torch.equal(got, want)              # the same kernels on the same data: the same bits
         for e in range(n):
             ref = attention_reference(qs[e], ks[e], vs[e], lens[e] - 1)
             assert rel_err(got[e].cpu().view(nq, d), ref) < TOL
@@ -91,6 +100,12 @@ def test_a_call_beyond_the_built_in_scratch_is_refused_in_words(lib):
     assert "exceed" in msg and "1048576" in msg
     torch.cuda.synchronize()
     assert float(out.float().min()) == 9.0         # nothing was launched
+    # slice counts outside 1..64 are an argument out of range, whatever the sizes
+    for bad in (0, 65):
+        code = _call(lib, q[:1], out[:1], k_pool, v_pool, cu_q[:2], kv_len[:1], table, ps, nq, nkv, d, bad, err)
+        assert code == -3 and "1..64" in lib.crane_noalloc_strerror(code).decode()
+    torch.cuda.synchronize()
+    assert float(out.float().min()) == 9.0
     # one slice needs no scratch at all and is always taken
     assert _call(lib, q, out, k_pool, v_pool, cu_q, kv_len, table, ps, nq, nkv, d, 1, err) == 0
     torch.cuda.synchronize()

@@ -13,16 +13,21 @@ import numpy as np
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 TRACE_RUN = os.path.join(ROOT, "bin", "trace_run")
 
-# relative to the largest |logit| of the compared rows
+# the largest error of a row, relative to the largest |logit| of the compared rows
 TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+# and the root-mean-square error of a row relative to the root-mean-square of its logits: rounding
+# spreads evenly over a row and stays far below the largest error's bound, while a fault of logic
+# (a key tile left out, a slice dropped) moves the whole row
+TOL_RMS = {"float32": 1e-5, "bfloat16": 2.5e-2}
+worst_rms = {"float32": 0.0, "bfloat16": 0.0}        # the largest seen so far in this process, for reports
 
 
 def run_trace(model_dir: str, dtype: str, steps: List[dict], max_tokens: int, page_size: int,
-              out_dir: str, timeout: int = 600) -> Dict[int, np.ndarray]:
+              out_dir: str, timeout: int = 600, extra_args: Sequence[str] = ()) -> Dict[int, np.ndarray]:
     os.makedirs(out_dir, exist_ok=True)
     text = "".join(json.dumps(s) + "\n" for s in steps)
     cmd = [sys.executable, TRACE_RUN, "--model", model_dir, "--dtype", dtype, "--out", out_dir,
-           "--max-tokens", str(max_tokens), "--page-size", str(page_size)]
+           "--max-tokens", str(max_tokens), "--page-size", str(page_size), *extra_args]
     proc = subprocess.run(cmd, input=text, capture_output=True, text=True, timeout=timeout)
     assert proc.returncode == 0, f"trace_run failed ({proc.returncode}):\n{proc.stdout[-2000:]}\n{proc.stderr[-4000:]}"
     done = [l for l in proc.stdout.splitlines() if l.startswith("done ")]
@@ -158,9 +163,47 @@ def trace_mixed(tb: TraceBuilder, reqs: Dict[str, List[int]], rng: np.random.Gen
 
 
 def expected_rows(rows: List[Tuple[str, int]], plain: Dict[str, np.ndarray]) -> np.ndarray:
-    def base(name: str) -> str:
-        return name.rstrip("tpm") if name[-1] in "tpm" else name
-    return np.stack([plain[base(r)][p] for r, p in rows])
+    return np.stack([plain[_base(r)][p] for r, p in rows])
+
+
+# The same position computed under different cuttings and batchings (whole, decoded one by one, in
+# portions, mixed with other requests) goes through the same weights and the same rounding places;
+# only the kernels that the cutting selects differ (prefill or decode attention, tile shapes of the
+# products).  So the engine agrees with ITSELF across cuttings far more closely than with the plain
+# float64 logits in true 32-bit (measured: 4e-6 at most), where this is the sharpest check of the
+# cache and the batch.  In bfloat16 the roundings of the activations differ between kernels as much
+# as they differ from float64 (measured: up to 1.5e-2 in the worst row), so there the bound is the
+# one of TOL_RMS; single wrong keys and tiles are caught by the kernels' own tests with planted keys.
+# Root-mean-square difference of two rows relative to the root-mean-square of the logits.
+TOL_CUTS = {"float32": 1e-5, "bfloat16": 2.5e-2}
+
+
+def _base(name: str) -> str:
+    return name.rstrip("tpm") if name[-1] in "tpm" else name
+
+
+def compare_cuts(runs: Sequence[Tuple[Dict[int, np.ndarray], "TraceBuilder"]], dtype: str, label: str = "") -> float:
+    """runs: (logits by step, the trace that asked for them) of one model.  Every
+    (request, position) that was wanted more than once is compared with its
+    first occurrence.  Returns the worst relative root-mean-square difference."""
+    first: Dict[Tuple[str, int], Tuple[np.ndarray, str]] = {}
+    worst, pairs = 0.0, 0
+    for got, tb in runs:
+        for sid in sorted(tb.rows):
+            for i, (r, p) in enumerate(tb.rows[sid]):
+                key, row = (_base(r), p), got[sid][i].astype(np.float64)
+                if key not in first:
+                    first[key] = (row, f"step {sid} as {r}")
+                    continue
+                ref, where = first[key]
+                d = float(np.sqrt(((row - ref) ** 2).mean()) / np.sqrt((ref ** 2).mean()))
+                pairs += 1
+                worst = max(worst, d)
+                assert d <= TOL_CUTS[dtype], (
+                    f"{label} {dtype}: request {key[0]} position {p} differs between {where} and step {sid} "
+                    f"as {r}: relative rms difference {d:.3e} > {TOL_CUTS[dtype]:.1e}")
+    print(f"{label} {dtype}: {pairs} positions computed more than once, worst difference between cuttings {worst:.3e}")
+    return worst
 
 
 def compare(got: Dict[int, np.ndarray], tb: TraceBuilder, plain: Dict[str, np.ndarray], dtype: str,
@@ -168,6 +211,7 @@ def compare(got: Dict[int, np.ndarray], tb: TraceBuilder, plain: Dict[str, np.nd
     """Asserts every wanted row against the plain logits; returns the worst
     relative error.  On failure names the first wrong (step, request, position)."""
     worst = 0.0
+    call_rms = 0.0
     tol = TOL[dtype]
     for sid in sorted(tb.rows):
         rows = tb.rows[sid]
@@ -185,4 +229,14 @@ def compare(got: Dict[int, np.ndarray], tb: TraceBuilder, plain: Dict[str, np.nd
                 f"relative error {err[bad[0]]:.3e} > {tol:.1e} "
                 f"(page offset {p % tb.page_size}, page {p // tb.page_size})")
         worst = max(worst, float(err.max()))
+        rms = np.sqrt(((have - want) ** 2).mean(axis=1)) / np.sqrt((want ** 2).mean(axis=1))
+        worst_rms[dtype] = max(worst_rms[dtype], float(rms.max()))
+        call_rms = max(call_rms, float(rms.max()))
+        bad = np.nonzero(rms > TOL_RMS[dtype])[0]
+        if bad.size:
+            r, p = rows[int(bad[0])]
+            raise AssertionError(
+                f"{label} {dtype}: root-mean-square error of the logits at step {sid}, request {r}, "
+                f"position {p}: {rms[bad[0]]:.3e} > {TOL_RMS[dtype]:.1e}")
+    print(f"{label} {dtype}: worst max error {worst:.3e}, worst rms error {call_rms:.3e}")
     return worst
