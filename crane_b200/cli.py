@@ -34,6 +34,9 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--prompt-ids", help="comma-separated token ids; ';' separates several prompts")
     g.add_argument("--prompt-file", help="file with one prompt of comma- or space-separated ids a line")
     g.add_argument("--prompt", help="text (needs tokenizer.json)")
+    ap.add_argument("--chat", action="store_true",
+                    help="with --prompt: the text is a user message, put into the Hunyuan chat template")
+    ap.add_argument("--system", default=None, help="with --chat: a system message before the user's")
     ap.add_argument("--max-new-tokens", type=int, default=245)
     ap.add_argument("--temperature", type=float, default=None, help="omit for greedy")
     ap.add_argument("--top-p", type=float, default=None)
@@ -68,7 +71,11 @@ def main(argv: Optional[List[str]] = None) -> int:
             return 2
         from tokenizers import Tokenizer
         tokenizer = Tokenizer.from_file(path)
-        prompts = [tokenizer.encode(args.prompt, add_special_tokens=True).ids]
+        text = args.prompt
+        if args.chat:
+            from .generation.chat import format_chat
+            text = format_chat(text, args.system)
+        prompts = [tokenizer.encode(text, add_special_tokens=True).ids]
     elif args.prompt_ids is not None:
         prompts = [_parse_ids(p) for p in args.prompt_ids.split(";") if p.strip()]
     else:

@@ -655,6 +655,28 @@ __global__ void to_float_kernel(const T* __restrict__ in, float* __restrict__ ou
     if (i < n) out[i] = to_f32(in[i]);
 }
 
+// out[r, c] = sum over the split-K partial sums parts[i][r][c], in slice order, kept in float (the
+// float logits of a head whose product was computed in slices of the inner dimension)
+__global__ void sum_parts_kernel(const float* __restrict__ parts, int n_parts, long long part_stride,
+                                 long long row_pitch, float* __restrict__ out, long long out_pitch,
+                                 int rows, int cols) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)rows * cols) return;
+    const long long r = i / cols, c = i % cols;
+    const float* p = parts + r * row_pitch + c;
+    float s = 0.f;
+    for (int k = 0; k < n_parts; k += 8) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = (k + j < n_parts) ? p[(long long)(k + j) * part_stride] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += v[j];
+    }
+    out[r * out_pitch + c] = s;
+}
+
 static bool norm_cluster_on() {
     static int on = -1;
     if (on < 0) {
@@ -809,4 +831,12 @@ CRANE_API int crane_to_float(int dtype, const void* in, float* out, long long n,
     const int blocks = (int)((n + 255) / 256);
     DISPATCH_T(dtype, (to_float_kernel<T><<<blocks, 256, 0, st>>>((const T*)in, out, n)));
     return crane_launch_status();
+}
+
+CRANE_API int crane_sum_parts(const float* parts, int n_parts, long long part_stride, long long row_pitch,
+                              float* out, long long out_pitch, int rows, int cols, cudaStream_t st) {
+    if (rows <= 0 || cols <= 0 || n_parts <= 0) return 0;
+    const long long n = (long long)rows * cols;
+    return crane_launch(sum_parts_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, parts, n_parts,
+                        part_stride, row_pitch, out, out_pitch, rows, cols);
 }

@@ -1,9 +1,10 @@
 """GenerationConfig, streamers and the ModelForCausalLM entry point."""
+from .chat import apply_chat_template, format_chat
 from .config import GenerationConfig
 from .streamer import AsyncTextStreamer, ListStreamer, TextStreamer, TokenStreamer
 
 __all__ = ["GenerationConfig", "TokenStreamer", "ListStreamer", "TextStreamer", "AsyncTextStreamer",
-           "ModelForCausalLM"]
+           "ModelForCausalLM", "apply_chat_template", "format_chat"]
 
 
 def __getattr__(name):

@@ -25,6 +25,7 @@ _SIGNATURES = {
                               I, I, I, I, P, P],
     "crane_silu_mul": [I, P, P, I, L, P, I, I, I, P],
     "crane_to_float": [I, P, P, L, P],
+    "crane_sum_parts": [P, I, L, L, P, L, I, I, P],
     "crane_gemm_simt": [I, I, P, P, P, P, I, I, I, L, L, L, P],
     "crane_gemm_bf16_tcgen05": [P, P, P, P, I, I, I, L, L, L, I, I, I, I, L, I, P, P],
     "crane_gemm_bf16_pair": [P, P, P, P, I, I, I, L, L, L, I, I, P, P],
@@ -154,6 +155,15 @@ class Kernels:
         self._check(self.lib.crane_silu_mul(_dt(out.dtype), whole, parts, n_parts, stride,
                                             out.data_ptr(), out.shape[0], out.shape[1],
                                             1 if blocked else 0, self._stream(out)), "silu_mul")
+
+    def sum_parts(self, parts: "Partials", out) -> None:
+        """out[rows, cols] (float) = the partial sums added up in slice order."""
+        p = parts.parts
+        assert p.dtype == torch.float32 and out.dtype == torch.float32 and out.shape == p.shape[1:]
+        assert p.stride(2) == 1 and out.stride(1) == 1
+        self._check(self.lib.crane_sum_parts(p.data_ptr(), p.shape[0], p.stride(0), p.stride(1),
+                                             out.data_ptr(), out.stride(0), p.shape[1], p.shape[2],
+                                             self._stream(out)), "sum_parts")
 
     def to_float(self, t, out) -> None:
         self._check(self.lib.crane_to_float(_dt(t.dtype), t.data_ptr(), out.data_ptr(), t.numel(),

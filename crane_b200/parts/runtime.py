@@ -114,7 +114,8 @@ class Runtime:
                     k.gemm_tcgen05(x, w, bias, parts, self.err, split_k=slices, swap=True, bn=bn)
                     self.launches += 1
                     if out.dtype == torch.float32:
-                        torch.sum(parts, dim=0, out=out)
+                        k.sum_parts(Partials(parts), out)      # float logits: the slices added in order
+                        self.launches += 1
                         return out
                     return Partials(parts)
                 k.gemm_tcgen05(x, w, bias, out, self.err, swap=True, bn=bn)
@@ -143,13 +144,11 @@ class Runtime:
                     k.gemm_tcgen05(x, w, bias, out, self.err, bn=bn)
             self.launches += 1
             return out
-        if out.dtype == torch.bfloat16:
+        if out.dtype == torch.bfloat16 and bias is None:
             torch.mm(x, w.t(), out=out)
-            if bias is not None:
-                out += bias.to(torch.bfloat16)
             return out
-        # float result from bfloat16 operands: the FP32-core kernel keeps the
-        # float accumulator instead of rounding it to bfloat16 first
+        # with a bias, or for a float result from bfloat16 operands: the FP32-core kernel, which adds
+        # the float bias to the float accumulator and rounds once, as the tcgen05 kernels do
         k.gemm_simt(x, w, bias, out)
         self.launches += 1
         return out

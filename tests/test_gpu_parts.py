@@ -64,6 +64,45 @@ def make_ctx(rt, entries, page_size, num_pages, max_blocks, table_rows):
     return c
 
 
+@pytest.mark.parametrize("M,N,K_", [(5, 72, 100), (70, 33, 52), (300, 120, 36)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_linear_on_widths_the_tensor_core_kernel_refuses_rounds_once(M, N, K_, out_dtype):
+    """An inner dimension that is no multiple of 8 takes another product kernel;
+    with a bias it still adds the float bias to the float sum and rounds the
+    result once, as the tensor-core kernels do: the same layer gives the same
+    value whichever kernel its shape selects.  A float result from split-K
+    slices is summed in float by the engine's own kernel."""
+    rt = runtime(torch.bfloat16, rows=512)
+    torch.manual_seed(M + N)
+    x = torch.randn(M, K_, device=DEV).bfloat16()
+    w = (torch.randn(N, K_, device=DEV) / K_ ** 0.5).bfloat16()
+    bias = 3.0 * torch.randn(N, device=DEV)
+    assert not rt.kernels.tcgen05_takes(x, w)
+    for b in (bias, None):
+        got = whole(rt.linear(x, w, b, "t", out_dtype=out_dtype), out_dtype)
+        want = x.double() @ w.double().T + (b.double() if b is not None else 0.0)
+        torch.cuda.synchronize()
+        # one rounding to bfloat16 (2^-9 relative) or float accumulation error only
+        tol = 2.0 ** -8 if out_dtype == torch.bfloat16 else 1e-5
+        assert ((got.double() - want).abs() <= tol * want.abs() + 1e-4).all()     # (+ cancellation in the float sum)
+
+
+def test_float_logits_from_split_k_slices():
+    """A head narrow enough to be computed in slices of the inner dimension: the
+    float result is the slices' sum in float (no rounding to bfloat16 between)."""
+    rt = runtime(torch.bfloat16, rows=512)
+    torch.manual_seed(3)
+    x = torch.randn(6, 2048, device=DEV).bfloat16()
+    w = (torch.randn(384, 2048, device=DEV) / 45.0).bfloat16()
+    before = rt.launches
+    got = rt.linear(x, w, None, "head", out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert rt.launches - before == 2                      # the sliced product and the sum of its slices
+    want = x.double() @ w.double().T
+    assert rel_err(got, want) < 2e-6
+    rt.check_errors()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_rms_norm_part(dtype):
     from crane_b200.config import PartSpec
