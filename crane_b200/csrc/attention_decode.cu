@@ -52,7 +52,17 @@ struct FusedArgs {
     float eps;
     __nv_bfloat16* k_pool_w;        // the pools again, writable
     __nv_bfloat16* v_pool_w;
+    RopeParams rope;                // pairing, rotated width, norm order, norm weight offset
+    int general;                    // 0: the defaults (whole head, contiguous halves, norm after, plain w)
 };
+
+// A single element of the raw product (see raw2 for pairs).
+__device__ __forceinline__ float raw1(const FusedArgs& a, long long idx) {
+    if (a.qkv_parts == nullptr) return __bfloat162float(a.qkv[idx]);
+    float s = 0.f;
+    for (int i = 0; i < a.n_parts; ++i) s += a.qkv_parts[(long long)i * a.part_stride + idx];
+    return __bfloat162float(__float2bfloat16_rn(s));
+}
 
 __device__ __forceinline__ float2 raw2(const FusedArgs& a, long long idx) {
     if (a.qkv_parts == nullptr) return __bfloat1622float2(*(const __nv_bfloat162*)(a.qkv + idx));
@@ -81,6 +91,16 @@ template <int D>
 __device__ __forceinline__ void rope_norm_row(const FusedArgs& a, long long src, int pos, bool rotate,
                                               const float* nw, int lane, __nv_bfloat16* dst0,
                                               __nv_bfloat16* dst1) {
+    if (a.general) {
+        rope_norm_general<(D / 2 + 31) / 32>(a.rope, D, pos, rotate, a.cos_tab, a.sin_tab, nw, a.eps, lane,
+                                             [&](int e) { return raw1(a, src + e); },
+                                             [&](int e, float v) {
+                                                 const __nv_bfloat16 b = __float2bfloat16_rn(v);
+                                                 dst0[e] = b;
+                                                 if (dst1 != nullptr) dst1[e] = b;
+                                             });
+        return;
+    }
     constexpr int HALF = D / 2;
     constexpr int IT = (HALF + 63) / 64;
     float2 x1[IT], x2[IT];
@@ -623,75 +643,103 @@ paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
             if (threadIdx.x == 0) atomicOr(err, CRANE_ERR_POSITION_RANGE);
             rotate = false;
         }
-        // this lane's cosines, sines and norm weights are the same for every query row; the
-        // loads of two rows and of the tables are in flight together
-        static_assert(RowRegs<D>::IT == 1, "head size 128: one pair of neighbours per lane and half");
-        float2 cs[1], sn[1], w1[1], w2[1];
-        const int j = 2 * lane;
-        const bool norm = fa.q_norm_w != nullptr;
-        cs[0] = sn[0] = w1[0] = w2[0] = make_float2(0.f, 0.f);
-        if (rotate) {
-            cs[0] = *(const float2*)(fa.cos_tab + (long long)pos * (D / 2) + j);
-            sn[0] = *(const float2*)(fa.sin_tab + (long long)pos * (D / 2) + j);
-        }
-        if (norm) {
-            w1[0] = *(const float2*)(fa.q_norm_w + j);
-            w2[0] = *(const float2*)(fa.q_norm_w + j + D / 2);
-        }
-        const long long row_src = (long long)t * fa.qkv_stride;
-        const long long q_src = row_src + (long long)(g * n_rep) * D;
-        auto load_two = [&](int r, RowRegs<D>& ra, RowRegs<D>& rb) {
-            // rows r and r + WARPS of the group: four places, one round of loads
-            const bool two = r + WARPS < n_rep;
-            const long long at[4] = {q_src + (long long)r * D + j, q_src + (long long)r * D + j + D / 2,
-                                     q_src + (long long)(r + WARPS) * D + j,
-                                     q_src + (long long)(r + WARPS) * D + j + D / 2};
-            float2 got[4];
-            raw2x4(fa, at, two ? 4 : 2, got);
-            ra.u[0] = got[0]; ra.v[0] = got[1];
-            rb.u[0] = got[2]; rb.v[0] = got[3];
-        };
-        RowRegs<D> ra, rb;
-        if (warp < n_rep) load_two(warp, ra, rb);
-        for (int i = threadIdx.x; i < 16 * D / 2; i += WARPS * 32) ((uint32_t*)q_s)[i] = 0u;
-        __syncthreads();
-        for (int r = warp; r < n_rep; r += 2 * WARPS) {
-            if (r != warp) load_two(r, ra, rb);
-            row_finish<D>(ra, rotate, cs, sn, norm, w1, w2, fa.eps, lane, q_s + r * D, nullptr);
-            if (r + WARPS < n_rep)
-                row_finish<D>(rb, rotate, cs, sn, norm, w1, w2, fa.eps, lane, q_s + (r + WARPS) * D, nullptr);
-        }
-        // The warp whose tiles include the new position makes that position's key (encoded,
-        // normalised) and value now, for the page and, kept in shared memory, for its tile later:
-        // at the end of the loop these loads and the arithmetic would lengthen the whole kernel.
-        if (makes_kv && pos / TILE >= tile_begin && pos / TILE < tile_end &&
-            (pos / TILE - tile_begin) % WARPS == warp) {
-            const int page = table[pos / page_size];
-            if (page < 0 || page >= num_pages) {
-                bad_page = true;
-            } else {
-                const long long prow = (((long long)page * nkv + g) * page_size + pos % page_size) * D;
-                const long long k_src = row_src + (long long)(nq + g) * D, v_src = row_src + (long long)(nq + nkv + g) * D;
-                const long long at[4] = {k_src + j, k_src + j + D / 2, v_src + j, v_src + j + D / 2};
-                float2 got[4];
-                raw2x4(fa, at, 4, got);
-                RowRegs<D> rk;
-                rk.u[0] = got[0]; rk.v[0] = got[1];
-                float2 kw1[1], kw2[1];
-                kw1[0] = kw2[0] = make_float2(0.f, 0.f);
-                const bool knorm = fa.k_norm_w != nullptr;
-                if (knorm) {
-                    kw1[0] = *(const float2*)(fa.k_norm_w + j);
-                    kw2[0] = *(const float2*)(fa.k_norm_w + j + D / 2);
+        if (fa.general) {
+            // another pairing, a partly rotated head, the norm first or (1 + w) weights: row by row
+            const long long row_src = (long long)t * fa.qkv_stride;
+            for (int i = threadIdx.x; i < 16 * D / 2; i += WARPS * 32) ((uint32_t*)q_s)[i] = 0u;
+            __syncthreads();
+            for (int r = warp; r < n_rep; r += WARPS)
+                rope_norm_row<D>(fa, row_src + (long long)(g * n_rep + r) * D, pos, rotate, fa.q_norm_w, lane,
+                                 q_s + r * D, nullptr);
+            if (makes_kv && pos / TILE >= tile_begin && pos / TILE < tile_end &&
+                (pos / TILE - tile_begin) % WARPS == warp) {
+                const int page = table[pos / page_size];
+                if (page < 0 || page >= num_pages) {
+                    bad_page = true;
+                } else {
+                    const long long prow = (((long long)page * nkv + g) * page_size + pos % page_size) * D;
+                    __nv_bfloat16* kv_lin = row_s + warp * 2 * D;              // [key row | value row]
+                    rope_norm_row<D>(fa, row_src + (long long)(nq + g) * D, pos, rotate, fa.k_norm_w, lane, kv_lin,
+                                     fa.k_pool_w + prow);
+                    for (int c = 2 * lane; c < D; c += 64) {
+                        const float2 x = raw2(fa, row_src + (long long)(nq + nkv + g) * D + c);
+                        const __nv_bfloat162 b = __floats2bfloat162_rn(x.x, x.y);
+                        *(__nv_bfloat162*)(kv_lin + D + c) = b;
+                        *(__nv_bfloat162*)(fa.v_pool_w + prow + c) = b;
+                    }
                 }
-                __nv_bfloat16* kv_lin = row_s + warp * 2 * D;              // [key row | value row]
-                row_finish<D>(rk, rotate, cs, sn, knorm, kw1, kw2, fa.eps, lane, kv_lin, fa.k_pool_w + prow);
-                const __nv_bfloat162 va = __floats2bfloat162_rn(got[2].x, got[2].y);
-                const __nv_bfloat162 vb = __floats2bfloat162_rn(got[3].x, got[3].y);
-                *(__nv_bfloat162*)(kv_lin + D + j) = va;
-                *(__nv_bfloat162*)(kv_lin + D + j + D / 2) = vb;
-                *(__nv_bfloat162*)(fa.v_pool_w + prow + j) = va;
-                *(__nv_bfloat162*)(fa.v_pool_w + prow + j + D / 2) = vb;
+            }
+        } else {
+            // this lane's cosines, sines and norm weights are the same for every query row; the
+            // loads of two rows and of the tables are in flight together
+            static_assert(RowRegs<D>::IT == 1, "head size 128: one pair of neighbours per lane and half");
+            float2 cs[1], sn[1], w1[1], w2[1];
+            const int j = 2 * lane;
+            const bool norm = fa.q_norm_w != nullptr;
+            cs[0] = sn[0] = w1[0] = w2[0] = make_float2(0.f, 0.f);
+            if (rotate) {
+                cs[0] = *(const float2*)(fa.cos_tab + (long long)pos * (D / 2) + j);
+                sn[0] = *(const float2*)(fa.sin_tab + (long long)pos * (D / 2) + j);
+            }
+            if (norm) {
+                w1[0] = *(const float2*)(fa.q_norm_w + j);
+                w2[0] = *(const float2*)(fa.q_norm_w + j + D / 2);
+            }
+            const long long row_src = (long long)t * fa.qkv_stride;
+            const long long q_src = row_src + (long long)(g * n_rep) * D;
+            auto load_two = [&](int r, RowRegs<D>& ra, RowRegs<D>& rb) {
+                // rows r and r + WARPS of the group: four places, one round of loads
+                const bool two = r + WARPS < n_rep;
+                const long long at[4] = {q_src + (long long)r * D + j, q_src + (long long)r * D + j + D / 2,
+                                         q_src + (long long)(r + WARPS) * D + j,
+                                         q_src + (long long)(r + WARPS) * D + j + D / 2};
+                float2 got[4];
+                raw2x4(fa, at, two ? 4 : 2, got);
+                ra.u[0] = got[0]; ra.v[0] = got[1];
+                rb.u[0] = got[2]; rb.v[0] = got[3];
+            };
+            RowRegs<D> ra, rb;
+            if (warp < n_rep) load_two(warp, ra, rb);
+            for (int i = threadIdx.x; i < 16 * D / 2; i += WARPS * 32) ((uint32_t*)q_s)[i] = 0u;
+            __syncthreads();
+            for (int r = warp; r < n_rep; r += 2 * WARPS) {
+                if (r != warp) load_two(r, ra, rb);
+                row_finish<D>(ra, rotate, cs, sn, norm, w1, w2, fa.eps, lane, q_s + r * D, nullptr);
+                if (r + WARPS < n_rep)
+                    row_finish<D>(rb, rotate, cs, sn, norm, w1, w2, fa.eps, lane, q_s + (r + WARPS) * D, nullptr);
+            }
+            // The warp whose tiles include the new position makes that position's key (encoded,
+            // normalised) and value now, for the page and, kept in shared memory, for its tile later:
+            // at the end of the loop these loads and the arithmetic would lengthen the whole kernel.
+            if (makes_kv && pos / TILE >= tile_begin && pos / TILE < tile_end &&
+                (pos / TILE - tile_begin) % WARPS == warp) {
+                const int page = table[pos / page_size];
+                if (page < 0 || page >= num_pages) {
+                    bad_page = true;
+                } else {
+                    const long long prow = (((long long)page * nkv + g) * page_size + pos % page_size) * D;
+                    const long long k_src = row_src + (long long)(nq + g) * D, v_src = row_src + (long long)(nq + nkv + g) * D;
+                    const long long at[4] = {k_src + j, k_src + j + D / 2, v_src + j, v_src + j + D / 2};
+                    float2 got[4];
+                    raw2x4(fa, at, 4, got);
+                    RowRegs<D> rk;
+                    rk.u[0] = got[0]; rk.v[0] = got[1];
+                    float2 kw1[1], kw2[1];
+                    kw1[0] = kw2[0] = make_float2(0.f, 0.f);
+                    const bool knorm = fa.k_norm_w != nullptr;
+                    if (knorm) {
+                        kw1[0] = *(const float2*)(fa.k_norm_w + j);
+                        kw2[0] = *(const float2*)(fa.k_norm_w + j + D / 2);
+                    }
+                    __nv_bfloat16* kv_lin = row_s + warp * 2 * D;              // [key row | value row]
+                    row_finish<D>(rk, rotate, cs, sn, knorm, kw1, kw2, fa.eps, lane, kv_lin, fa.k_pool_w + prow);
+                    const __nv_bfloat162 va = __floats2bfloat162_rn(got[2].x, got[2].y);
+                    const __nv_bfloat162 vb = __floats2bfloat162_rn(got[3].x, got[3].y);
+                    *(__nv_bfloat162*)(kv_lin + D + j) = va;
+                    *(__nv_bfloat162*)(kv_lin + D + j + D / 2) = vb;
+                    *(__nv_bfloat162*)(fa.v_pool_w + prow + j) = va;
+                    *(__nv_bfloat162*)(fa.v_pool_w + prow + j + D / 2) = vb;
+                }
             }
         }
         __syncthreads();
@@ -1247,12 +1295,16 @@ CRANE_API int crane_paged_decode_attention_fused(
     const float* q_norm_w, const float* k_norm_w, float eps, void* out, float* part_o, float* part_ml,
     void* k_pool, void* v_pool, const int* cu_q, const int* kv_len,
     const int* block_table, int max_blocks, int num_pages, int page_size, int n_entries, int nq, int nkv,
-    int d, int window, float scale, int n_splits, int* err, cudaStream_t st) {
+    int d, int window, float scale, int n_splits, int rotary_dim, int interleaved, int norm_first,
+    float norm_offset, int* err, cudaStream_t st) {
     if (n_entries <= 0) return 0;
+    if (rotary_dim <= 0) rotary_dim = d;
     if (!crane_paged_decode_attention_supports(d, nq, nkv) || n_splits < 1 || n_splits > 64 || (d & 3) ||
-        (qkv_stride & 1) || (part_stride & 1))
+        (qkv_stride & 1) || (part_stride & 1) || rotary_dim > d || (rotary_dim & 1))
         return (int)cudaErrorInvalidValue;
     FusedArgs fa;
+    fa.rope = RopeParams{rotary_dim, interleaved ? 1 : 0, norm_first ? 1 : 0, norm_offset};
+    fa.general = rope_is_default(fa.rope, d) ? 0 : 1;
     fa.qkv = (const __nv_bfloat16*)qkv; fa.qkv_parts = qkv_parts; fa.n_parts = n_parts;
     fa.part_stride = part_stride; fa.qkv_stride = qkv_stride; fa.has_kv = has_kv; fa.rotary = rotary;
     fa.cos_tab = cos_tab; fa.sin_tab = sin_tab; fa.table_len = table_len; fa.q_norm_w = q_norm_w;

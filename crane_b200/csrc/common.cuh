@@ -48,6 +48,100 @@ __device__ __forceinline__ float block_sum(float v, float* scratch32) {
     return warp_sum(t);
 }
 
+// How a mixer's heads are rotated and normalised.  The defaults are Hunyuan Dense's: the whole head
+// rotated in the contiguous-halves pairing, RMSNorm after the rotation, plain weights.
+struct RopeParams {
+    int rotary_dim;      // the leading elements of a head that are rotated (even, <= head size)
+    int interleaved;     // 0: element i pairs with i + rotary_dim / 2;  1: 2i with 2i + 1
+    int norm_first;      // 0: per-head RMSNorm after the rotation;  1: before it
+    float norm_offset;   // the norm multiplies by (norm_offset + w): 0 plain, 1 for weights stored as w - 1
+};
+static inline bool rope_is_default(const RopeParams& p, int d) {
+    return p.rotary_dim == d && !p.interleaved && !p.norm_first && p.norm_offset == 0.f;
+}
+// A head of d elements seen as d / 2 slots of two elements: slot i < rotary_dim / 2 holds a rotated
+// pair (its angle is column i of the tables), the other slots hold the neighbours behind the rotated part.
+__device__ __forceinline__ void rope_slot(const RopeParams& p, int i, int& ea, int& eb, bool& rot) {
+    const int hr = p.rotary_dim >> 1;
+    rot = i < hr;
+    if (rot) {
+        ea = p.interleaved ? 2 * i : i;
+        eb = p.interleaved ? 2 * i + 1 : i + hr;
+    } else {
+        ea = p.rotary_dim + 2 * (i - hr);
+        eb = ea + 1;
+    }
+}
+// One head row by one warp for any RopeParams: `load(e)` gives element e as float, `store(e, v)`
+// takes the result.  cos/sin tables are [positions][rotary_dim / 2].  nw: the norm's weight or null.
+template <int MAXS, typename Load, typename Store>
+__device__ __forceinline__ void rope_norm_general(const RopeParams& rp, int d, int pos, bool rotate,
+                                                  const float* __restrict__ cos_tab,
+                                                  const float* __restrict__ sin_tab,
+                                                  const float* __restrict__ nw, float eps, int lane,
+                                                  Load load, Store store) {
+    const int hr = rp.rotary_dim >> 1, slots = d >> 1;
+    float a[MAXS], b[MAXS];
+    float ss = 0.f;
+#pragma unroll
+    for (int s = 0; s < MAXS; ++s) {
+        const int i = lane + 32 * s;
+        a[s] = b[s] = 0.f;
+        if (i < slots) {
+            int ea, eb; bool rot;
+            rope_slot(rp, i, ea, eb, rot);
+            a[s] = load(ea);
+            b[s] = load(eb);
+            ss += a[s] * a[s] + b[s] * b[s];
+        }
+    }
+    if (nw != nullptr && rp.norm_first) {
+        unsigned m = 0xffffffffu;
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(m, ss, o);
+        const float rstd = rsqrtf(ss / (float)d + eps);
+#pragma unroll
+        for (int s = 0; s < MAXS; ++s) {
+            const int i = lane + 32 * s;
+            if (i < slots) {
+                int ea, eb; bool rot;
+                rope_slot(rp, i, ea, eb, rot);
+                a[s] = a[s] * rstd * (rp.norm_offset + nw[ea]);
+                b[s] = b[s] * rstd * (rp.norm_offset + nw[eb]);
+            }
+        }
+    }
+    ss = 0.f;
+#pragma unroll
+    for (int s = 0; s < MAXS; ++s) {
+        const int i = lane + 32 * s;
+        if (i < slots) {
+            if (rotate && i < hr) {
+                const float c = cos_tab[(long long)pos * hr + i], sn = sin_tab[(long long)pos * hr + i];
+                const float x1 = a[s], x2 = b[s];
+                a[s] = x1 * c - x2 * sn;
+                b[s] = x2 * c + x1 * sn;
+            }
+            ss += a[s] * a[s] + b[s] * b[s];
+        }
+    }
+    float rstd = 1.f;
+    const bool after = nw != nullptr && !rp.norm_first;
+    if (after) {
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        rstd = rsqrtf(ss / (float)d + eps);
+    }
+#pragma unroll
+    for (int s = 0; s < MAXS; ++s) {
+        const int i = lane + 32 * s;
+        if (i < slots) {
+            int ea, eb; bool rot;
+            rope_slot(rp, i, ea, eb, rot);
+            store(ea, after ? a[s] * rstd * (rp.norm_offset + nw[ea]) : a[s]);
+            store(eb, after ? b[s] * rstd * (rp.norm_offset + nw[eb]) : b[s]);
+        }
+    }
+}
+
 // Programmatic dependent launch: a kernel launched with the attribute may start
 // while the kernel before it in the stream is still running.  It must not touch
 // anything that kernel (or one before it) writes or reads-then-overwrites until

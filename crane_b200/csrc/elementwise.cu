@@ -342,7 +342,7 @@ __global__ void rope_norm_cache_kernel(GemmOut<T> qkv, int qkv_stride,
                                        T* __restrict__ q_out, T* __restrict__ k_pool,
                                        T* __restrict__ v_pool, int num_pages, int page_size,
                                        int n_tokens, int nq, int nkv, int d, int has_kv,
-                                       int rotary, int* err) {
+                                       int rotary, RopeParams rp, int general, int* err) {
     pdl_launch_dependents();
     const int heads = nq + (has_kv ? 2 * nkv : 0);
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -394,6 +394,13 @@ __global__ void rope_norm_cache_kernel(GemmOut<T> qkv, int qkv_stride,
     if (rotate && (pos < 0 || pos >= table_len)) {
         if (lane == 0) atomicOr(err, CRANE_ERR_POSITION_RANGE);
         rotate = false;
+    }
+    if (general) {
+        // another pairing, a partly rotated head, the norm first or (1 + w) weights: element by element
+        rope_norm_general<8>(rp, d, pos, rotate, cos_tab, sin_tab, nw, eps, lane,
+                             [&](int e) { return qkv.load(src + e); },
+                             [&](int e, float v) { dst[e] = from_f32<T>(v); });
+        return;
     }
     if (PAIRS) {
         // each lane owns j, j + 1 and their partners j + d/2, j + 1 + d/2 for j = 2 lane, 2 lane + 64, ...
@@ -772,14 +779,19 @@ CRANE_API int crane_rope_norm_cache(int dtype, const void* qkv, const float* qkv
                                     const float* q_norm_w, const float* k_norm_w, float eps,
                                     void* q_out, void* k_pool, void* v_pool, int num_pages,
                                     int page_size, int n_tokens, int nq, int nkv, int d, int has_kv,
-                                    int rotary, int* err, cudaStream_t st) {
+                                    int rotary, int rotary_dim, int interleaved, int norm_first,
+                                    float norm_offset, int* err, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (d > 512 || (d & 1)) return (int)cudaErrorInvalidValue;
+    if (rotary_dim <= 0) rotary_dim = d;
+    if (rotary_dim > d || (rotary_dim & 1)) return (int)cudaErrorInvalidValue;
+    const RopeParams rp{rotary_dim, interleaved ? 1 : 0, norm_first ? 1 : 0, norm_offset};
+    const int general = rope_is_default(rp, d) ? 0 : 1;
     const int heads = nq + (has_kv ? 2 * nkv : 0);
     const long long warps = (long long)n_tokens * heads;
     const int threads = 128;
     const int blocks = (int)((warps * 32 + threads - 1) / threads);
-    if (dtype == 1 && d == 128 && qkv != nullptr && qkv_stride % 8 == 0 && n_tokens >= 32 &&
+    if (!general && dtype == 1 && d == 128 && qkv != nullptr && qkv_stride % 8 == 0 && n_tokens >= 32 &&
         ((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)cos_tab |
          (uintptr_t)sin_tab | (uintptr_t)q_norm_w | (uintptr_t)k_norm_w) % 16 == 0) {
         const long long lanes = warps * 8;
@@ -800,11 +812,11 @@ CRANE_API int crane_rope_norm_cache(int dtype, const void* qkv, const float* qkv
             return crane_launch(rope_norm_cache_kernel<T, true>, dim3(blocks), dim3(threads), 0, st, src,
                                 qkv_stride, positions, tok_entry, block_table, max_blocks, cos_tab, sin_tab,
                                 table_len, q_norm_w, k_norm_w, eps, (T*)q_out, (T*)k_pool, (T*)v_pool,
-                                num_pages, page_size, n_tokens, nq, nkv, d, has_kv, rotary, err);
+                                num_pages, page_size, n_tokens, nq, nkv, d, has_kv, rotary, rp, general, err);
         return crane_launch(rope_norm_cache_kernel<T, false>, dim3(blocks), dim3(threads), 0, st, src,
                             qkv_stride, positions, tok_entry, block_table, max_blocks, cos_tab, sin_tab,
                             table_len, q_norm_w, k_norm_w, eps, (T*)q_out, (T*)k_pool, (T*)v_pool,
-                            num_pages, page_size, n_tokens, nq, nkv, d, has_kv, rotary, err);
+                            num_pages, page_size, n_tokens, nq, nkv, d, has_kv, rotary, rp, general, err);
     });
 }
 

@@ -144,9 +144,15 @@ class ModelRunner:
         self._graphs: Dict[object, tuple] = {}
         self._shape_seen: Dict[tuple, int] = {}      # how often a shape of small step has come
         self._graph_generation = -1
+        has_state = any(n.kind == "state" for n in self.model.cache_needs())
         self._graphs_ok = (self.cfg.use_cuda_graphs and not self.rt.exact and self.model.capturable()
-                           and all(n.kind != "state" for n in self.model.cache_needs()))
+                           and (not has_state or self.model.state_graph_safe()))
+        # Steps of single tokens are padded to a batch-size bucket with copies of their first entry
+        # unless a mixer keeps state: a copy would advance that request's state twice.  Such a model's
+        # decode steps are padded like steps with prompt portions: rows of no entry, entries without rows.
+        self._pad_with_copies = not has_state
         self.graph_replays = 0
+        self.graph_captures = 0                    # steps that ran kernel by kernel and were recorded for their shape
         self._step_done = torch.cuda.Event()       # recorded behind every step's kernels
         self._step_done.record()
 
@@ -248,7 +254,8 @@ class ModelRunner:
         # a pure decode step is padded to a fixed batch size (copies of entry 0, which
         # recompute and rewrite exactly what entry 0 does) so that a captured graph fits it
         pad_to = 0
-        if (self._graphs_ok and max(counts) == 1 and all(len(e.want) == 1 for e in entries)):
+        if (self._graphs_ok and self._pad_with_copies and max(counts) == 1
+                and all(len(e.want) == 1 for e in entries)):
             pad_to = self._bucket(n_entries)
         m = self.meta
         m.copied.synchronize()                      # the last step's copy has left the host block
@@ -269,7 +276,7 @@ class ModelRunner:
         # worth the split-KV decode kernel (the prefill kernel would give each a whole query tile with
         # one live row and walk its context unsliced).
         singles = 0
-        if not pad_to and n_tokens > n_entries and not self.rt.exact:
+        if not pad_to and not self.rt.exact:
             one = cnt == 1
             if one.any() and int(m.view("kv_len", n_entries, False)[one].sum()) >= self.cfg.mixed_decode_min_keys:
                 singles = int(one.sum())
@@ -400,7 +407,7 @@ class ModelRunner:
                 self._shape_seen[shapes[0]] = -8
         if entry is None:
             # once eagerly, so that every buffer exists; then the same step again under capture
-            # (it rewrites the same cache rows with the same values)
+            # (nothing runs while it is recorded)
             eager = self.model.forward(ctx, self.pools.layers)
             if self._graph_generation != self.rt.ws.generation:
                 self._graphs.clear()
@@ -418,7 +425,13 @@ class ModelRunner:
                     "a step could not be recorded as a CUDA graph; a part that reads results on the "
                     "host in its forward must set `capturable = False` (or run the engine with "
                     "use_cuda_graphs=False)") from exc
-            entry = (graph, logits, self.rt.launches - before)
+            # The step itself has just run, kernel by kernel; the graph serves the later steps of its
+            # shape.  (Replaying it now as well would run the step twice, which pages bear, since the
+            # same rows get the same values, but a mixer's per-request state does not.)
+            self._graphs[key] = (graph, logits, self.rt.launches - before)
+            self.rt.launches = before
+            self.graph_captures += 1
+            return eager
         self._graphs[key] = entry                   # (back) at the end: the most recently used
         graph, logits, launches = entry
         graph.replay()

@@ -22,7 +22,7 @@ _SIGNATURES = {
     "crane_embed_gather": [I, P, P, P, I, I, I, P, I, P, P],
     "crane_add_rmsnorm": [I, P, P, P, I, L, P, P, P, I, I, F, P],
     "crane_rope_norm_cache": [I, P, P, I, L, I, P, P, P, I, P, P, I, P, P, F, P, P, P, I, I, I, I,
-                              I, I, I, I, P, P],
+                              I, I, I, I, I, I, I, F, P, P],
     "crane_silu_mul": [I, P, P, I, L, P, I, I, I, P],
     "crane_to_float": [I, P, P, L, P],
     "crane_sum_parts": [P, I, L, L, P, L, I, I, P],
@@ -35,7 +35,7 @@ _SIGNATURES = {
     "crane_paged_prefill_attention_supports": [I, I, I],
     "crane_paged_prefill_attention": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
     "crane_paged_decode_attention_fused": [P, P, I, L, I, I, I, P, P, I, P, P, F, P, P, P, P, P, P, P, P,
-                                           I, I, I, I, I, I, I, I, F, I, P, P],
+                                           I, I, I, I, I, I, I, I, F, I, I, I, I, F, P, P],
     "crane_prefill_attention_tc_supports": [I, I, I, I],
     "crane_prefill_attention_tc": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
     "crane_repetition_penalty": [P, L, I, I, P, I, P, P, P],
@@ -135,7 +135,11 @@ class Kernels:
 
     def rope_norm_cache(self, qkv: Act, qkv_cols: int, dtype, positions, tok_entry, block_table,
                         cos, sin, q_norm_w, k_norm_w, eps, q_out, k_pool, v_pool, page_size, nq,
-                        nkv, d, has_kv: bool, rotary: bool, err) -> None:
+                        nkv, d, has_kv: bool, rotary: bool, err, rope=None) -> None:
+        """``rope``: (rotary_dim, interleaved pairs, norm before the rotation,
+        norm weight offset); None: the whole head, contiguous halves, norm after,
+        plain weights.  cos/sin are [positions, rotary_dim / 2]."""
+        rd, inter, first, off = rope or (d, False, False, 0.0)
         whole, parts, n_parts, stride = _split(qkv)
         n_tokens = q_out.shape[0]
         num_pages = k_pool.shape[0] if k_pool is not None else 0
@@ -145,8 +149,8 @@ class Kernels:
             _ptr(tok_entry), _ptr(block_table), max_blocks, _ptr(cos), _ptr(sin),
             cos.shape[0] if cos is not None else 0, _ptr(q_norm_w), _ptr(k_norm_w), float(eps),
             q_out.data_ptr(), _ptr(k_pool), _ptr(v_pool), num_pages, page_size, n_tokens, nq, nkv,
-            d, 1 if has_kv else 0, 1 if rotary else 0, err.data_ptr(), self._stream(q_out)),
-            "rope_norm_cache")
+            d, 1 if has_kv else 0, 1 if rotary else 0, int(rd), 1 if inter else 0, 1 if first else 0,
+            float(off), err.data_ptr(), self._stream(q_out)), "rope_norm_cache")
 
     def silu_mul(self, gu: Act, out, blocked: bool = False) -> None:
         """out = silu(gate) * up.  ``gu`` rows are [gate | up], or, ``blocked``,
@@ -349,10 +353,12 @@ class Kernels:
 
     def paged_decode_attention_fused(self, qkv: Act, qkv_cols, has_kv, cos, sin, q_norm_w, k_norm_w,
                                      eps, out, k_pool, v_pool, cu_q, kv_len, block_table, page_size,
-                                     nq, nkv, d, window, scale, n_splits, part_o, part_ml, err) -> None:
+                                     nq, nkv, d, window, scale, n_splits, part_o, part_ml, err,
+                                     rope=None) -> None:
         """One token per entry, straight from the q/k/v product: rotary encoding,
         per-head norm, cache write and attention in one kernel, then the merge of
-        the key slices."""
+        the key slices.  ``rope`` as in ``rope_norm_cache``."""
+        rd, inter, first, off = rope or (d, False, False, 0.0)
         whole, parts, n_parts, stride = _split(qkv)
         n_entries = kv_len.shape[0]
         self._check(self.lib.crane_paged_decode_attention_fused(
@@ -361,7 +367,8 @@ class Kernels:
             _ptr(k_norm_w), float(eps), out.data_ptr(), _ptr(part_o), _ptr(part_ml),
             k_pool.data_ptr(), v_pool.data_ptr(), cu_q.data_ptr(), kv_len.data_ptr(),
             block_table.data_ptr(), block_table.shape[1], k_pool.shape[0], page_size, n_entries, nq,
-            nkv, d, int(window), float(scale), int(n_splits), err.data_ptr(), self._stream(out)),
+            nkv, d, int(window), float(scale), int(n_splits), int(rd), 1 if inter else 0,
+            1 if first else 0, float(off), err.data_ptr(), self._stream(out)),
             "paged_decode_attention_fused")
 
     # ---- sampling -------------------------------------------------------

@@ -26,7 +26,12 @@ class GqaAttention(Part):
     ``bias`` (q/k/v/o biases), ``qk_norm`` + ``qk_norm_eps``, ``window`` (0: all
     earlier positions), ``own_kv`` (False: reads another layer's cache),
     ``position`` (a PartSpec of kind position, or None), ``scale`` (default
-    1/sqrt(head_dim)).
+    1/sqrt(head_dim)); and how heads are rotated and normalised, whose defaults
+    are the reference's: ``rotary_dim`` (the leading elements of a head that
+    are rotated; default all), ``rope_pairing`` ("half": element i with
+    i + rotary_dim/2, or "interleaved": 2i with 2i + 1), ``qk_norm_order``
+    ("after_rope" or "before_rope"), ``qk_norm_offset`` (the norms multiply by
+    offset + w: 0, or 1 for weights stored as w - 1).
     Tensors: ``<prefix>{q,k,v,o}_proj.weight`` (+ ``.bias``),
     ``<prefix>query_layernorm.weight`` / ``key_layernorm.weight`` [head_dim]."""
     kind = "mixer"
@@ -78,6 +83,16 @@ class GqaAttention(Part):
         if self.position is not None:
             self.position.load(weights, rt)          # a position encoding may have tensors of its own
         self.qkv_cols = self.qkv_w.shape[0]
+        rotary_dim = int(a.get("rotary_dim") or self.d)
+        pairing, order = a.get("rope_pairing") or "half", a.get("qk_norm_order") or "after_rope"
+        if rotary_dim % 2 or not 0 < rotary_dim <= self.d:
+            raise ValueError(f"{p}: rotary_dim {rotary_dim} must be even and at most head_dim {self.d}")
+        if pairing not in ("half", "interleaved") or order not in ("after_rope", "before_rope"):
+            raise ValueError(f"{p}: rope_pairing is 'half' or 'interleaved', qk_norm_order 'after_rope' or "
+                             f"'before_rope'; got {pairing!r}, {order!r}")
+        # (rotated width, interleaved pairs, norm before the rotation, offset added to the norm weights)
+        self.rope = (rotary_dim, pairing == "interleaved", order == "before_rope",
+                     float(a.get("qk_norm_offset") or 0.0))
         self.max_splits = int(os.environ.get("CRANE_DECODE_SPLITS", "64"))
 
     def cache_need(self) -> CacheNeed:
@@ -92,6 +107,9 @@ class GqaAttention(Part):
         cos = sin = None
         if self.position is not None:
             cos, sin = self.position.tables(rt, ctx.max_positions)
+            if cos.shape[1] * 2 != self.rope[0]:
+                raise ValueError(f"{self.prefix}: the position encoding gives tables for a rotated width of "
+                                 f"{cos.shape[1] * 2}, the mixer rotates {self.rope[0]}")
         table = ctx.block_tables[cache.group]
         o = rt.ws.get("attn_o", n, self.nq * self.d, rt.dtype)
         decode = (not rt.exact and ctx.max_q_len == 1 and n == ctx.n_entries
@@ -108,14 +126,14 @@ class GqaAttention(Part):
                                            self.k_norm, self.eps, o, cache.k, cache.v, ctx.cu_q,
                                            ctx.kv_len, table, cache.page_size, self.nq, self.nkv,
                                            self.d, self.window, self.scale, splits, part_o, part_ml,
-                                           rt.err)
+                                           rt.err, rope=self.rope)
             rt.launches += 1 if splits <= 8 else 2     # the merge is a launch of its own above 8 slices
             return rt.linear(o, self.o_w, self.o_b, "attn_out")
         q = rt.ws.get("attn_q", n, self.nq * self.d, rt.dtype)
         k.rope_norm_cache(qkv, self.qkv_cols, rt.dtype, ctx.positions, ctx.tok_entry, table, cos,
                           sin, self.q_norm, self.k_norm, self.eps, q, cache.k, cache.v,
                           cache.page_size, self.nq, self.nkv, self.d, self.own_kv,
-                          self.position is not None, rt.err)
+                          self.position is not None, rt.err, rope=self.rope)
         use_tc = (not rt.exact and rt.use_tc_attention
                   and k.prefill_attention_tc_supports(self.d, self.nq, self.nkv, cache.page_size))
         use_mma = not rt.exact and k.prefill_attention_supports(self.d, self.nq, self.nkv)

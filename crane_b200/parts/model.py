@@ -72,6 +72,11 @@ class DecoderModel:
             parts += list(b.parts())
         return all(getattr(p, "capturable", True) for p in parts)
 
+    def state_graph_safe(self) -> bool:
+        """Whether every mixer that keeps per-request state bears graphs and padding."""
+        return all(getattr(b.mixer, "state_graph_safe", False) for b in self.blocks
+                   if b.mixer.cache_need().kind == "state")
+
     def forward(self, ctx, caches: List[LayerCache]) -> torch.Tensor:
         """Runs the step's tokens through the schedule (``caches``: one entry
         per step of the schedule) and returns float logits

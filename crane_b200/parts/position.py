@@ -20,12 +20,17 @@ _TABLES = {}
 
 @register_part("position", "rope")
 class Rope(Part):
-    """params: ``head_dim``, ``theta``, ``alpha`` (<= 0: none), ``max_positions``.
-    No tensors.  ``tables(rt, limit)`` gives (cos, sin) for positions < limit."""
+    """params: ``head_dim``, ``theta``, ``alpha`` (<= 0: none), ``max_positions``,
+    ``rotary_dim`` (the rotated width of a head; default: all of it, which is
+    what the reference does).  No tensors.  ``tables(rt, limit)`` gives (cos,
+    sin) [positions < limit, rotary_dim / 2]."""
     kind = "position"
 
+    def width(self) -> int:
+        return int(self.params.get("rotary_dim") or self.params["head_dim"])
+
     def inv_freq(self) -> np.ndarray:
-        d = int(self.params["head_dim"])
+        d = self.width()
         base = float(self.params["theta"])
         alpha = float(self.params.get("alpha") or 0.0)
         if alpha > 0.0:
@@ -35,7 +40,7 @@ class Rope(Part):
 
     def tables(self, rt, limit: int):
         n = min(int(self.params["max_positions"]), int(limit))
-        key = (int(self.params["head_dim"]), float(self.params["theta"]),
+        key = (self.width(), float(self.params["theta"]),
                float(self.params.get("alpha") or 0.0), n, str(rt.device))
         if key not in _TABLES:
             pos = np.arange(n, dtype=np.float32)[:, None]

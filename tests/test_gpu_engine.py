@@ -319,7 +319,7 @@ def test_small_steps_replay_graphs_with_the_same_logits(name, model_folders):
             ids = list(range(4)) + [4, 5] + [10, 11, 12, 13]
             out.append(r.step([StepEntry(i, [int(rng.integers(0, vocab))], [0]) for i in ids]).float().cpu())
         r.rt.check_errors()
-        runs[graphs] = (out, r.graph_replays)
+        runs[graphs] = (out, r.graph_replays + r.graph_captures)     # steps that took the graph path
         for i in list(range(6)) + [10, 11, 12, 13]:
             r.end(i)
         r.table.check()

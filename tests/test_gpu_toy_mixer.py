@@ -113,3 +113,127 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
         eng.table.check()
     # and the state really matters: without the decay the logits differ
     assert float((whole_a[5] - whole_a[4]).abs().max()) > 0
+
+
+def register_device_toy():
+    """The same running sum written so that a recorded graph can replay it: it
+    reads the step's metadata on the device only, leaves padding rows (entry -1)
+    alone and touches no slot for an entry without rows."""
+    from crane_b200.config import (LayerSpec, ModelSpec, PartSpec, ScheduleStep, register_architecture)
+    from crane_b200.parts import CacheNeed, Part, register_part
+    from crane_b200.weights import TensorSpec
+
+    @register_part("mixer", "toy_running_sum_on_device")
+    class RunningSumOnDevice(Part):
+        kind = "mixer"
+        state_graph_safe = True
+
+        @classmethod
+        def manifest(cls, spec):
+            h = spec.params["hidden_size"]
+            return {spec.prefix + "w": TensorSpec((h, h))}
+
+        def load(self, weights, rt):
+            self.w = weights[self.prefix + "w"]
+            self.h = self.params["hidden_size"]
+            self.decay = float(self.params["decay"])
+
+        def cache_need(self):
+            return CacheNeed("state", state_shape=(self.h,), state_dtype=torch.float32)
+
+        def forward(self, h, ctx, cache, rt):
+            n, dev = h.shape[0], h.device
+            ent = ctx.tok_entry.long()                         # -1: a row that pads the step
+            live = ent >= 0
+            e_safe = ent.clamp_min(0)
+            cu = ctx.cu_q.long()
+            q_len = cu[1:] - cu[:-1]
+            valid = q_len > 0                                  # False: an entry that pads the step
+            slots = ctx.slots.long()
+            fresh = (ctx.kv_len.long() - q_len) == 0           # the request's first tokens: state starts at 0
+            prev = cache.state[slots] * (valid & ~fresh)[:, None]
+            idx = torch.arange(n, device=dev)
+            gap = idx[:, None] - idx[None, :]
+            same = (ent[:, None] == ent[None, :]) & live[:, None] & live[None, :] & (gap >= 0)
+            weights = torch.where(same, torch.pow(self.decay, gap.clamp_min(0).float()), 0.0)
+            first = idx - cu[e_safe]
+            s = weights @ h.float() + (torch.pow(self.decay, (first + 1).float()) * live)[:, None] * prev[e_safe]
+            out = (s @ self.w.float().T).to(h.dtype)
+            s_last = s[(cu[1:] - 1).clamp_min(0)]              # the state behind each entry's last row
+            n_slots = cache.state.shape[0]
+            onehot = ((slots[:, None] == torch.arange(n_slots, device=dev)[None, :]) & valid[:, None]).float()
+            hit = onehot.sum(0) > 0
+            cache.state.copy_(torch.where(hit[:, None], onehot.T @ s_last, cache.state))
+            return out
+
+    def build_spec(cfg):
+        h = cfg["hidden_size"]
+        norm = lambda p: PartSpec("norm", "rms_norm", {"size": h, "eps": cfg["eps"]}, p)
+        ffn = lambda p: PartSpec("ffn", "swiglu", {"hidden_size": h, "intermediate_size": cfg["inter"]}, p)
+        attn = PartSpec("mixer", "gqa_attention", {
+            "hidden_size": h, "num_heads": 2, "num_kv_heads": 1, "head_dim": 16, "bias": False,
+            "qk_norm": False, "window": 0, "own_kv": True,
+            "position": PartSpec("position", "rope", {"head_dim": 16, "theta": 1e4, "alpha": 0.0,
+                                                      "max_positions": cfg["max_pos"]})}, "l1.attn.")
+        toy = PartSpec("mixer", "toy_running_sum_on_device", {"hidden_size": h, "decay": cfg["decay"]}, "l0.mix.")
+        layers = [LayerSpec("prenorm_residual", {"norm1": norm("l0.n1."), "mixer": toy,
+                                                 "norm2": norm("l0.n2."), "ffn": ffn("l0.ffn.")}),
+                  LayerSpec("prenorm_residual", {"norm1": norm("l1.n1."), "mixer": attn,
+                                                 "norm2": norm("l1.n2."), "ffn": ffn("l1.ffn.")})]
+        return ModelSpec("ToyDeviceStateForCausalLM", h, cfg["vocab"], cfg["max_pos"],
+                         PartSpec("embed", "token_embedding", {"vocab_size": cfg["vocab"], "hidden_size": h}, "emb."),
+                         layers, [ScheduleStep(0), ScheduleStep(1), ScheduleStep(0)],
+                         norm("final."), PartSpec("head", "lm_head", {"vocab_size": cfg["vocab"],
+                                                                      "hidden_size": h, "tied_to": "emb.weight"}, "head."))
+
+    register_architecture("ToyDeviceStateForCausalLM", lambda d: d, build_spec)
+
+
+def test_a_mixer_with_state_replays_graphs_when_it_bears_padding():
+    """A model with a stateful mixer that says ``state_graph_safe`` replays graphs
+    on the bfloat16 path: its steps of single tokens are padded with rows of no
+    entry and entries without rows (never with copies of an entry), and give
+    what the engine without graphs gives; states of requests that sit a step out
+    or share a step with padding entries stay as they were."""
+    from crane_b200.config import EngineConfig, resolve
+    from crane_b200.engine import ModelRunner, StepEntry
+    from crane_b200.parts import model_manifest
+    from crane_b200.weights.random_init import random_tensors
+    register_device_toy()
+    cfg = {"architectures": ["ToyDeviceStateForCausalLM"], "hidden_size": 48, "inter": 64, "vocab": 90,
+           "max_pos": 256, "eps": 1e-5, "decay": 0.7}
+    spec = resolve(cfg).build_spec(cfg)
+    tensors = random_tensors(model_manifest(spec), 3, torch.bfloat16, std=0.1)
+    rng = np.random.default_rng(1)
+    reqs = {i: rng.integers(0, 90, n).tolist() for i, n in ((1, 40), (2, 23), (3, 31))}
+    runs = {}
+    for graphs in (False, True):
+        r = ModelRunner(None, EngineConfig(dtype="bfloat16", page_size=16, num_pages=16, max_concurrent=4,
+                                           max_batched_tokens=64, use_cuda_graphs=graphs),
+                        config=cfg, tensors=tensors)
+        assert r._graphs_ok == graphs
+        out = []
+        # prompts in portions, then single tokens: three requests, then two (one sits steps out), then three
+        out.append(r.step([StepEntry(1, reqs[1][:20], [19]), StepEntry(2, reqs[2][:9], [8])]).float().cpu())
+        out.append(r.step([StepEntry(3, reqs[3][:12], [11]), StepEntry(1, reqs[1][20:30], [9])]).float().cpu())
+        pos = {1: 30, 2: 9, 3: 12}
+        for live in ([1, 2, 3], [1, 2, 3], [1, 2, 3], [1, 3], [1, 3], [1, 3], [2], [1, 2, 3], [1, 2, 3]):
+            torch.cuda.synchronize()                      # an idle device: a step of a seen shape replays its graph
+            out.append(r.step([StepEntry(i, [reqs[i][pos[i]]], [0]) for i in live]).float().cpu())
+            for i in live:
+                pos[i] += 1
+        torch.cuda.synchronize()
+        r.rt.check_errors()
+        runs[graphs] = (out, r.graph_replays)
+        # whole sequences in a fresh pass give the same last logits
+        for i in (1, 2, 3):
+            r.end(i)
+        whole = r.step([StepEntry(7, reqs[1][:pos[1]], [pos[1] - 1])]).float().cpu()
+        assert rel_err(whole[0], runs[graphs][0][-1][0]) < 3e-2
+        r.end(7)
+    assert runs[False][1] == 0 and runs[True][1] >= 3
+    for a, b in zip(runs[False][0], runs[True][0]):
+        assert a.shape == b.shape
+        # (padded steps send single tokens through the prefill attention, unpadded ones through the
+        # fused decode attention: the same values up to bfloat16 rounding)
+        assert (a - b).abs().max() <= 2e-2 * a.abs().max()
