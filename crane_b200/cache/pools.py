@@ -1,8 +1,10 @@
 """Device side of the cache: per layer the K and V page pools, or the state
 tensor, laid out for the page and slot numbers of ``PageTable``.
 
-K and V pools of a layer are [pages, kv_heads, page_size, head_dim]: the
-``page_size x head_dim`` slab of one (page, head) is contiguous.  Pages are
+The K pool of a layer is [pages, kv_heads, page_size, head_dim], its V pool
+[pages, kv_heads, page_size, v_head_dim] (as wide as the keys unless the mixer
+says otherwise): the ``page_size x width`` slab of one (page, head) is
+contiguous.  Pages are
 never cleared: what a request may read is decided by its length, not by the
 pages' content.
 """
@@ -16,16 +18,16 @@ from ..parts.base import CacheNeed, LayerCache
 from .manager import GroupSpec, PageTable
 
 
-def group_layers(needs: List[CacheNeed]) -> Tuple[List[Tuple[int, int, int]], List[int]]:
-    """Group keys (kv_heads, head_dim, window) in order of first use, and for
-    every layer the index of its group (-1: the layer holds no pages)."""
-    keys: List[Tuple[int, int, int]] = []
+def group_layers(needs: List[CacheNeed]) -> Tuple[List[Tuple[int, int, int, int]], List[int]]:
+    """Group keys (kv_heads, head_dim, window, value width) in order of first use,
+    and for every layer the index of its group (-1: the layer holds no pages)."""
+    keys: List[Tuple[int, int, int, int]] = []
     of_layer: List[int] = []
     for need in needs:
         if need.kind != "kv":
             of_layer.append(-1)
             continue
-        key = (need.kv_heads, need.head_dim, need.window)
+        key = (need.kv_heads, need.head_dim, need.window, need.value_dim)
         if key not in keys:
             keys.append(key)
         of_layer.append(keys.index(key))
@@ -38,7 +40,7 @@ def bytes_per_page(needs: List[CacheNeed], page_size: int, elem_size: int) -> Li
     out = [0] * len(keys)
     for need, g in zip(needs, of_layer):
         if g >= 0:
-            out[g] += 2 * need.kv_heads * page_size * need.head_dim * elem_size
+            out[g] += need.kv_heads * page_size * (need.head_dim + need.value_dim) * elem_size
     return out
 
 
@@ -56,10 +58,11 @@ class CachePools:
         self.layers: List[LayerCache] = []
         for need, g in zip(needs, self.group_of_layer):
             if need.kind == "kv":
-                shape = (pages_per_group[g], need.kv_heads, page_size, need.head_dim)
+                k_shape = (pages_per_group[g], need.kv_heads, page_size, need.head_dim)
+                v_shape = (pages_per_group[g], need.kv_heads, page_size, need.value_dim)
                 # zeros, not uninitialised memory: rows that a tile loads but masks must be finite
-                self.layers.append(LayerCache(need, g, torch.zeros(shape, dtype=dtype, device=device),
-                                              torch.zeros(shape, dtype=dtype, device=device), page_size))
+                self.layers.append(LayerCache(need, g, torch.zeros(k_shape, dtype=dtype, device=device),
+                                              torch.zeros(v_shape, dtype=dtype, device=device), page_size))
             elif need.kind == "state":
                 st = torch.zeros((max_requests, *need.state_shape), dtype=need.state_dtype,
                                  device=device)

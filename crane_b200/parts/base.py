@@ -68,8 +68,11 @@ def block_class(name: str):
 @dataclass(frozen=True)
 class CacheNeed:
     """What a mixer keeps between steps, per request.
-    ``kind == "kv"``: keys and values of ``kv_heads`` x ``head_dim`` per
-    position in pages, all positions (``window == 0``) or the last ``window``.
+    ``kind == "kv"``: keys of ``kv_heads`` x ``head_dim`` and values of
+    ``kv_heads`` x ``v_head_dim`` (0: as wide as the keys) per position in pages,
+    all positions (``window == 0``) or the last ``window``.  The two pools are
+    shaped independently, so values wider or narrower than keys need no change
+    to the cache.
     ``kind == "state"``: one tensor of ``state_shape`` / ``state_dtype`` in the
     request's slot.  ``kind == "none"``: nothing (or another layer's cache)."""
     kind: str = "none"
@@ -78,12 +81,18 @@ class CacheNeed:
     window: int = 0
     state_shape: Tuple[int, ...] = ()
     state_dtype: torch.dtype = torch.float32
+    v_head_dim: int = 0
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
 
 
 @dataclass
 class LayerCache:
-    """The storage one layer's mixer reads and writes.  For ``kv``: the K and V
-    pools [pages, kv_heads, page_size, head_dim] of the layer and the index of
+    """The storage one layer's mixer reads and writes.  For ``kv``: the K pool
+    [pages, kv_heads, page_size, head_dim] and the V pool [pages, kv_heads,
+    page_size, v_head_dim or head_dim] of the layer and the index of
     its layer group, whose block table for the step is
     ``ctx.block_tables[group]``.  For ``state``: a tensor [slots, *state_shape],
     indexed by ``ctx.slots``."""

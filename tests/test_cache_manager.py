@@ -116,3 +116,16 @@ def test_random_orders_keep_the_books_straight(seed):
     t.check()
     assert t.free_pages(0) == 40 and t.free_pages(1) == 24 and t.free_slots() == 5
     assert t.pages_reused() > 0
+
+
+def test_pools_shape_keys_and_values_independently():
+    """A mixer may keep values wider or narrower than its keys: the group key,
+    the bytes a page costs and (on a device) the pools' shapes follow."""
+    from crane_b200.cache.pools import bytes_per_page, group_layers
+    from crane_b200.parts import CacheNeed
+    needs = [CacheNeed("kv", kv_heads=2, head_dim=16), CacheNeed("kv", kv_heads=2, head_dim=16, v_head_dim=40),
+             CacheNeed("none"), CacheNeed("kv", kv_heads=2, head_dim=16), CacheNeed("kv", kv_heads=1, head_dim=24, v_head_dim=8)]
+    keys, of_layer = group_layers(needs)
+    assert keys == [(2, 16, 0, 16), (2, 16, 0, 40), (1, 24, 0, 8)] and of_layer == [0, 1, -1, 0, 2]
+    assert bytes_per_page(needs, 8, 2) == [2 * (2 * 8 * 32 * 2), 2 * 8 * 56 * 2, 1 * 8 * 32 * 2]
+    assert needs[0].value_dim == 16 and needs[1].value_dim == 40

@@ -237,3 +237,91 @@ def test_a_mixer_with_state_replays_graphs_when_it_bears_padding():
         # (padded steps send single tokens through the prefill attention, unpadded ones through the
         # fused decode attention: the same values up to bfloat16 rounding)
         assert (a - b).abs().max() <= 2e-2 * a.abs().max()
+
+
+def test_a_mixer_whose_values_are_wider_than_its_keys_gets_pools_of_its_own_shapes():
+    """A toy single-head attention with 8-wide keys and 24-wide values, defined
+    here: the cache manager gives it a K pool and a V pool of those widths, and
+    it steps in portions over reused pages like any other mixer."""
+    from crane_b200.config import (EngineConfig, LayerSpec, ModelSpec, PartSpec, ScheduleStep,
+                                   register_architecture, resolve)
+    from crane_b200.engine import ModelRunner, StepEntry
+    from crane_b200.parts import CacheNeed, Part, model_manifest, register_part
+    from crane_b200.weights import TensorSpec
+    from crane_b200.weights.random_init import random_tensors
+
+    @register_part("mixer", "toy_wide_values")
+    class WideValues(Part):
+        kind = "mixer"
+        capturable = False          # it plans on the host
+
+        @classmethod
+        def manifest(cls, spec):
+            h, dk, dv = (spec.params[k] for k in ("hidden_size", "key_dim", "value_dim"))
+            p = spec.prefix
+            return {p + "wq": TensorSpec((dk, h)), p + "wk": TensorSpec((dk, h)), p + "wv": TensorSpec((dv, h)),
+                    p + "wo": TensorSpec((h, dv))}
+
+        def load(self, weights, rt):
+            p = self.prefix
+            self.wq, self.wk, self.wv, self.wo = (weights[p + n] for n in ("wq", "wk", "wv", "wo"))
+
+        def cache_need(self):
+            return CacheNeed("kv", kv_heads=1, head_dim=self.params["key_dim"], v_head_dim=self.params["value_dim"])
+
+        def forward(self, h, ctx, cache, rt):
+            x = h.float()
+            q, k, v = x @ self.wq.float().t(), x @ self.wk.float().t(), x @ self.wv.float().t()
+            table = ctx.block_tables[cache.group].cpu().numpy()
+            ps = cache.page_size
+            out = torch.empty(h.shape[0], self.wv.shape[0], device=h.device)
+            for e in range(ctx.n_entries):
+                a, b, n = int(ctx.h_cu_q[e]), int(ctx.h_cu_q[e + 1]), int(ctx.h_kv_len[e])
+                for t in range(a, b):                          # write, then attend to everything so far
+                    p = n - (b - a) + (t - a)
+                    cache.k[int(table[e, p // ps]), 0, p % ps] = k[t].to(cache.k.dtype)
+                    cache.v[int(table[e, p // ps]), 0, p % ps] = v[t].to(cache.v.dtype)
+                pages = torch.from_numpy(table[e, :(n + ps - 1) // ps].astype(np.int64)).to(h.device)
+                keys = cache.k[pages, 0].reshape(-1, cache.k.shape[-1])[:n].float()
+                vals = cache.v[pages, 0].reshape(-1, cache.v.shape[-1])[:n].float()
+                for t in range(a, b):
+                    p = n - (b - a) + (t - a)
+                    w = torch.softmax(keys[:p + 1] @ q[t] / keys.shape[1] ** 0.5, dim=0)
+                    out[t] = w @ vals[:p + 1]
+            return (out @ self.wo.float().t()).to(h.dtype)
+
+    def build_spec(cfg):
+        h = cfg["hidden_size"]
+        norm = lambda p: PartSpec("norm", "rms_norm", {"size": h, "eps": 1e-5}, p)
+        ffn = PartSpec("ffn", "swiglu", {"hidden_size": h, "intermediate_size": 64}, "l0.ffn.")
+        mix = PartSpec("mixer", "toy_wide_values", {"hidden_size": h, "key_dim": 8, "value_dim": 24}, "l0.mix.")
+        layers = [LayerSpec("prenorm_residual", {"norm1": norm("l0.n1."), "mixer": mix, "norm2": norm("l0.n2."),
+                                                 "ffn": ffn})]
+        return ModelSpec("ToyWideValuesForCausalLM", h, cfg["vocab"], 128,
+                         PartSpec("embed", "token_embedding", {"vocab_size": cfg["vocab"], "hidden_size": h}, "emb."),
+                         layers, [ScheduleStep(0)], norm("final."),
+                         PartSpec("head", "lm_head", {"vocab_size": cfg["vocab"], "hidden_size": h,
+                                                      "tied_to": "emb.weight"}, "head."))
+
+    register_architecture("ToyWideValuesForCausalLM", lambda d: d, build_spec)
+    cfg = {"architectures": ["ToyWideValuesForCausalLM"], "hidden_size": 48, "vocab": 70}
+    spec = resolve(cfg).build_spec(cfg)
+    tensors = random_tensors(model_manifest(spec), 5, torch.float32, std=0.2)
+    r = ModelRunner(None, EngineConfig(dtype="float32", page_size=8, num_pages=9, max_concurrent=2,
+                                       max_batched_tokens=64), config=cfg, tensors=tensors)
+    lc = r.pools.layers[0]
+    assert tuple(lc.k.shape) == (9, 1, 8, 8) and tuple(lc.v.shape) == (9, 1, 8, 24)
+    rng = np.random.default_rng(2)
+    a, b = rng.integers(0, 70, 37).tolist(), rng.integers(0, 70, 30).tolist()
+    whole_a = r.step([StepEntry(1, a, list(range(37)))]).cpu()
+    r.end(1)
+    whole_b = r.step([StepEntry(2, b, list(range(30)))]).cpu()
+    r.end(2)
+    got_a = [r.step([StepEntry(3, a[:5], list(range(5)))]).cpu()]
+    out = r.step([StepEntry(3, a[5:20], list(range(15))), StepEntry(4, b[:9], list(range(9)))]).cpu()
+    got_a.append(out[:15]); got_b = [out[15:]]
+    out = r.step([StepEntry(4, b[9:], list(range(21))), StepEntry(3, a[20:], list(range(17)))]).cpu()
+    got_b.append(out[:21]); got_a.append(out[21:])
+    assert rel_err(torch.cat(got_a), whole_a) < 2e-5 and rel_err(torch.cat(got_b), whole_b) < 2e-5
+    r.end(3); r.end(4)
+    r.table.check()
