@@ -517,6 +517,314 @@ done:
     }
 }
 
+// ---------------------------------------------------------------------------
+// The same attention with TWO query heads of one kv head per CTA (the heads
+// 2y and 2y + 1 of head pair y = blockIdx.y; the group size nq / nkv must be
+// even).  Both heads have the same rows and therefore the same key tiles, so
+//   * every K and V tile that comes into shared memory serves two heads: half
+//     the traffic from L2 per product, which is what bounds the one-head kernel
+//     once a prompt's keys no longer stay close to the SMs;
+//   * the two heads take turns on the tensor cores: while one head's softmax
+//     threads work on their scores, the other head's products run.
+// Tensor memory: S of head A at columns 0..127, S of head B at 128..255, O of A
+// at 256..383, O of B at 384..511.  P (bf16 pairs, 64 columns) is written over
+// the first half of its head's S, from where the second product reads it.
+// One thread issues all products, in this order (j: key tile):
+//   S_A(0) S_B(0) | PV_A(j) S_A(j+1) PV_B(j) S_B(j+1) | ...
+// The tensor cores run products in the order of issue, so S_x(j+1) overwrites
+// P_x(j) only after PV_x(j) has read it, and a completed S_x(j) tells head x's
+// softmax threads that PV_x(j-1) is complete as well (O_x may be rescaled).
+// One softmax thread per query row and head: warps 4..7 head A, warps 8..11
+// head B (a warp reaches the 32 lanes of tensor memory given by its index
+// modulo 4).  They hold a whole row of 128 scores in registers, for which the
+// two softmax warpgroups take registers over from the first one (setmaxnreg).
+constexpr int PAIR_THREADS = 384;
+
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
+prefill_attn_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, const Params p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sm_q = smem;                          // [2 heads][2 halves][128][128 B]
+    uint8_t* sm_k = sm_q + 2 * TILE_BYTES;         // [2 stages][2 halves][128][128 B]
+    uint8_t* sm_v = sm_k + 2 * TILE_BYTES;         // [2 stages][2 halves (of d)][128 keys][128 B]
+    uint64_t* bars = (uint64_t*)(sm_v + 2 * TILE_BYTES);
+    uint64_t* q_full = bars;            // both heads' Q have landed
+    uint64_t* k_full = bars + 1;        // [2]
+    uint64_t* v_full = bars + 3;        // [2]
+    uint64_t* k_empty = bars + 5;       // [2] both heads' S products that read the stage are done
+    uint64_t* v_empty = bars + 7;       // [2] both heads' O products that read the stage are done
+    uint64_t* s_full = bars + 9;        // [2 heads] S of the head's next tile is complete
+    uint64_t* p_full = bars + 11;       // [2 heads] the head's P is in tensor memory (O rescaled if need be)
+    uint64_t* o_done = bars + 13;       // every product is complete
+    uint32_t* tmem_slot = (uint32_t*)(bars + 14);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    int e = 0, tile = blockIdx.x;
+    for (; e < p.n_entries; ++e) {
+        const int rows = p.cu_q[e + 1] - p.cu_q[e];
+        const int tiles = (p.skip_single && rows == 1) ? 0 : (rows + BQ - 1) / BQ;
+        if (tile < tiles) {
+            tile = tiles - 1 - tile;
+            break;
+        }
+        tile -= tiles;
+    }
+    const bool active = e < p.n_entries;
+    const int h_a = 2 * blockIdx.y, g = active ? h_a / (p.nq / p.nkv) : 0;
+    const int row0 = active ? p.cu_q[e] : 0, q_len = active ? p.cu_q[e + 1] - row0 : 0;
+    const int pos0 = active ? p.kv_len[e] - q_len : 0;
+    const int r_begin = tile * BQ, r_end = min(q_len, r_begin + BQ);
+    const int p_first = pos0 + r_begin, p_last = pos0 + r_end - 1;
+    const int lo = (p.window > 0 && p_first - p.window + 1 > 0) ? p_first - p.window + 1 : 0;
+    const int t_begin = lo / BKV, t_end = active ? p_last / BKV + 1 : 0;
+    const int n_tiles = max(0, t_end - t_begin);
+    const int* table = p.block_table + (long long)e * p.max_blocks;
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(q_full), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&k_full[s]), 1);
+            mbar_init(smem_u32(&v_full[s]), 1);
+            mbar_init(smem_u32(&k_empty[s]), 1);
+            mbar_init(smem_u32(&v_empty[s]), 1);
+            mbar_init(smem_u32(&s_full[s]), 1);
+            mbar_init(smem_u32(&p_full[s]), 4);          // the four warps of a head's softmax warpgroup
+        }
+        mbar_init(smem_u32(o_done), 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(tmem_slot)),
+                     "r"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+
+    if (warp < 4) {
+        // the copying and the issuing warps need few registers: the softmax warpgroups take the rest
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+        if (warp == 0 && n_tiles > 0) {
+            // ---------------- TMA: the whole warp (as in the one-head kernel) ----------------
+            pdl_wait();
+            if (lane == 0) {
+                mbar_expect_tx(smem_u32(q_full), 2 * TILE_BYTES);
+                for (int x = 0; x < 2; ++x) {
+                    tma_load_2d(smem_u32(sm_q + x * TILE_BYTES), &map_q, smem_u32(q_full), (h_a + x) * D,
+                                row0 + r_begin);
+                    tma_load_2d(smem_u32(sm_q + x * TILE_BYTES + HALF_BYTES), &map_q, smem_u32(q_full),
+                                (h_a + x) * D + 64, row0 + r_begin);
+                }
+            }
+            const int ps = p.page_size;                    // 16, 32, 64 or 128
+            const int shift = 31 - __clz(ps);
+            const int chunks = BKV >> shift;               // pages per tile: 8, 4, 2 or 1
+            const int per_kv = 2 * chunks;                 // copies per tile of K (or V)
+            const bool worker = lane < 2 * per_kv;
+            const int my_kv = lane / per_kv, c = (lane % per_kv) >> 1, hf = lane & 1;
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j & 1;
+                const uint32_t parity = ((j >> 1) & 1) ^ 1;
+                int blk = (((t_begin + j) * BKV) >> shift) + c;
+                blk = max(lo >> shift, min(blk, p_last >> shift));
+                int page = worker ? table[blk] : 0;
+                if (page < 0 || page >= p.num_pages) {
+                    atomicOr(p.err, CRANE_ERR_PAGE_RANGE);
+                    page = 0;
+                }
+                const int row = (page * p.nkv + g) << shift;
+                for (int kv = 0; kv < 2; ++kv) {
+                    uint64_t* full = kv ? &v_full[s] : &k_full[s];
+                    uint64_t* empty = kv ? &v_empty[s] : &k_empty[s];
+                    uint8_t* dst = (kv ? sm_v : sm_k) + s * TILE_BYTES;
+                    if (!mbar_wait(smem_u32(empty), parity, abort_flag)) goto done;
+                    if (lane == 0) mbar_expect_tx(smem_u32(full), TILE_BYTES);
+                    __syncwarp();
+                    if (worker && my_kv == kv)
+                        tma_load_2d(smem_u32(dst + hf * HALF_BYTES + c * ps * 128), kv ? &map_v : &map_k,
+                                    smem_u32(full), hf * 64, row);
+                }
+            }
+        } else if (warp == 1 && lane == 0 && n_tiles > 0) {
+            // ---------------- all products, one thread ----------------
+            const uint32_t id_s = idesc(false), id_o = idesc(true);
+            const uint64_t dq = desc_kmajor(smem_u32(sm_q)), dk = desc_kmajor(smem_u32(sm_k));
+            const uint64_t dv = desc_mnmajor(smem_u32(sm_v));
+            auto issue_s = [&](int x, int stage) {              // S_x = Q_x K^T
+                const uint64_t dqx = dq + (uint64_t)(x * (TILE_BYTES >> 4)), dks = dk + (uint64_t)(stage * (TILE_BYTES >> 4));
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint64_t off = (uint64_t)(((kk >> 2) * HALF_BYTES + (kk & 3) * 32) >> 4);
+                    umma(tmem_base + x * 128, dqx + off, dks + off, id_s, kk > 0);
+                }
+                umma_commit(smem_u32(&s_full[x]));
+            };
+            auto issue_pv = [&](int x, int stage, bool first) {  // O_x += P_x V, P_x from tensor memory
+                const uint64_t dvs = dv + (uint64_t)(stage * (TILE_BYTES >> 4));
+#pragma unroll
+                for (int kk = 0; kk < BKV / 16; ++kk)
+                    umma_ts(tmem_base + 256 + x * 128, tmem_base + x * 128 + kk * 8, dvs + (uint64_t)(kk * (2048 >> 4)),
+                            id_o, (!first || kk > 0));
+            };
+            if (!mbar_wait(smem_u32(q_full), 0, abort_flag)) goto done;
+            if (!mbar_wait(smem_u32(&k_full[0]), 0, abort_flag)) goto done;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_s(0, 0);
+            issue_s(1, 0);
+            umma_commit(smem_u32(&k_empty[0]));
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j & 1;
+                const bool more = j + 1 < n_tiles;
+                if (!mbar_wait(smem_u32(&v_full[s]), (j >> 1) & 1, abort_flag)) goto done;
+                if (!mbar_wait(smem_u32(&p_full[0]), j & 1, abort_flag)) goto done;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                issue_pv(0, s, j == 0);
+                if (more) {
+                    if (!mbar_wait(smem_u32(&k_full[s ^ 1]), ((j + 1) >> 1) & 1, abort_flag)) goto done;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    issue_s(0, s ^ 1);
+                }
+                if (!mbar_wait(smem_u32(&p_full[1]), j & 1, abort_flag)) goto done;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                issue_pv(1, s, j == 0);
+                umma_commit(smem_u32(&v_empty[s]));
+                if (more) {
+                    issue_s(1, s ^ 1);
+                    umma_commit(smem_u32(&k_empty[s ^ 1]));
+                }
+            }
+            umma_commit(smem_u32(o_done));
+        }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+        if (n_tiles > 0) {
+            // ---------------- softmax, correction, epilogue: one thread per query row and head ----------------
+            const int x = (warp >> 2) - 1;                      // 0: head A, 1: head B
+            const int quarter = warp & 3;
+            const int r = quarter * 32 + lane;                  // row of the tile = lane of tensor memory
+            const int pos = pos0 + r_begin + r;                 // this row's position
+            const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+            const uint32_t tmem_s = tmem_base + x * 128 + lane_addr;
+            const uint32_t tmem_ox = tmem_base + 256 + x * 128 + lane_addr;
+            float m_ref = -INFINITY, l = 0.f;                   // maximum in use, running sum
+            for (int j = 0; j < n_tiles; ++j) {
+                if (!mbar_wait(smem_u32(&s_full[x]), j & 1, abort_flag)) goto done;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int tile_base = (t_begin + j) * BKV;
+                uint32_t v[BKV];
+#pragma unroll
+                for (int c0 = 0; c0 < BKV; c0 += 32) tmem_ld32(tmem_s + c0, v + c0);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const bool need_mask = tile_base + BKV - 1 > p_first || tile_base < lo ||
+                                       (p.window > 0 && tile_base <= p_last - p.window);
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < BKV; ++i) {
+                        const int key = tile_base + i;
+                        const bool ok = key <= pos && (p.window <= 0 || key > pos - p.window);
+                        if (!ok) v[i] = 0xff800000u;            // -inf
+                    }
+                }
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < BKV; i += 4) {
+                    mx0 = fmaxf(mx0, __uint_as_float(v[i]));
+                    mx1 = fmaxf(mx1, __uint_as_float(v[i + 1]));
+                    mx2 = fmaxf(mx2, __uint_as_float(v[i + 2]));
+                    mx3 = fmaxf(mx3, __uint_as_float(v[i + 3]));
+                }
+                const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;    // scale > 0
+                const bool far = mx > m_ref + RESCALE_THRESHOLD;
+                const bool warp_far = __any_sync(0xffffffffu, far);
+                float factor = 1.f;
+                if (far) {
+                    factor = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - mx);
+                    m_ref = mx;
+                }
+                const float nbase = (m_ref == -INFINITY) ? 0.f : -m_ref;
+                float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+                for (int i = 0; i < BKV; i += 4) {
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), p.scale_log2, nbase));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, nbase));
+                    const float p2 = fast_exp2(fmaf(__uint_as_float(v[i + 2]), p.scale_log2, nbase));
+                    const float p3 = fast_exp2(fmaf(__uint_as_float(v[i + 3]), p.scale_log2, nbase));
+                    s0 += p0; s1 += p1; s2 += p2; s3 += p3;
+                    __nv_bfloat162 b0 = __floats2bfloat162_rn(p0, p1), b1 = __floats2bfloat162_rn(p2, p3);
+                    v[i >> 1] = *(uint32_t*)&b0;                 // the first half of v now holds the packed pairs
+                    v[(i >> 1) + 1] = *(uint32_t*)&b1;
+                }
+                l = l * factor + ((s0 + s1) + (s2 + s3));
+                if (warp_far && j > 0) {
+                    // the head's O product of the tile before is complete (its S product was issued behind it)
+#pragma unroll 1
+                    for (int c0 = 0; c0 < D; c0 += 32) {
+                        uint32_t o[32];
+                        tmem_ld32(tmem_ox + c0, o);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+                        tmem_st32(tmem_ox + c0, o);
+                    }
+                }
+                // the row's 128 keys, two to a column, over the first half of the head's S
+                tmem_st32(tmem_s, v);
+                tmem_st32(tmem_s + 32, v + 32);
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&p_full[x]));
+            }
+            // ---- epilogue: O / l ----
+            if (!mbar_wait(smem_u32(o_done), 0, abort_flag)) goto done;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            const bool store = r_begin + r < r_end;
+            __nv_bfloat16* orow = p.out + ((long long)(row0 + r_begin + r) * p.nq + h_a + x) * D;
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t o[32];
+                tmem_ld32(tmem_ox + c0, o);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (store) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 w;
+                        __nv_bfloat162 b0 = __floats2bfloat162_rn(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+                        __nv_bfloat162 b1 = __floats2bfloat162_rn(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+                        __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+                        __nv_bfloat162 b3 = __floats2bfloat162_rn(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+                        w.x = *(uint32_t*)&b0; w.y = *(uint32_t*)&b1; w.z = *(uint32_t*)&b2; w.w = *(uint32_t*)&b3;
+                        *(uint4*)(orow + c0 + i) = w;
+                    }
+                }
+            }
+        }
+    }
+done:
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicOr(p.err, CRANE_ERR_WAIT_TIMEOUT);
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512)
+                     : "memory");
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -532,6 +840,16 @@ EncodeTiledFn encode_fn() {
         fn = (EncodeTiledFn)sym;
     }
     return fn;
+}
+// CRANE_PREFILL_PAIR=0 keeps the kernel of one head per CTA for every shape, =2 takes the kernel of
+// two heads per CTA wherever the group size allows it (for measuring one against the other).
+int pair_kernel_mode() {
+    static int mode = -1;
+    if (mode < 0) {
+        const char* v = getenv("CRANE_PREFILL_PAIR");
+        mode = v == nullptr ? 1 : (v[0] == '0' ? 0 : (v[0] == '2' ? 2 : 1));
+    }
+    return mode;
 }
 // [rows, cols] bf16, cols contiguous; box of 64 columns x box_rows rows, 128-byte swizzle
 bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, int box_rows) {
@@ -570,6 +888,27 @@ CRANE_API int crane_prefill_attention_tc(const void* q, void* out, const void* k
     p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.kv_len = kv_len; p.block_table = block_table;
     p.max_blocks = max_blocks; p.num_pages = num_pages; p.page_size = page_size; p.n_entries = n_entries;
     p.nq = nq; p.nkv = nkv; p.window = window; p.skip_single = skip_single; p.scale_log2 = scale * 1.4426950408889634f; p.err = err;
+    // Two heads of a kv head per CTA (every K and V tile serves both, the heads take turns on the
+    // tensor cores) where there are CTAs enough to fill the SMs more than twice over even so:
+    // measured at 16 / 4 heads, 2,048 rows behind 30,000 cached keys 514 us against 562 us with one head
+    // per CTA; a whole prompt of 8,192 the same; below that the coarser grain loses (2,048 tokens 43
+    // against 41 us, 512 rows behind 8,192 keys, 32 CTAs instead of 64, 143 against 81 us).
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int pair_mode = pair_kernel_mode();
+    if ((nq / nkv) % 2 == 0 && (pair_mode == 2 || (pair_mode == 1 && (long long)total_q_tiles * (nq / 2) >= 2LL * sms))) {
+        constexpr size_t pair_smem = 6 * TILE_BYTES + 14 * 8 + 16 + 1024;
+        static bool pair_configured = false;
+        if (!pair_configured) {
+            if (cudaFuncSetAttribute(prefill_attn_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)pair_smem) != cudaSuccess)
+                return (int)cudaGetLastError();
+            pair_configured = true;
+        }
+        return crane_launch(prefill_attn_tc_pair_kernel, dim3(total_q_tiles, nq / 2), dim3(PAIR_THREADS), pair_smem,
+                            st, mq, mk, mv, p);
+    }
     constexpr size_t smem = 5 * TILE_BYTES + 18 * 8 + 2 * SPLIT * BQ * 4 + 16 + 1024;
     static bool configured = false;
     if (!configured) {

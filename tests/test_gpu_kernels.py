@@ -879,3 +879,21 @@ def test_rope_norm_cache_wide_kernel_head_size_128(K, err, qk_norm):
         assert rel_err(k_pool[page, :, off].cpu(), torch.from_numpy(k[t])) < 1e-2
         assert torch.equal(v_pool[page, :, off].cpu(), qkv[t, (nq + nkv) * d:].view(nkv, d).cpu())
     assert int((k_pool.float().abs().sum(-1) > 0).sum()) == n_tok * nkv
+
+
+def test_the_two_heads_per_cta_attention_on_the_shapes_of_these_tests():
+    """The tcgen05 flash attention picks between one and two query heads per CTA by
+    the size of its grid; the shapes of this file are small and would all take
+    the first.  Here the same tests run once more in a process that takes the
+    two-head kernel wherever the group size is even."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, CRANE_PREFILL_PAIR="2")
+    here = os.path.dirname(os.path.abspath(__file__))
+    p = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", "-p", "no:cacheprovider",
+                        os.path.join(here, "test_gpu_kernels.py"), os.path.join(here, "test_gpu_long_context.py"),
+                        "-k", "(tcgen05 or window_edge or split_between) and not two_heads_per_cta"],
+                       capture_output=True, text=True, env=env, timeout=900)
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-2000:]
+    assert " passed" in p.stdout

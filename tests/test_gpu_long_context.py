@@ -141,11 +141,13 @@ def test_decode_attention_at_long_contexts(K, err, lens, nq, nkv, splits, fused)
         assert rel_err(attention_reference(qq[0], k2, vv, lens[e] - 1), want) > 5e-2
 
 
-@pytest.mark.parametrize("cached,q_len,nq,nkv,page_size", [(0, 8192, 8, 2, 64), (16000, 512, 16, 4, 64),
-                                                           (33000, 300, 4, 1, 128)])
+@pytest.mark.parametrize("cached,q_len,nq,nkv,page_size", [(0, 8192, 16, 4, 64), (16000, 512, 16, 4, 64),
+                                                           (33000, 300, 4, 1, 128), (0, 8192, 4, 4, 32)])
 def test_prefill_attention_tcgen05_at_long_contexts(K, err, cached, q_len, nq, nkv, page_size):
-    """A whole prompt of 8,192 tokens, and portions behind 16,000 and 33,000 cached
-    positions, on the tcgen05 flash attention; a handful of rows against float64."""
+    """A whole prompt of 8,192 tokens (with 16 / 4 heads enough CTAs for the kernel
+    that takes two heads per CTA; with 4 / 4 the kernel of one head per CTA), and
+    portions behind 16,000 and 33,000 cached positions, on the tcgen05 flash
+    attention; a handful of rows against float64."""
     d = 128
     n = cached + q_len
     gen = torch.Generator().manual_seed(n)
