@@ -87,11 +87,11 @@ __device__ __forceinline__ float2 raw2(const FusedArgs& a, long long idx) {
 // RMSNorm with weight nw (if any); lane owns the neighbours j, j + 1 and their
 // partners in the second half.  Results (rounded to bf16) go to dst0 and, if
 // given, dst1.
-template <int D>
+template <int D, bool GENERAL>
 __device__ __forceinline__ void rope_norm_row(const FusedArgs& a, long long src, int pos, bool rotate,
                                               const float* nw, int lane, __nv_bfloat16* dst0,
                                               __nv_bfloat16* dst1) {
-    if (a.general) {
+    if (GENERAL) {
         rope_norm_general<(D / 2 + 31) / 32>(a.rope, D, pos, rotate, a.cos_tab, a.sin_tab, nw, a.eps, lane,
                                              [&](int e) { return raw1(a, src + e); },
                                              [&](int e, float v) {
@@ -241,7 +241,9 @@ __device__ __forceinline__ void row_finish(const RowRegs<D>& r, bool rotate, con
     }
 }
 
-template <int D, bool FUSED>
+// GENERAL: the instantiation for heads rotated or normalised otherwise than by the defaults (FusedArgs::
+// rope); it is a kernel of its own so that the serving kernel carries none of its code.
+template <int D, bool FUSED, bool GENERAL>
 __global__ void __launch_bounds__(WARPS * 32)
 paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                          float* __restrict__ part_o, float* __restrict__ part_ml,
@@ -318,8 +320,8 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
         for (int i = threadIdx.x; i < 16 * D / 2; i += WARPS * 32) ((uint32_t*)q_s)[i] = 0u;
         __syncthreads();
         for (int r = warp; r < n_rep; r += WARPS)
-            rope_norm_row<D>(fa, (long long)t * fa.qkv_stride + (long long)(g * n_rep + r) * D, pos, rotate,
-                             fa.q_norm_w, lane, q_s + r * D, nullptr);
+            rope_norm_row<D, GENERAL>(fa, (long long)t * fa.qkv_stride + (long long)(g * n_rep + r) * D, pos, rotate,
+                                      fa.q_norm_w, lane, q_s + r * D, nullptr);
         __syncthreads();
         const int r0 = lane >> 2, c0 = (lane & 3) * 2;
 #pragma unroll
@@ -367,8 +369,8 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
                 __nv_bfloat16* k_row = (__nv_bfloat16*)(stage + (pos % TILE) * RB);
                 __nv_bfloat16* v_row = (__nv_bfloat16*)(stage + TILE_BYTES + (pos % TILE) * RB);
                 const long long row_src = (long long)t * fa.qkv_stride;
-                rope_norm_row<D>(fa, row_src + (long long)(nq + g) * D, pos, rotate, fa.k_norm_w, lane, k_row,
-                                 fa.k_pool_w + prow);
+                rope_norm_row<D, GENERAL>(fa, row_src + (long long)(nq + g) * D, pos, rotate, fa.k_norm_w, lane, k_row,
+                                          fa.k_pool_w + prow);
                 for (int c = 2 * lane; c < D; c += 64) {
                     const float2 x = raw2(fa, row_src + (long long)(nq + nkv + g) * D + c);
                     const __nv_bfloat162 b = __floats2bfloat162_rn(x.x, x.y);
@@ -556,7 +558,7 @@ __device__ __forceinline__ uint32_t sw_off(int row, int chunk) {
 // cluster barrier each CTA works out its share of the output columns from all slices, in slice
 // order.  No scratch memory, no second kernel (a kernel of its own costs its place in the chain
 // of dependent launches, about 3 us per layer here, whatever little it does).
-template <bool FUSED, bool CLUSTER>
+template <bool FUSED, bool CLUSTER, bool GENERAL>
 __global__ void __launch_bounds__(WARPS * 32)
 paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
                              const __grid_constant__ CUtensorMap v_map,
@@ -643,14 +645,14 @@ paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
             if (threadIdx.x == 0) atomicOr(err, CRANE_ERR_POSITION_RANGE);
             rotate = false;
         }
-        if (fa.general) {
+        if (GENERAL) {
             // another pairing, a partly rotated head, the norm first or (1 + w) weights: row by row
             const long long row_src = (long long)t * fa.qkv_stride;
             for (int i = threadIdx.x; i < 16 * D / 2; i += WARPS * 32) ((uint32_t*)q_s)[i] = 0u;
             __syncthreads();
             for (int r = warp; r < n_rep; r += WARPS)
-                rope_norm_row<D>(fa, row_src + (long long)(g * n_rep + r) * D, pos, rotate, fa.q_norm_w, lane,
-                                 q_s + r * D, nullptr);
+                rope_norm_row<D, true>(fa, row_src + (long long)(g * n_rep + r) * D, pos, rotate, fa.q_norm_w, lane,
+                                       q_s + r * D, nullptr);
             if (makes_kv && pos / TILE >= tile_begin && pos / TILE < tile_end &&
                 (pos / TILE - tile_begin) % WARPS == warp) {
                 const int page = table[pos / page_size];
@@ -659,8 +661,8 @@ paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
                 } else {
                     const long long prow = (((long long)page * nkv + g) * page_size + pos % page_size) * D;
                     __nv_bfloat16* kv_lin = row_s + warp * 2 * D;              // [key row | value row]
-                    rope_norm_row<D>(fa, row_src + (long long)(nq + g) * D, pos, rotate, fa.k_norm_w, lane, kv_lin,
-                                     fa.k_pool_w + prow);
+                    rope_norm_row<D, true>(fa, row_src + (long long)(nq + g) * D, pos, rotate, fa.k_norm_w, lane, kv_lin,
+                                           fa.k_pool_w + prow);
                     for (int c = 2 * lane; c < D; c += 64) {
                         const float2 x = raw2(fa, row_src + (long long)(nq + nkv + g) * D + c);
                         const __nv_bfloat162 b = __floats2bfloat162_rn(x.x, x.y);
@@ -1135,7 +1137,7 @@ bool pool_map(CUtensorMap* map, const void* pool, long long rows) {
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <bool FUSED>
+template <bool FUSED, bool GENERAL>
 int launch_decode_tma(const void* q, void* out, float* part_o, float* part_ml, const void* k_pool,
                       const void* v_pool, const int* cu_q, const int* kv_len, const int* block_table,
                       int max_blocks, int num_pages, int page_size, int nq, int nkv, int window,
@@ -1149,7 +1151,7 @@ int launch_decode_tma(const void* q, void* out, float* part_o, float* part_ml, c
     const long long rows = (long long)num_pages * nkv * page_size;
     if (!pool_map(&km, k_pool, rows) || !pool_map(&vm, v_pool, rows)) return (int)cudaErrorInvalidValue;
     if (cluster) {
-        auto kern = paged_decode_attn_tma_kernel<FUSED, true>;
+        auto kern = paged_decode_attn_tma_kernel<FUSED, true, GENERAL>;
         static bool configured = false;
         if (!configured) {
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
@@ -1161,7 +1163,7 @@ int launch_decode_tma(const void* q, void* out, float* part_o, float* part_ml, c
                                     block_table, max_blocks, num_pages, page_size, nq, nkv, window,
                                     scale * 1.4426950408889634f, n_splits, err, fa);
     }
-    auto kern = paged_decode_attn_tma_kernel<FUSED, false>;
+    auto kern = paged_decode_attn_tma_kernel<FUSED, false, GENERAL>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
@@ -1174,7 +1176,7 @@ int launch_decode_tma(const void* q, void* out, float* part_o, float* part_ml, c
                         fa);
 }
 
-template <int D, bool FUSED>
+template <int D, bool FUSED, bool GENERAL>
 int launch_decode(const void* q, void* out, float* part_o, float* part_ml, const void* k_pool,
                   const void* v_pool, const int* cu_q, const int* kv_len, const int* block_table,
                   int max_blocks, int num_pages, int page_size, int n_entries, int nq, int nkv,
@@ -1182,7 +1184,7 @@ int launch_decode(const void* q, void* out, float* part_o, float* part_ml, const
     constexpr int tiles = WARPS * NSTAGE * 2 * TILE * Tile<D>::ROW_BYTES + (FUSED ? 16 * D * 2 : 0);
     constexpr int merge = WARPS * 16 * (D + 2) * 4;
     constexpr int smem = tiles > merge ? tiles : merge;
-    auto kern = paged_decode_attn_kernel<D, FUSED>;
+    auto kern = paged_decode_attn_kernel<D, FUSED, GENERAL>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
@@ -1193,7 +1195,7 @@ int launch_decode(const void* q, void* out, float* part_o, float* part_ml, const
     if (D == D128 && page_size % TILE == 0 && tma_path_enabled()) {
         // 2 to 8 slices merge themselves in a cluster; more go through scratch memory and a second kernel
         const bool cluster = n_splits > 1 && n_splits <= 8 && cluster_merge_enabled();
-        const int rc = launch_decode_tma<FUSED>(q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len,
+        const int rc = launch_decode_tma<FUSED, GENERAL>(q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len,
                                                 block_table, max_blocks, num_pages, page_size, nq, nkv,
                                                 window, scale, n_splits, err, fa, grid, cluster, st);
         if (rc != 0) return rc;
@@ -1228,13 +1230,13 @@ int launch_decode(const void* q, void* out, float* part_o, float* part_ml, const
 #ifdef CRANE_HEAD_SIZE
 extern "C" int CRANE_CAT(crane_decode_launch_d, CRANE_HEAD_SIZE)(CRANE_DECODE_LAUNCHER_ARGS) {
     const FusedArgs& fa = *(const FusedArgs*)fused_args;
-    if (fused)
-        return launch_decode<CRANE_HEAD_SIZE, true>(q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len,
-                                                    block_table, max_blocks, num_pages, page_size,
-                                                    n_entries, nq, nkv, window, scale, n_splits, err, fa, st);
-    return launch_decode<CRANE_HEAD_SIZE, false>(q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len,
-                                                 block_table, max_blocks, num_pages, page_size, n_entries,
-                                                 nq, nkv, window, scale, n_splits, err, fa, st);
+#define CRANE_DECODE_CALL(F, G)                                                                        \
+    launch_decode<CRANE_HEAD_SIZE, F, G>(q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len, block_table, \
+                                         max_blocks, num_pages, page_size, n_entries, nq, nkv, window, scale, \
+                                         n_splits, err, fa, st)
+    if (fused) return fa.general ? CRANE_DECODE_CALL(true, true) : CRANE_DECODE_CALL(true, false);
+    return CRANE_DECODE_CALL(false, false);
+#undef CRANE_DECODE_CALL
 }
 #else
 #define CRANE_DECODE_HEAD_SIZES(X) X(16) X(32) X(48) X(64) X(80) X(96) X(112) X(128) X(160) X(192) X(256)

@@ -119,7 +119,30 @@ struct GemmParams {
     long long split_stride;         // elements between consecutive slices (split_k > 1)
     const float* bias;              // over the feature dimension, or null
     int* err;
+    const uint8_t* prefetch;        // what the NEXT product of the step will stream (its weights), or null:
+    long long prefetch_bytes;       // asked into L2 by this kernel's idle warp as soon as it starts
 };
+
+// The kernels of a decode step run one after the other, each for a few microseconds, and each begins
+// by waiting for its operands to arrive from DRAM.  A product that is told what the next product
+// will stream asks for it at once (a hint: bulk prefetches into L2, no data comes to the SM, nothing
+// waits for them), so that DRAM keeps streaming through the short kernels between the two and the
+// next product finds its weights in L2.
+__device__ __forceinline__ void prefetch_l2(const GemmParams& p, int lane) {
+    if (p.prefetch == nullptr) return;
+    constexpr long long PIECE = 16384;
+    const long long ctas = (long long)gridDim.x * gridDim.y * gridDim.z;
+    const long long cta = blockIdx.x + (long long)gridDim.x * (blockIdx.y + (long long)gridDim.y * blockIdx.z);
+    const long long pieces = (p.prefetch_bytes + PIECE - 1) / PIECE;
+    const long long per = (pieces + ctas - 1) / ctas;
+    const long long end = min(pieces, (cta + 1) * per);
+    for (long long i = cta * per + lane; i < end; i += 32) {
+        const long long off = i * PIECE;
+        const uint32_t bytes = (uint32_t)min(PIECE, p.prefetch_bytes - off) & ~15u;
+        if (bytes)
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.prefetch + off), "r"(bytes) : "memory");
+    }
+}
 
 // OUT_F32: float output (else bf16).  TRANSPOSED: element (a, b) goes to out[b * ld + a].
 template <int BN, int STAGES, bool OUT_F32, bool TRANSPOSED>
@@ -220,6 +243,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         umma_commit(smem_u32(acc_ready));
     } else if (warp >= 2) {
         // ---------------- epilogue ----------------
+        if (warp == 2) prefetch_l2(p, lane);               // idle until the accumulator is done
         // a warp may touch the 32 lanes of tensor memory given by its index modulo 4
         const int quarter = warp & 3;
         const bool ok = num_kb == 0 || mbar_wait(smem_u32(acc_ready), 0, abort_flag);
@@ -885,7 +909,8 @@ int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const Gemm
 CRANE_API int crane_gemm_bf16_tcgen05(const void* A, const void* B, const float* bias, void* out,
                                       int rows_a, int rows_b, int k, long long lda, long long ldb,
                                       long long ld_out, int bn, int out_f32, int transposed,
-                                      int split_k, long long split_stride, int epilogue, int* err,
+                                      int split_k, long long split_stride, int epilogue,
+                                      const void* prefetch, long long prefetch_bytes, int* err,
                                       cudaStream_t st) {
     if (rows_a <= 0 || rows_b <= 0) return 0;
     if (k <= 0 || (k & 7) || (lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15))
@@ -900,6 +925,8 @@ CRANE_API int crane_gemm_bf16_tcgen05(const void* A, const void* B, const float*
     GemmParams p;
     p.rows_a = rows_a; p.rows_b = rows_b; p.k = k;
     p.out = out; p.ld_out = ld_out; p.split_stride = split_stride; p.bias = bias; p.err = err;
+    p.prefetch = ((uintptr_t)prefetch & 15) ? nullptr : (const uint8_t*)prefetch;   // (only the narrow-tile kernel asks)
+    p.prefetch_bytes = prefetch_bytes > 0 ? prefetch_bytes : 0;
     dim3 grid((rows_a + BM - 1) / BM, (rows_b + bn - 1) / bn, split_k);
     if (epilogue == 1) {
         // silu(gate) * up: bf16 output of rows_b / 2 columns; the weights' rows in blocks of 16 + 16
@@ -950,6 +977,7 @@ CRANE_API int crane_gemm_bf16_pair(const void* A, const void* B, const float* bi
     GemmParams p;
     p.rows_a = rows_a; p.rows_b = rows_b; p.k = k;
     p.out = out; p.ld_out = ld_out; p.split_stride = 0; p.bias = bias; p.err = err;
+    p.prefetch = nullptr; p.prefetch_bytes = 0;
     if (epilogue == 1) {
         if (bias != nullptr || (rows_b & 31) || (ld_out & 7) || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
         switch (bn) {

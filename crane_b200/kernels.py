@@ -27,7 +27,7 @@ _SIGNATURES = {
     "crane_to_float": [I, P, P, L, P],
     "crane_sum_parts": [P, I, L, L, P, L, I, I, P],
     "crane_gemm_simt": [I, I, P, P, P, P, I, I, I, L, L, L, P],
-    "crane_gemm_bf16_tcgen05": [P, P, P, P, I, I, I, L, L, L, I, I, I, I, L, I, P, P],
+    "crane_gemm_bf16_tcgen05": [P, P, P, P, I, I, I, L, L, L, I, I, I, I, L, I, P, L, P, P],
     "crane_gemm_bf16_pair": [P, P, P, P, I, I, I, L, L, L, I, I, P, P],
     "crane_paged_attention_simt": [I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P],
     "crane_paged_decode_attention_supports": [I, I, I],
@@ -262,12 +262,14 @@ class Kernels:
         return best
 
     def gemm_tcgen05(self, x, w, bias, out, err, split_k: int = 1, swap: bool = False,
-                     bn: int = 128, silu_mul: bool = False) -> None:
+                     bn: int = 128, silu_mul: bool = False, prefetch=None) -> None:
         """out[M,N] = x[M,K] @ w[N,K]^T (+ bias).  ``swap``: the weight fills the
         128-row side of the MMA and ``bn`` (16..64) covers the tokens.  With
         ``split_k`` > 1 ``out`` is float [slices, M, N] of partial sums.
         ``silu_mul``: w's rows come as 16 gate rows then the 16 up rows of the same
-        features, and out[M, N/2] = silu(gate) * up."""
+        features, and out[M, N/2] = silu(gate) * up.  ``prefetch``: (address,
+        bytes) of what the step's next product will stream, asked into L2 by the
+        narrow-tile kernel while it runs (a hint; ignored by the other kernels)."""
         M, K = x.shape
         N = w.shape[0]
         if silu_mul:
@@ -283,8 +285,9 @@ class Kernels:
         self._check(self.lib.crane_gemm_bf16_tcgen05(
             a.data_ptr(), b.data_ptr(), _ptr(bias), out.data_ptr(), a.shape[0], b.shape[0], K,
             a.stride(0), b.stride(0), ld, bn, 1 if out.dtype == torch.float32 else 0,
-            1 if swap else 0, split_k, stride, 1 if silu_mul else 0, err.data_ptr(), self._stream(x)),
-            "gemm_tcgen05")
+            1 if swap else 0, split_k, stride, 1 if silu_mul else 0,
+            prefetch[0] if prefetch else None, prefetch[1] if prefetch else 0, err.data_ptr(),
+            self._stream(x)), "gemm_tcgen05")
 
     # ---- attention ------------------------------------------------------
     def paged_attention_simt(self, q, out, k_pool, v_pool, positions, tok_entry, block_table,

@@ -103,7 +103,10 @@ class GqaAttention(Part):
     def forward(self, h, ctx, cache, rt):
         n = h.shape[0]
         k = rt.kernels
-        qkv = rt.linear(h, self.qkv_w, self.qkv_b, "attn_qkv")
+        # (keys and values of more than a few MB stream through L2 between this product and the output
+        # projection: asking for that one's weights now would only fetch them twice)
+        kv_bytes = int(ctx.h_kv_len[:ctx.n_entries].sum()) * self.nkv * self.d * 4
+        qkv = rt.linear(h, self.qkv_w, self.qkv_b, "attn_qkv", hint_next=kv_bytes < (8 << 20))
         cos = sin = None
         if self.position is not None:
             cos, sin = self.position.tables(rt, ctx.max_positions)

@@ -92,6 +92,7 @@ class DecoderModel:
 
     def _forward(self, ctx, caches: List[LayerCache]) -> torch.Tensor:
         rt = self.rt
+        rt.begin_step()
         n = ctx.n_tokens
         x = rt.ws.get("residual", n, self.spec.hidden_size, torch.float32)
         self.embed.forward(ctx.tokens, x, rt, getattr(ctx, "deferred_tokens", None))
