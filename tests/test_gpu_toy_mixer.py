@@ -229,7 +229,7 @@ def test_a_mixer_with_state_replays_graphs_when_it_bears_padding():
         for i in (1, 2, 3):
             r.end(i)
         whole = r.step([StepEntry(7, reqs[1][:pos[1]], [pos[1] - 1])]).float().cpu()
-        assert rel_err(whole[0], runs[graphs][0][-1][0]) < 3e-2
+        assert rel_err(whole[0], runs[graphs][0][-1][0]) < 3e-2, (graphs, r.graph_replays, r.graph_captures)
         r.end(7)
     assert runs[False][1] == 0 and runs[True][1] >= 3
     for a, b in zip(runs[False][0], runs[True][0]):
