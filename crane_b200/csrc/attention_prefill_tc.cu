@@ -219,7 +219,11 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     // which request and which of its query tiles (a request's last tiles, which read the most
     // keys, come first)
-    int e = 0, tile = blockIdx.x;
+    // CTAs are handed to the SMs in the order of their index, heads fastest: all heads of a request's
+    // last query tile (which reads the most keys) first, its first tile's last.  SMs that finish a
+    // short tile early then pick up what is left of the long work, and heads of one kv head read the
+    // same K and V tiles at about the same time.
+    int e = 0, tile = blockIdx.y;
     for (; e < p.n_entries; ++e) {
         const int rows = p.cu_q[e + 1] - p.cu_q[e];
         const int tiles = (p.skip_single && rows == 1) ? 0 : (rows + BQ - 1) / BQ;
@@ -230,7 +234,7 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tile -= tiles;
     }
     const bool active = e < p.n_entries;
-    const int h = blockIdx.y, g = active ? h / (p.nq / p.nkv) : 0;
+    const int h = blockIdx.x, g = active ? h / (p.nq / p.nkv) : 0;
     const int row0 = active ? p.cu_q[e] : 0, q_len = active ? p.cu_q[e + 1] - row0 : 0;
     const int pos0 = active ? p.kv_len[e] - q_len : 0;
     const int r_begin = tile * BQ, r_end = min(q_len, r_begin + BQ);
@@ -562,7 +566,7 @@ prefill_attn_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    int e = 0, tile = blockIdx.x;
+    int e = 0, tile = blockIdx.y;                  // head pairs fastest, as in the one-head kernel
     for (; e < p.n_entries; ++e) {
         const int rows = p.cu_q[e + 1] - p.cu_q[e];
         const int tiles = (p.skip_single && rows == 1) ? 0 : (rows + BQ - 1) / BQ;
@@ -573,7 +577,7 @@ prefill_attn_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         tile -= tiles;
     }
     const bool active = e < p.n_entries;
-    const int h_a = 2 * blockIdx.y, g = active ? h_a / (p.nq / p.nkv) : 0;
+    const int h_a = 2 * blockIdx.x, g = active ? h_a / (p.nq / p.nkv) : 0;
     const int row0 = active ? p.cu_q[e] : 0, q_len = active ? p.cu_q[e + 1] - row0 : 0;
     const int pos0 = active ? p.kv_len[e] - q_len : 0;
     const int r_begin = tile * BQ, r_end = min(q_len, r_begin + BQ);
@@ -889,15 +893,16 @@ CRANE_API int crane_prefill_attention_tc(const void* q, void* out, const void* k
     p.max_blocks = max_blocks; p.num_pages = num_pages; p.page_size = page_size; p.n_entries = n_entries;
     p.nq = nq; p.nkv = nkv; p.window = window; p.skip_single = skip_single; p.scale_log2 = scale * 1.4426950408889634f; p.err = err;
     // Two heads of a kv head per CTA (every K and V tile serves both, the heads take turns on the
-    // tensor cores) where there are CTAs enough to fill the SMs more than twice over even so:
-    // measured at 16 / 4 heads, 2,048 rows behind 30,000 cached keys 514 us against 562 us with one head
-    // per CTA; a whole prompt of 8,192 the same; below that the coarser grain loses (2,048 tokens 43
-    // against 41 us, 512 rows behind 8,192 keys, 32 CTAs instead of 64, 143 against 81 us).
+    // tensor cores) where there are CTAs enough to keep every SM busy to the end even so.  Measured
+    // at 16 / 4 heads, one head against two per CTA: a whole prompt of 4,096 tokens 88 against 78 us, of
+    // 8,192 the same (265 us, 0.63 of the bf16 peak), 2,048 rows behind 30,000 cached keys 562 against
+    // 519 us; below that the coarser grain loses (2,048 tokens 29 against 44 us; 512 rows behind 8,192
+    // keys, 64 CTAs against 32, 81 against 143 us).
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int pair_mode = pair_kernel_mode();
-    if ((nq / nkv) % 2 == 0 && (pair_mode == 2 || (pair_mode == 1 && (long long)total_q_tiles * (nq / 2) >= 2LL * sms))) {
+    if ((nq / nkv) % 2 == 0 && (pair_mode == 2 || (pair_mode == 1 && 10LL * total_q_tiles * (nq / 2) >= 17LL * sms))) {
         constexpr size_t pair_smem = 6 * TILE_BYTES + 14 * 8 + 16 + 1024;
         static bool pair_configured = false;
         if (!pair_configured) {
@@ -906,7 +911,7 @@ CRANE_API int crane_prefill_attention_tc(const void* q, void* out, const void* k
                 return (int)cudaGetLastError();
             pair_configured = true;
         }
-        return crane_launch(prefill_attn_tc_pair_kernel, dim3(total_q_tiles, nq / 2), dim3(PAIR_THREADS), pair_smem,
+        return crane_launch(prefill_attn_tc_pair_kernel, dim3(nq / 2, total_q_tiles), dim3(PAIR_THREADS), pair_smem,
                             st, mq, mk, mv, p);
     }
     constexpr size_t smem = 5 * TILE_BYTES + 18 * 8 + 2 * SPLIT * BQ * 4 + 16 + 1024;
@@ -917,6 +922,6 @@ CRANE_API int crane_prefill_attention_tc(const void* q, void* out, const void* k
             return (int)cudaGetLastError();
         configured = true;
     }
-    return crane_launch(prefill_attn_tc_kernel, dim3(total_q_tiles, nq), dim3(NUM_THREADS), smem, st, mq, mk,
+    return crane_launch(prefill_attn_tc_kernel, dim3(nq, total_q_tiles), dim3(NUM_THREADS), smem, st, mq, mk,
                         mv, p);
 }
