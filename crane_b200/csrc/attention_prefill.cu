@@ -36,7 +36,8 @@ paged_prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __
 
     // which request and which of its query tiles this CTA has; a request's last tiles (which
     // read the most keys) come first, so that the long CTAs start early
-    int e = 0, tile = blockIdx.x;
+    // (CTAs go to the SMs in the order of their index, heads fastest: all heads of a long tile first)
+    int e = 0, tile = blockIdx.y;
     for (; e < n_entries; ++e) {
         const int rows = cu_q[e + 1] - cu_q[e];
         // skip_single: entries of one token have no tile here (the decode kernel takes them)
@@ -48,7 +49,7 @@ paged_prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __
         tile -= tiles;
     }
     if (e >= n_entries) return;
-    const int h = blockIdx.y, g = h / (nq / nkv);
+    const int h = blockIdx.x, g = h / (nq / nkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row0 = cu_q[e], q_len = cu_q[e + 1] - row0;
     const int pos0 = kv_len[e] - q_len;                  // position of the request's first row
@@ -211,7 +212,7 @@ int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_p
             return (int)cudaGetLastError();
         configured = true;
     }
-    dim3 grid(total_q_tiles, nq);
+    dim3 grid(nq, total_q_tiles);
     kern<<<grid, THREADS, smem, st>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out,
                                       (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, cu_q,
                                       kv_len, block_table, max_blocks, num_pages, page_size, n_entries,
