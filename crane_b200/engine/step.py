@@ -251,22 +251,37 @@ class ModelRunner:
                 if not self.table.is_live(e.request_id):
                     self.table.admit(e.request_id)
                 self.table.extend(e.request_id, c)
-        # a pure decode step is padded to a fixed batch size (copies of entry 0, which
-        # recompute and rewrite exactly what entry 0 does) so that a captured graph fits it
+        # a pure decode step is padded to a fixed batch size (copies of one of its entries, which
+        # recompute and rewrite exactly what that entry does) so that a captured graph fits it
         pad_to = 0
         if (self._graphs_ok and self._pad_with_copies and max(counts) == 1
                 and all(len(e.want) == 1 for e in entries)):
             pad_to = self._bucket(n_entries)
+        # The entries run in the order of their cached lengths, longest first: the attention kernels'
+        # CTAs go to the SMs in the order of the entries, and what is left for the end should be short.
+        # Wanted rows are looked up through the order, so the logits come back in the caller's order.
+        place = list(range(n_entries))              # place[i]: where the caller's entry i runs
+        if n_entries >= 4:
+            lengths = [self.table.length(e.request_id) for e in entries]
+            order = sorted(range(n_entries), key=lambda i: -lengths[i])
+            if order != place:
+                for p, i in enumerate(order):
+                    place[i] = p
+                arrays = [arrays[i] for i in order]
+                counts = [counts[i] for i in order]
+        else:
+            order = place
         m = self.meta
         m.copied.synchronize()                      # the last step's copy has left the host block
         real_entries = n_entries
-        ids = np.fromiter((e.request_id for e in entries), dtype=np.int64, count=n_entries)
+        ids = np.fromiter((entries[i].request_id for i in order), dtype=np.int64, count=n_entries)
         cnt = np.asarray(counts, dtype=np.int32)
         if pad_to:
+            # (copies of the LAST entry, the shortest: they recompute and rewrite exactly what it does)
             extra = pad_to - n_entries
-            ids = np.concatenate([ids, np.full(extra, ids[0], dtype=np.int64)])
+            ids = np.concatenate([ids, np.full(extra, ids[-1], dtype=np.int64)])
             cnt = np.concatenate([cnt, np.ones(extra, dtype=np.int32)])
-            arrays = arrays + [arrays[0]] * extra
+            arrays = arrays + [arrays[-1]] * extra
             n_entries = pad_to
         # one native call lays out positions, entry of each token, cu_q, kv_len, slots, block tables
         n_tokens = self.table.fill_step(ids, cnt, m.np, m.off["positions"], m.off["tok_entry"],
@@ -320,9 +335,11 @@ class ModelRunner:
             n_entries = key[2]
         if pad_to:
             n_want = pad_to
-            m.view("want_rows", n_want, False)[:] = np.arange(n_want, dtype=np.int32)
+            rows_of = m.view("want_rows", n_want, False)
+            rows_of[:real_entries] = np.asarray(place, dtype=np.int32)    # one row per entry
+            rows_of[real_entries:] = np.arange(real_entries, n_want, dtype=np.int32)
         else:
-            want_rows = [int(cu[i]) + w for i, e in enumerate(entries) for w in e.want]
+            want_rows = [int(cu[place[i]]) + w for i, e in enumerate(entries) for w in e.want]
             n_want = real_want = len(want_rows)
             if key is not None and key[3] > n_want:
                 want_rows += [0] * (key[3] - n_want)        # more rows of logits than are wanted

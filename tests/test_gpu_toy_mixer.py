@@ -157,7 +157,9 @@ def register_device_toy():
             same = (ent[:, None] == ent[None, :]) & live[:, None] & live[None, :] & (gap >= 0)
             weights = torch.where(same, torch.pow(self.decay, gap.clamp_min(0).float()), 0.0)
             first = idx - cu[e_safe]
-            s = weights @ h.float() + (torch.pow(self.decay, (first + 1).float()) * live)[:, None] * prev[e_safe]
+            # (rows that pad the step hold whatever the buffers held: they must not reach a sum, not even times 0)
+            hf = torch.where(live[:, None], h.float(), 0.0)
+            s = weights @ hf + (torch.pow(self.decay, (first + 1).float()) * live)[:, None] * prev[e_safe]
             out = (s @ self.w.float().T).to(h.dtype)
             s_last = s[(cu[1:] - 1).clamp_min(0)]              # the state behind each entry's last row
             n_slots = cache.state.shape[0]
