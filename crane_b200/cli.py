@@ -14,7 +14,6 @@ import argparse
 import json
 import os
 import sys
-import tempfile
 from typing import List, Optional
 
 
@@ -87,16 +86,8 @@ def main(argv: Optional[List[str]] = None) -> int:
                    gpu_memory_limit=args.gpu_memory_limit,
                    max_batched_tokens=max(args.max_batched_tokens, args.max_concurrent),
                    chunk_size=args.chunk_size)
-    if args.random_weights:
-        from .config import read_config_json
-        from .weights.random_init import model_manifest_for, random_tensors
-        import torch
-        cfg = read_config_json(args.model_path)
-        store = torch.float32 if args.dtype in ("fp32", "float32") else torch.bfloat16
-        tensors = random_tensors(model_manifest_for(cfg, args.model_type), args.seed, store, "cuda:0")
-        model = ModelForCausalLM.from_tensors(cfg, tensors, args.dtype, **options)
-    else:
-        model = ModelForCausalLM.from_pretrained(args.model_path, args.dtype, args.model_type, **options)
+    model = ModelForCausalLM.from_pretrained(args.model_path, args.dtype, args.model_type,
+                                             random_weights=args.random_weights, seed=args.seed, **options)
 
     gen = GenerationConfig(max_new_tokens=args.max_new_tokens, temperature=args.temperature,
                            top_p=args.top_p, top_k=args.top_k,

@@ -36,9 +36,21 @@ class ModelForCausalLM:
 
     @classmethod
     def from_pretrained(cls, model_dir: str, dtype: str = "bf16", model_type: Optional[str] = None,
-                        **engine_options) -> "ModelForCausalLM":
+                        random_weights: bool = False, seed: int = 0, **engine_options) -> "ModelForCausalLM":
         """``model_dir`` holds config.json and safetensors; the model class is
-        chosen by config.json.  ``engine_options`` are ``EngineConfig`` fields."""
+        chosen by config.json.  ``random_weights``: only config.json is read and
+        the weights are drawn from ``seed``.  ``engine_options`` are
+        ``EngineConfig`` fields."""
+        if random_weights:
+            import torch
+            from ..config import read_config_json
+            from ..weights.random_init import model_manifest_for, random_tensors
+            cfg = read_config_json(model_dir)
+            store = torch.float32 if dtype in ("fp32", "float32", "f32") else torch.bfloat16
+            device = engine_options.get("device", "cuda:0")
+            tensors = random_tensors(model_manifest_for(cfg, model_type), seed, store, device)
+            return cls(ModelRunner(None, EngineConfig(dtype=dtype, **engine_options), config=cfg,
+                                   tensors=tensors, model_type=model_type))
         return cls(ModelRunner(model_dir, EngineConfig(dtype=dtype, **engine_options),
                                model_type=model_type))
 
