@@ -1239,7 +1239,13 @@ extern "C" int CRANE_CAT(crane_decode_launch_d, CRANE_HEAD_SIZE)(CRANE_DECODE_LA
 #undef CRANE_DECODE_CALL
 }
 #else
+// The head sizes whose objects are linked into this library: all that there are, or the ones the build
+// names (-D"CRANE_HEAD_SIZE_LIST(X)=X(64) X(128)": a library for the models at hand compiles faster).
+#ifdef CRANE_HEAD_SIZE_LIST
+#define CRANE_DECODE_HEAD_SIZES(X) CRANE_HEAD_SIZE_LIST(X)
+#else
 #define CRANE_DECODE_HEAD_SIZES(X) X(16) X(32) X(48) X(64) X(80) X(96) X(112) X(128) X(160) X(192) X(256)
+#endif
 #define DECLARE(DD) extern "C" int crane_decode_launch_d##DD(CRANE_DECODE_LAUNCHER_ARGS);
 CRANE_DECODE_HEAD_SIZES(DECLARE)
 #undef DECLARE

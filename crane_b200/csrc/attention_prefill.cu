@@ -237,7 +237,11 @@ extern "C" int CRANE_CAT(crane_prefill_launch_d, CRANE_HEAD_SIZE)(CRANE_PREFILL_
                                            scale, skip_single, err, st);
 }
 #else
+#ifdef CRANE_HEAD_SIZE_LIST          // the head sizes linked into this library (see attention_decode.cu)
+#define CRANE_PREFILL_HEAD_SIZES(X) CRANE_HEAD_SIZE_LIST(X)
+#else
 #define CRANE_PREFILL_HEAD_SIZES(X) X(16) X(32) X(48) X(64) X(80) X(96) X(112) X(128) X(160) X(192) X(256)
+#endif
 #define DECLARE(DD) extern "C" int crane_prefill_launch_d##DD(CRANE_PREFILL_LAUNCHER_ARGS);
 CRANE_PREFILL_HEAD_SIZES(DECLARE)
 #undef DECLARE

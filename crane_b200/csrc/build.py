@@ -6,6 +6,13 @@ flags; an up-to-date object is reused.  Objects go to ``_build/`` beside the
 sources when that is writable, otherwise to a per-user folder under the
 system's temporary directory, so a read-only checkout and an empty HOME both
 work.  There is no fallback: a failed build raises.
+
+The warp-level attention kernels are compiled per head size, two objects a
+size.  The CUDA library is linked for a set of head sizes: all eleven
+(``build_all``, what the build check and the tests use), or just the ones the
+models at hand have, so that a first call compiles what its model needs and no
+more.  A library that holds more sizes than asked for is taken as it is;
+compiled objects are kept, so a library for one more size compiles two files.
 """
 from __future__ import annotations
 
@@ -26,12 +33,19 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 # "file@NAME=VALUE": the file compiled once more with -DNAME=VALUE into an object of its own.  The
 # warp-level attention kernels are compiled per head size this way, side by side.
 ATTENTION_HEAD_SIZES = (16, 32, 48, 64, 80, 96, 112, 128, 160, 192, 256)
-KERNEL_SOURCES = (["elementwise.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "attention_simt.cu",
-                   "attention_decode.cu", "attention_prefill.cu", "attention_prefill_tc.cu",
-                   "sampling.cu"]
-                  # the slowest to compile first
-                  + [f"attention_decode.cu@CRANE_HEAD_SIZE={d}" for d in reversed(ATTENTION_HEAD_SIZES)]
-                  + [f"attention_prefill.cu@CRANE_HEAD_SIZE={d}" for d in reversed(ATTENTION_HEAD_SIZES)])
+BASE_SOURCES = ["elementwise.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "attention_simt.cu",
+                "attention_decode.cu", "attention_prefill.cu", "attention_prefill_tc.cu", "sampling.cu"]
+# the two files whose entry points pick a head size's launcher: compiled for the library's set of sizes
+DISPATCH_SOURCES = ("attention_decode.cu", "attention_prefill.cu")
+
+
+def kernel_sources(head_sizes: Sequence[int]) -> List[str]:
+    sizes = sorted(set(head_sizes), reverse=True)          # the slowest to compile first
+    return (BASE_SOURCES + [f"attention_decode.cu@CRANE_HEAD_SIZE={d}" for d in sizes]
+            + [f"attention_prefill.cu@CRANE_HEAD_SIZE={d}" for d in sizes])
+
+
+KERNEL_SOURCES = kernel_sources(ATTENTION_HEAD_SIZES)
 HOST_SOURCES = ["host/cache_manager.cpp", "host/scheduler.cpp"]
 
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
@@ -120,25 +134,45 @@ def _run(cmd: List[str], what: str) -> None:
 
 
 def _build(lib: str, sources: Sequence[str], compiler: str, flags: Sequence[str],
-           link_flags: Sequence[str], verbose_ptxas: bool = False) -> str:
+           link_flags: Sequence[str], verbose_ptxas: bool = False, label: str = "",
+           per_file_flags: Optional[Dict[str, List[str]]] = None) -> str:
+    """Compiles what is not yet compiled and links ``lib``.  ``label`` tells
+    libraries of one name apart (the CUDA library's set of head sizes);
+    ``per_file_flags``: further flags for single source files."""
     bdir = build_dir()
-    tag = _digest(sources, list(flags) + [compiler])
-    so = os.path.join(bdir, f"{lib}_{tag}.so")
+    per_file_flags = per_file_flags or {}
+    extra = [f for rel in sorted(per_file_flags) for f in [rel] + per_file_flags[rel]]
+    tag = _digest(sources, list(flags) + [compiler] + extra)
+    so = os.path.join(bdir, f"{lib}{'_' + label if label else ''}_{tag}.so")
     if os.path.isfile(so):
         return so
-    _say(f"building {lib} ({len(sources)} source files) in {bdir}")
+    _say(f"building {lib}{' (' + label + ')' if label else ''}: {len(sources)} source files in {bdir}")
     t0 = time.time()
-    objs = []
 
     def one(rel: str) -> str:
         path, _, define = rel.partition("@")
-        obj = os.path.join(bdir, f"{lib}_{tag}_{os.path.basename(path)}{'_' + define.replace('=', '_') if define else ''}.o")
-        cmd = [compiler, *flags, "-I", HERE, "-c", os.path.join(HERE, path), "-o", obj]
+        mine = list(flags) + per_file_flags.get(rel, [])
+        # an object is kept under the digest of its own source, the headers and its flags
+        otag = _digest([rel], mine + [compiler])
+        obj = os.path.join(bdir, f"obj_{otag}_{os.path.basename(path)}{'_' + define.replace('=', '_') if define else ''}.o")
+        if os.path.isfile(obj):
+            return obj
+        tmp_obj = obj + f".tmp{os.getpid()}"
+        cmd = [compiler, *mine, "-I", HERE, "-c", os.path.join(HERE, path), "-o", tmp_obj]
         if define:
             cmd.insert(1, "-D" + define)
         if verbose_ptxas:
             cmd.insert(1, "-Xptxas=-v")
         _run(cmd, rel)
+        os.replace(tmp_obj, obj)
+        suffix = obj[len(os.path.join(bdir, f"obj_{otag}")):]
+        for name in os.listdir(bdir):                  # the same file's objects of earlier source versions
+            if name.startswith("obj_") and name.endswith(suffix) and len(name) == len(os.path.basename(obj)) \
+                    and name != os.path.basename(obj) and not per_file_flags.get(rel):
+                try:
+                    os.remove(os.path.join(bdir, name))
+                except OSError:
+                    pass
         _say(f"compiled {rel} ({time.time() - t0:.0f} s)")
         return obj
     with ThreadPoolExecutor(max_workers=min(os.cpu_count() or 8, 16, len(sources))) as pool:
@@ -146,17 +180,15 @@ def _build(lib: str, sources: Sequence[str], compiler: str, flags: Sequence[str]
     tmp = so + f".tmp{os.getpid()}"
     _run([compiler, "-shared", "-o", tmp, *objs, *link_flags], lib)
     os.replace(tmp, so)
-    for name in os.listdir(bdir):                      # objects of earlier source versions
-        if name.startswith(lib + "_") and name.endswith(".so") and name != os.path.basename(so):
+    prefix = f"{lib}{'_' + label if label else ''}_"
+    for name in os.listdir(bdir):                      # libraries of earlier source versions
+        stale_lib = (name.startswith(prefix) and name.endswith(".so") and name != os.path.basename(so)
+                     and len(name) == len(os.path.basename(so)))
+        if stale_lib:
             try:
                 os.remove(os.path.join(bdir, name))
             except OSError:
                 pass
-    for o in objs:
-        try:
-            os.remove(o)
-        except OSError:
-            pass
     _say(f"built {os.path.basename(so)} in {time.time() - t0:.0f} s")
     return so
 
@@ -166,8 +198,38 @@ def build_host() -> str:
     return _build("libcrane_host", HOST_SOURCES, cxx, CXX_FLAGS, [])
 
 
-def build_kernels() -> str:
-    return _build("libcrane_kernels", KERNEL_SOURCES, nvcc_path(), NVCC_FLAGS, [])
+def _size_list_flag(head_sizes: Sequence[int]) -> str:
+    return "-DCRANE_HEAD_SIZE_LIST(X)=" + " ".join(f"X({d})" for d in sorted(set(head_sizes)))
+
+
+def _kernels_label(head_sizes: Sequence[int]) -> str:
+    sizes = sorted(set(head_sizes))
+    if sizes == sorted(ATTENTION_HEAD_SIZES):
+        return "all"
+    return "d" + "-".join(str(d) for d in sizes) if sizes else "d0"
+
+
+def build_kernels(head_sizes: Optional[Sequence[int]] = None) -> str:
+    """The CUDA library with the attention kernels of ``head_sizes`` (None: of all
+    head sizes there are kernels for).  Returns its path; compiles what is missing."""
+    sizes = sorted(set(ATTENTION_HEAD_SIZES if head_sizes is None else head_sizes))
+    unknown = [d for d in sizes if d not in ATTENTION_HEAD_SIZES]
+    if unknown:
+        raise BuildError(f"no attention kernels are written for head sizes {unknown}")
+    per_file = {}
+    if sizes != sorted(ATTENTION_HEAD_SIZES):
+        per_file = {f: [_size_list_flag(sizes)] for f in DISPATCH_SOURCES}
+    return _build("libcrane_kernels", kernel_sources(sizes), nvcc_path(), NVCC_FLAGS, [],
+                  label=_kernels_label(sizes), per_file_flags=per_file)
+
+
+def built_kernels_with(head_sizes: Sequence[int]) -> Optional[str]:
+    """The path of an up-to-date library that is already built and holds at least
+    ``head_sizes``: the one with every head size, if it is there."""
+    bdir = build_dir()
+    tag = _digest(KERNEL_SOURCES, list(NVCC_FLAGS) + [nvcc_path()])
+    so = os.path.join(bdir, f"libcrane_kernels_all_{tag}.so")
+    return so if os.path.isfile(so) else None
 
 
 def load_host() -> ctypes.CDLL:
@@ -177,16 +239,22 @@ def load_host() -> ctypes.CDLL:
         return _loaded["host"]
 
 
-def load_kernels() -> ctypes.CDLL:
-    """The CUDA library.  Raises BuildError if it cannot be built or loaded."""
+def load_kernels(head_sizes: Sequence[int] = ()) -> ctypes.CDLL:
+    """The CUDA library with (at least) the attention kernels of ``head_sizes``:
+    the library with every head size if that is built already, else one for
+    just these sizes, compiled now.  Raises BuildError if it cannot be built or
+    loaded."""
+    sizes = tuple(sorted(set(head_sizes)))
     with _lock:
-        if "kernels" not in _loaded:
-            path = build_kernels()
+        key = "kernels:" + ",".join(map(str, sizes))
+        if key not in _loaded:
+            path = built_kernels_with(sizes) or build_kernels(sizes)
             try:
-                _loaded["kernels"] = ctypes.CDLL(path)
+                _loaded[key] = ctypes.CDLL(path)
             except OSError as e:
                 raise BuildError(f"cannot load {path}: {e}") from None
-        return _loaded["kernels"]
+            _loaded[key]._crane_path = path
+        return _loaded[key]
 
 
 def build_all() -> Dict[str, str]:

@@ -132,8 +132,10 @@ class ModelRunner:
         self.max_seq_len = min(self.cfg.max_seq_len or self.spec.max_positions, self.spec.max_positions)
         self.cap_tokens = self.cfg.max_batched_tokens
         self.cap_entries = max(self.cfg.max_concurrent, 1)
+        head_sizes = sorted({int(ps.params["head_dim"]) for layer in self.spec.layers
+                             for ps in layer.parts.values() if "head_dim" in ps.params})
         self.rt = Runtime(self.cfg.device, dtype, self.cfg.workspace_rows or self.cap_tokens,
-                          self.cap_entries)
+                          self.cap_entries, head_sizes)
         torch.cuda.set_device(self.rt.device)
         self.model = DecoderModel(self.spec, source, self.rt, where)
         self._build_cache()

@@ -88,8 +88,12 @@ def _split(a: Act):
 
 
 class Kernels:
-    def __init__(self) -> None:
-        self.lib = build.load_kernels()
+    def __init__(self, head_sizes=()) -> None:
+        self.head_sizes: set = set()      # head sizes whose warp-level attention kernels the loaded library holds
+        self._bind(build.load_kernels([d for d in head_sizes if d in build.ATTENTION_HEAD_SIZES]))
+
+    def _bind(self, lib) -> None:
+        self.lib = lib
         for name, sig in _SIGNATURES.items():
             fn = getattr(self.lib, name)
             fn.argtypes = sig
@@ -98,6 +102,18 @@ class Kernels:
         self.lib.crane_set_pdl.argtypes = [c_int]
         self.lib.crane_set_pdl.restype = None
         self.lib.crane_set_pdl(0 if os.environ.get("CRANE_PDL", "1") == "0" else 1)
+        self.head_sizes = {d for d in build.ATTENTION_HEAD_SIZES
+                           if self.lib.crane_paged_decode_attention_supports(d, 1, 1)}
+
+    def require_head_size(self, d: int) -> None:
+        """Makes sure the loaded library holds the warp-level attention kernels of
+        head size ``d`` (if there are any for it): a first call for a model
+        compiles what that model needs, a model with another head size adds its
+        two files.  The library that was loaded before stays loaded (graphs that
+        were recorded with it keep working)."""
+        if d in self.head_sizes or d not in build.ATTENTION_HEAD_SIZES:
+            return
+        self._bind(build.load_kernels(sorted(self.head_sizes | {d})))
 
     # While a model runs a step, every launch goes to the stream that was current when the step
     # began (looked up once, not per launch); outside a step the current stream is asked for.
@@ -312,6 +328,7 @@ class Kernels:
         return splits
 
     def decode_attention_supports(self, d: int, nq: int, nkv: int) -> bool:
+        self.require_head_size(d)
         return bool(self.lib.crane_paged_decode_attention_supports(d, nq, nkv))
 
     def paged_decode_attention(self, q, out, k_pool, v_pool, cu_q, kv_len, block_table, page_size,
@@ -320,6 +337,7 @@ class Kernels:
         rows are skipped.  ``part_o`` [entries * nq * n_splits * d] and ``part_ml``
         [entries * nq * n_splits * 2] floats are scratch for n_splits > 1."""
         n_entries = kv_len.shape[0]
+        self.require_head_size(d)
         self._check(self.lib.crane_paged_decode_attention(
             q.data_ptr(), out.data_ptr(), _ptr(part_o), _ptr(part_ml), k_pool.data_ptr(),
             v_pool.data_ptr(), cu_q.data_ptr(), kv_len.data_ptr(), block_table.data_ptr(),
@@ -327,6 +345,7 @@ class Kernels:
             float(scale), int(n_splits), err.data_ptr(), self._stream(q)), "paged_decode_attention")
 
     def prefill_attention_supports(self, d: int, nq: int, nkv: int) -> bool:
+        self.require_head_size(d)
         return bool(self.lib.crane_paged_prefill_attention_supports(d, nq, nkv))
 
     def paged_prefill_attention(self, q, out, k_pool, v_pool, cu_q, kv_len, block_table, page_size,
@@ -334,6 +353,7 @@ class Kernels:
         """Any mix of portions and single tokens (bfloat16).  ``total_q_tiles``:
         the sum over the entries of ceil(tokens / 64), or more.  ``skip_single``:
         entries of exactly one token are left to the decode kernel."""
+        self.require_head_size(d)
         self._check(self.lib.crane_paged_prefill_attention(
             q.data_ptr(), out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), cu_q.data_ptr(),
             kv_len.data_ptr(), block_table.data_ptr(), block_table.shape[1], k_pool.shape[0],
@@ -364,6 +384,7 @@ class Kernels:
         rd, inter, first, off = rope or (d, False, False, 0.0)
         whole, parts, n_parts, stride = _split(qkv)
         n_entries = kv_len.shape[0]
+        self.require_head_size(d)
         self._check(self.lib.crane_paged_decode_attention_fused(
             whole, parts, n_parts, stride, qkv_cols, 1 if has_kv else 0, 1 if cos is not None else 0,
             _ptr(cos), _ptr(sin), cos.shape[0] if cos is not None else 0, _ptr(q_norm_w),
@@ -394,8 +415,13 @@ class Kernels:
 _kernels: Optional[Kernels] = None
 
 
-def get_kernels() -> Kernels:
+def get_kernels(head_sizes=()) -> Kernels:
+    """The process's kernels.  ``head_sizes``: head sizes that will be needed (a
+    model's), so that a library compiled at this first call holds them at once."""
     global _kernels
     if _kernels is None:
-        _kernels = Kernels()
+        _kernels = Kernels(head_sizes)
+    else:
+        for d in head_sizes:
+            _kernels.require_head_size(d)
     return _kernels

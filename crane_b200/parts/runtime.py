@@ -28,7 +28,7 @@ class DeviceFault(RuntimeError):
 
 
 class Runtime:
-    def __init__(self, device, dtype: torch.dtype, max_rows: int, max_decode_rows: int = 64):
+    def __init__(self, device, dtype: torch.dtype, max_rows: int, max_decode_rows: int = 64, head_sizes=()):
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise KernelError("the engine runs on a CUDA device only; there is no CPU path")
@@ -36,7 +36,7 @@ class Runtime:
             raise KernelError(f"model dtype must be float32 or bfloat16, got {dtype}")
         self.dtype = dtype
         self.exact = dtype == torch.float32
-        self.kernels = get_kernels()
+        self.kernels = get_kernels(head_sizes)       # (the model's head sizes: compiled at this first call if need be)
         self.ws = Workspace(self.device, max_rows)
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.max_rows = max_rows

@@ -17,6 +17,10 @@ def pytest_configure(config):
 def pytest_collection_modifyitems(config, items):
     import torch
     if torch.cuda.is_available():
+        # the GPU tests go through every head size: the library with all of them, built once
+        if any("gpu" in item.keywords for item in items):
+            from crane_b200.csrc import build
+            build.build_kernels()
         return
     skip = pytest.mark.skip(reason="no CUDA device here")
     for item in items:
