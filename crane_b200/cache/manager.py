@@ -9,10 +9,9 @@ Dense has one group (all layers, every earlier position) and no state.
 """
 from __future__ import annotations
 
-import ctypes
-from ctypes import c_int, c_int32, c_int64, c_void_p, POINTER
+from ctypes import c_int, c_int64, c_void_p
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Sequence
+from typing import Sequence
 
 import numpy as np
 

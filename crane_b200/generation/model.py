@@ -12,10 +12,10 @@ continuous batching.
 from __future__ import annotations
 
 import time
-from typing import Dict, List, Optional, Sequence
+from typing import List, Optional, Sequence
 
 from ..config import EngineConfig
-from ..engine.llm_engine import LLMEngine, RequestOutput
+from ..engine.llm_engine import LLMEngine
 from ..engine.step import ModelRunner
 from ..sampling import SamplingParams
 from .config import GenerationConfig

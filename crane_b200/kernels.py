@@ -7,7 +7,6 @@ raises.
 """
 from __future__ import annotations
 
-import ctypes
 import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional, Union

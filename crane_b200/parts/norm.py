@@ -6,8 +6,6 @@ add+norm kernel exists but is never launched, fused_ops/cuda_impl.rs:241-260).
 """
 from __future__ import annotations
 
-import torch
-
 from ..weights.loader import TensorSpec
 from .base import Part, register_part
 

@@ -14,7 +14,6 @@ import time
 from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
-import numpy as np
 import torch
 
 

@@ -17,11 +17,11 @@ How a tensor is kept:
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Mapping, Optional, Tuple
+from typing import Dict, List, Mapping, Tuple
 
 import torch
 
-from .safetensors_io import DictSource, TensorSource, model_files
+from .safetensors_io import TensorSource, model_files
 
 
 class WeightsError(ValueError):
