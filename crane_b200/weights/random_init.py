@@ -67,3 +67,25 @@ def write_model_folder(folder: str, config: dict, seed: int, dtype: str = "bfloa
     save_file(tensors, os.path.join(folder, "model.safetensors"),
               {"format": "pt", "seed": seed, "generator": "crane_b200.weights.random_init"})
     return folder
+
+
+def main(argv=None) -> int:
+    """``python -m crane_b200.weights.random_init --config config.json --seed 0 --out DIR``"""
+    import argparse
+    ap = argparse.ArgumentParser(description="write a model folder with random weights")
+    ap.add_argument("--config", required=True, help="a config.json of a registered architecture")
+    ap.add_argument("--out", required=True, help="folder to write config.json and model.safetensors into")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
+                    help="how matrices are stored")
+    ap.add_argument("--std", type=float, default=0.02)
+    args = ap.parse_args(argv)
+    with open(args.config) as f:
+        config = json.load(f)
+    write_model_folder(args.out, config, args.seed, args.dtype, args.std)
+    print(args.out)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -142,3 +142,14 @@ def test_write_model_folder(tmp_path):
     assert src.info("model.layers.0.mlp.up_proj.weight")[0] == torch.bfloat16
     assert src.info("model.norm.weight")[0] == torch.float32
     assert json.load(open(os.path.join(d, "config.json")))["hidden_size"] == 160
+
+
+def test_random_weights_command_line_writes_the_same_folder(tmp_path):
+    from crane_b200.weights.random_init import main
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(tiny_configs.A))
+    assert main(["--config", str(cfg), "--out", str(tmp_path / "cli"), "--seed", "9"]) == 0
+    write_model_folder(str(tmp_path / "api"), tiny_configs.A, 9, "bfloat16")
+    a, b = open_folder(str(tmp_path / "cli")), open_folder(str(tmp_path / "api"))
+    assert sorted(a.names()) == sorted(b.names())
+    assert all(torch.equal(a.tensor(n), b.tensor(n)) for n in a.names())
