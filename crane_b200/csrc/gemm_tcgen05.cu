@@ -440,13 +440,21 @@ __device__ __forceinline__ void store_chunk32(const GemmParams& p, const uint32_
 // rows of the same features; the epilogue writes silu(gate) * up, half as many
 // columns as the product has (silu(x) = x / (1 + exp(-x)) in float:
 // crane-core/kernels/fused_ops.cu:39-42, 112-130).
-template <int BN, int STAGES, bool OUT_F32, bool SILU>
+//
+// MT: how many 128-row blocks of A a tile has.  With MT = 1 a CTA has two accumulators and works on
+// the next tile while the epilogue reads the last one out.  With MT = 2 a tile is 256 x BN: both
+// accumulators belong to one tile, every row of B that comes into shared memory is used twice,
+// and a product whose 128-row tiles would need a second, partly empty round over the SMs has
+// half as many tiles (the epilogue then runs after the products, not beside them).
+template <int BN, int STAGES, bool OUT_F32, bool SILU, int MT = 1>
 __global__ void __launch_bounds__(NUM_THREADS)
 gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                             const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
-    constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    constexpr uint32_t A_SUB = BM * BK * 2, A_BYTES = MT * A_SUB, B_BYTES = BN * BK * 2;
     static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "the epilogue reads 32 columns at a time");
-    constexpr uint32_t TMEM_COLS = 2 * BN <= 256 ? 256 : 512;   // two accumulators; powers of two only
+    static_assert(MT == 1 || MT == 2, "one or two 128-row blocks per tile");
+    constexpr int NACC = MT == 1 ? 2 : 1;                       // accumulators of MT x BN columns
+    constexpr uint32_t TMEM_COLS = 2 * BN <= 256 ? 256 : 512;   // 2 x BN columns in use; powers of two only
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* smem_a = smem;
@@ -460,7 +468,7 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles_a = (p.rows_a + BM - 1) / BM, tiles_b = (p.rows_b + BN - 1) / BN;
+    const int tiles_a = (p.rows_a + MT * BM - 1) / (MT * BM), tiles_b = (p.rows_b + BN - 1) / BN;
     const int num_tiles = tiles_a * tiles_b;
     const int num_kb = (p.k + BK - 1) / BK;
 
@@ -495,13 +503,16 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
         pdl_wait();                                          // the activations come from the kernel before
         int it = 0;                                          // k-blocks issued so far, over all tiles
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-            const int a0 = (tile % tiles_a) * BM, b0 = (tile / tiles_a) * BN;
+            const int a0 = (tile % tiles_a) * (MT * BM), b0 = (tile / tiles_a) * BN;
             for (int kb = 0; kb < num_kb; ++kb, ++it) {
                 const int s = it % STAGES;
                 if (!mbar_wait(smem_u32(&empty[s]), ((it / STAGES) & 1) ^ 1, abort_flag)) goto done;
                 const uint32_t bar = smem_u32(&full[s]);
                 mbar_expect_tx(bar, A_BYTES + B_BYTES);
-                tma_load_2d(smem_u32(smem_a + s * A_BYTES), &map_a, bar, kb * BK, a0);
+                // (a block of rows past the end of A arrives as zeros and counts its bytes all the same)
+#pragma unroll
+                for (int m = 0; m < MT; ++m)
+                    tma_load_2d(smem_u32(smem_a + s * A_BYTES + m * A_SUB), &map_a, bar, kb * BK, a0 + m * BM);
                 tma_load_2d(smem_u32(smem_b + s * B_BYTES), &map_b, bar, kb * BK, b0);
             }
         }
@@ -510,20 +521,25 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
         const uint32_t idesc = instr_desc_bf16(BN);
         int it = 0, local = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
-            const int acc = local & 1;
-            // the epilogue must have emptied this accumulator (two tiles ago)
-            if (!mbar_wait(smem_u32(&acc_empty[acc]), ((local >> 1) & 1) ^ 1, abort_flag)) goto done;
+            const int acc = local % NACC;
+            // the epilogue must have emptied this accumulator (NACC tiles ago)
+            if (!mbar_wait(smem_u32(&acc_empty[acc]), ((local / NACC) & 1) ^ 1, abort_flag)) goto done;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+            const uint32_t tmem_d = tmem_base + (uint32_t)(acc * MT * BN);
             for (int kb = 0; kb < num_kb; ++kb, ++it) {
                 const int s = it % STAGES;
                 if (!mbar_wait(smem_u32(&full[s]), (it / STAGES) & 1, abort_flag)) goto done;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t da = smem_desc_sw128(smem_u32(smem_a + s * A_BYTES));
                 const uint64_t db = smem_desc_sw128(smem_u32(smem_b + s * B_BYTES));
 #pragma unroll
-                for (int kk = 0; kk < BK / UMMA_K; ++kk)
-                    umma_bf16(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        const uint64_t da = smem_desc_sw128(smem_u32(smem_a + s * A_BYTES + m * A_SUB));
+                        umma_bf16(tmem_d + (uint32_t)(m * BN), da + 2 * kk, db + 2 * kk, idesc,
+                                  (kb > 0 || kk > 0) ? 1u : 0u);
+                    }
+                }
                 umma_commit(smem_u32(&empty[s]));
             }
             umma_commit(smem_u32(&acc_full[acc]));
@@ -533,16 +549,17 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
         const int quarter = warp & 3;
         int local = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
-            const int acc = local & 1;
-            const int a0 = (tile % tiles_a) * BM, b0 = (tile / tiles_a) * BN;
-            if (!mbar_wait(smem_u32(&acc_full[acc]), (local >> 1) & 1, abort_flag)) break;
+            const int acc = local % NACC;
+            const int a0 = (tile % tiles_a) * (MT * BM), b0 = (tile / tiles_a) * BN;
+            if (!mbar_wait(smem_u32(&acc_full[acc]), (local / NACC) & 1, abort_flag)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int a = a0 + quarter * 32 + lane;
-            const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c = 0; c < MT * BN; c += 32) {
+                const int m = c / BN, c0 = c - m * BN;       // BN is a multiple of 32: no chunk spans two blocks
+                const int a = a0 + m * BM + quarter * 32 + lane;
+                const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * MT * BN);
                 uint32_t r[32];
-                tmem_ld32(trow + (uint32_t)c0, r);
+                tmem_ld32(trow + (uint32_t)c, r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (a >= p.rows_a) continue;
                 const int b_first = b0 + c0;
@@ -633,14 +650,22 @@ __device__ __forceinline__ void cluster_sync_all() {
                  "barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-template <int BN, int STAGES, bool SILU>
+//
+// MT = 2: the pair's tile is 512 x BN, two 256-row blocks one under the other, each CTA holding two
+// accumulators of BN columns (rows 0..127 / 128..255 of either block).  A CTA then takes in 32 KB of
+// A and BN / 2 rows of B per k-block for twice the products, the least operand traffic per product
+// of all the kernels here; with more than 256 accumulator columns per tile there is no second
+// accumulator to work into while the epilogue reads, so the epilogue of a tile is not hidden.
+template <int BN, int STAGES, bool SILU, int MT = 1>
 __global__ void __launch_bounds__(NUM_THREADS)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const GemmParams p) {
     static_assert(BN % 32 == 0 && BN >= 64 && BN <= 256, "BN / 2 rows of B per CTA, 32 columns per epilogue step");
+    static_assert(MT == 1 || MT == 2, "one or two 256-row blocks per tile");
     constexpr int BH = BN / 2;                                   // rows of B that one CTA loads
-    constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BH * BK * 2;
-    constexpr uint32_t TMEM_COLS = 2 * BN <= 256 ? 256 : 512;    // two accumulators
+    constexpr uint32_t A_SUB = BM * BK * 2, A_BYTES = MT * A_SUB, B_BYTES = BH * BK * 2;
+    constexpr int NACC = 2 * MT * BN <= 512 ? 2 : 1;             // accumulators of MT x BN columns
+    constexpr uint32_t TMEM_COLS = NACC * MT * BN <= 256 ? 256 : 512;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // both CTAs of a pair round up by the same amount, so offsets match across them
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -657,7 +682,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();                     // 0: issues the MMAs
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-    const int tiles_a = (p.rows_a + 2 * BM - 1) / (2 * BM), tiles_b = (p.rows_b + BN - 1) / BN;
+    constexpr int TILE_ROWS = 2 * BM * MT;
+    const int tiles_a = (p.rows_a + TILE_ROWS - 1) / TILE_ROWS, tiles_b = (p.rows_b + BN - 1) / BN;
     const int num_tiles = tiles_a * tiles_b;
     const int num_kb = (p.k + BK - 1) / BK;
 
@@ -694,14 +720,17 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         pdl_wait();
         int it = 0;
         for (int tile = pair; tile < num_tiles; tile += num_pairs) {
-            const int a0 = (tile % tiles_a) * 2 * BM + (int)rank * BM;
+            const int a0 = (tile % tiles_a) * TILE_ROWS + (int)rank * BM;
             const int b0 = (tile / tiles_a) * BN + (int)rank * BH;
             for (int kb = 0; kb < num_kb; ++kb, ++it) {
                 const int s = it % STAGES;
                 if (!mbar_wait(smem_u32(&empty[s]), ((it / STAGES) & 1) ^ 1, abort_flag)) goto done;
                 const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
                 if (rank == 0) mbar_expect_tx(smem_u32(&full[s]), 2 * (A_BYTES + B_BYTES));   // both CTAs' bytes
-                tma_load_2d_pair(smem_u32(smem_a + s * A_BYTES), &map_a, bar, kb * BK, a0);
+#pragma unroll
+                for (int m = 0; m < MT; ++m)
+                    tma_load_2d_pair(smem_u32(smem_a + s * A_BYTES + m * A_SUB), &map_a, bar, kb * BK,
+                                     a0 + m * 2 * BM);
                 tma_load_2d_pair(smem_u32(smem_b + s * B_BYTES), &map_b, bar, kb * BK, b0);
             }
         }
@@ -711,19 +740,24 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                                ((uint32_t)((2 * BM) >> 4) << 24);
         int it = 0, local = 0;
         for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local) {
-            const int acc = local & 1;
-            if (!mbar_wait(smem_u32(&acc_empty[acc]), ((local >> 1) & 1) ^ 1, abort_flag)) goto done;
+            const int acc = local % NACC;
+            if (!mbar_wait(smem_u32(&acc_empty[acc]), ((local / NACC) & 1) ^ 1, abort_flag)) goto done;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+            const uint32_t tmem_d = tmem_base + (uint32_t)(acc * MT * BN);
             for (int kb = 0; kb < num_kb; ++kb, ++it) {
                 const int s = it % STAGES;
                 if (!mbar_wait(smem_u32(&full[s]), (it / STAGES) & 1, abort_flag)) goto done;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t da = smem_desc_sw128(smem_u32(smem_a + s * A_BYTES));
                 const uint64_t db = smem_desc_sw128(smem_u32(smem_b + s * B_BYTES));
 #pragma unroll
-                for (int kk = 0; kk < BK / UMMA_K; ++kk)
-                    umma_bf16_pair(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        const uint64_t da = smem_desc_sw128(smem_u32(smem_a + s * A_BYTES + m * A_SUB));
+                        umma_bf16_pair(tmem_d + (uint32_t)(m * BN), da + 2 * kk, db + 2 * kk, idesc,
+                                       (kb > 0 || kk > 0) ? 1u : 0u);
+                    }
+                }
                 umma_commit_pair(smem_u32(&empty[s]), 3);        // the stage is free in both CTAs
             }
             umma_commit_pair(smem_u32(&acc_full[acc]), 3);
@@ -733,16 +767,17 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         const int quarter = warp & 3;
         int local = 0;
         for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local) {
-            const int acc = local & 1;
-            const int a0 = (tile % tiles_a) * 2 * BM + (int)rank * BM, b0 = (tile / tiles_a) * BN;
-            if (!mbar_wait(smem_u32(&acc_full[acc]), (local >> 1) & 1, abort_flag)) break;
+            const int acc = local % NACC;
+            const int a0 = (tile % tiles_a) * TILE_ROWS + (int)rank * BM, b0 = (tile / tiles_a) * BN;
+            if (!mbar_wait(smem_u32(&acc_full[acc]), (local / NACC) & 1, abort_flag)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int a = a0 + quarter * 32 + lane;
-            const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+            const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * MT * BN);
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c = 0; c < MT * BN; c += 32) {
+                const int m = c / BN, c0 = c - m * BN;           // BN is a multiple of 32: no chunk spans two blocks
+                const int a = a0 + m * 2 * BM + quarter * 32 + lane;
                 uint32_t r[32];
-                tmem_ld32(trow + (uint32_t)c0, r);
+                tmem_ld32(trow + (uint32_t)c, r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (a >= p.rows_a) continue;
                 const int b_first = b0 + c0;
@@ -841,11 +876,12 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
     return crane_launch(kern, grid, dim3(NUM_THREADS), smem, st, ma, mb, p);
 }
 
-template <int BN, int STAGES, bool OUT_F32, bool SILU = false>
+template <int BN, int STAGES, bool OUT_F32, bool SILU = false, int MT = 1>
 int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int num_tiles,
                       cudaStream_t st) {
-    constexpr size_t smem = STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
-    auto kern = gemm_bf16_persistent_kernel<BN, STAGES, OUT_F32, SILU>;
+    constexpr size_t smem = STAGES * (MT * BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
+    static_assert(smem <= 232448, "more shared memory than a CTA can have");
+    auto kern = gemm_bf16_persistent_kernel<BN, STAGES, OUT_F32, SILU, MT>;
     static bool configured = false;
     static int sms = 0;
     if (!configured) {
@@ -860,11 +896,12 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPa
     return crane_launch(kern, dim3(ctas), dim3(NUM_THREADS), smem, st, ma, mb, p);
 }
 
-template <int BN, int STAGES, bool SILU>
+template <int BN, int STAGES, bool SILU, int MT = 1>
 int launch_pair(const void* A, const void* B, int rows_a, int rows_b, int k, long long lda, long long ldb,
                 const GemmParams& p, cudaStream_t st) {
-    constexpr size_t smem = STAGES * (BM * BK * 2 + (BN / 2) * BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
-    auto kern = gemm_bf16_pair_kernel<BN, STAGES, SILU>;
+    constexpr size_t smem = STAGES * (MT * BM * BK * 2 + (BN / 2) * BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
+    static_assert(smem <= 232448, "more shared memory than a CTA can have");
+    auto kern = gemm_bf16_pair_kernel<BN, STAGES, SILU, MT>;
     static bool configured = false;
     static int sms = 0;
     if (!configured) {
@@ -878,7 +915,7 @@ int launch_pair(const void* A, const void* B, int rows_a, int rows_b, int k, lon
     CUtensorMap ma, mb;
     if (!make_map(&ma, A, rows_a, k, lda, BM) || !make_map(&mb, B, rows_b, k, ldb, BN / 2))
         return (int)cudaErrorInvalidValue;
-    const int tiles = ((rows_a + 2 * BM - 1) / (2 * BM)) * ((rows_b + BN - 1) / BN);
+    const int tiles = ((rows_a + 2 * BM * MT - 1) / (2 * BM * MT)) * ((rows_b + BN - 1) / BN);
     const int pairs = tiles < sms / 2 ? tiles : sms / 2;
     return crane_launch_cluster(kern, dim3(2 * pairs), dim3(NUM_THREADS), smem, dim3(2, 1, 1), st, ma, mb, p);
 }
@@ -901,6 +938,7 @@ int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const Gemm
 }  // namespace
 
 // D[a, b] = sum_k A[a, k] B[b, k].  bn: columns (rows of B) per tile, 16..256.
+// tile_rows: 128, or 256 (bf16 output, untransposed, no slices, no epilogue, bn 128 / 192 / 256 only).
 // epilogue: 0 none, 1 silu(gate) * up (see the persistent kernel).
 // out_f32 / transposed as in the kernel; split_k > 1 writes float partial sums
 // [split_k][...] into `out` (which must then be float) `split_stride` apart.
@@ -908,7 +946,7 @@ int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const Gemm
 // ldb multiples of 8 elements, A and B 16-byte aligned.
 CRANE_API int crane_gemm_bf16_tcgen05(const void* A, const void* B, const float* bias, void* out,
                                       int rows_a, int rows_b, int k, long long lda, long long ldb,
-                                      long long ld_out, int bn, int out_f32, int transposed,
+                                      long long ld_out, int bn, int tile_rows, int out_f32, int transposed,
                                       int split_k, long long split_stride, int epilogue,
                                       const void* prefetch, long long prefetch_bytes, int* err,
                                       cudaStream_t st) {
@@ -928,6 +966,17 @@ CRANE_API int crane_gemm_bf16_tcgen05(const void* A, const void* B, const float*
     p.prefetch = ((uintptr_t)prefetch & 15) ? nullptr : (const uint8_t*)prefetch;   // (only the narrow-tile kernel asks)
     p.prefetch_bytes = prefetch_bytes > 0 ? prefetch_bytes : 0;
     dim3 grid((rows_a + BM - 1) / BM, (rows_b + bn - 1) / bn, split_k);
+    if (tile_rows == 2 * BM) {
+        if (transposed || split_k != 1 || out_f32 || epilogue != 0) return (int)cudaErrorInvalidValue;
+        const int tiles = (int)(((rows_a + 2 * BM - 1) / (2 * BM)) * grid.y);
+        switch (bn) {
+            case 128: return launch_persistent<128, 4, false, false, 2>(ma, mb, p, tiles, st);
+            case 192: return launch_persistent<192, 4, false, false, 2>(ma, mb, p, tiles, st);
+            case 256: return launch_persistent<256, 3, false, false, 2>(ma, mb, p, tiles, st);
+        }
+        return (int)cudaErrorInvalidValue;
+    }
+    if (tile_rows != BM) return (int)cudaErrorInvalidValue;
     if (epilogue == 1) {
         // silu(gate) * up: bf16 output of rows_b / 2 columns; the weights' rows in blocks of 16 + 16
         if (transposed || split_k != 1 || out_f32 || bias != nullptr || (rows_b & 31) || (ld_out & 7) ||
@@ -967,19 +1016,28 @@ CRANE_API int crane_gemm_bf16_tcgen05(const void* A, const void* B, const float*
 }
 
 // The same product as crane_gemm_bf16_tcgen05 for many tokens (bf16 output, untransposed, no
-// slices) on pairs of SMs: 256 x bn tiles, bn in 128, 192, 224, 256.  epilogue as there.
+// slices) on pairs of SMs: 256 x bn tiles, bn in 128, 192, 224, 256, or (tile_rows 512) 512 x bn
+// tiles, bn in 192, 224, 256.  epilogue as there.
 CRANE_API int crane_gemm_bf16_pair(const void* A, const void* B, const float* bias, void* out, int rows_a,
                                    int rows_b, int k, long long lda, long long ldb, long long ld_out,
-                                   int bn, int epilogue, int* err, cudaStream_t st) {
+                                   int bn, int tile_rows, int epilogue, int* err, cudaStream_t st) {
     if (rows_a <= 0 || rows_b <= 0) return 0;
     if (k <= 0 || (k & 7) || (lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15))
         return (int)cudaErrorInvalidValue;
+    if (tile_rows != 2 * BM && tile_rows != 4 * BM) return (int)cudaErrorInvalidValue;
+    const bool tall = tile_rows == 4 * BM;                  // 512-row tiles: bn 192, 224 or 256
     GemmParams p;
     p.rows_a = rows_a; p.rows_b = rows_b; p.k = k;
     p.out = out; p.ld_out = ld_out; p.split_stride = 0; p.bias = bias; p.err = err;
     p.prefetch = nullptr; p.prefetch_bytes = 0;
     if (epilogue == 1) {
         if (bias != nullptr || (rows_b & 31) || (ld_out & 7) || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
+        if (tall) switch (bn) {
+            case 192: return launch_pair<192, 5, true, 2>(A, B, rows_a, rows_b, k, lda, ldb, p, st);
+            case 224: return launch_pair<224, 4, true, 2>(A, B, rows_a, rows_b, k, lda, ldb, p, st);
+            case 256: return launch_pair<256, 4, true, 2>(A, B, rows_a, rows_b, k, lda, ldb, p, st);
+            default: return (int)cudaErrorInvalidValue;
+        }
         switch (bn) {
             case 128: return launch_pair<128, 8, true>(A, B, rows_a, rows_b, k, lda, ldb, p, st);
             case 192: return launch_pair<192, 7, true>(A, B, rows_a, rows_b, k, lda, ldb, p, st);
@@ -989,6 +1047,12 @@ CRANE_API int crane_gemm_bf16_pair(const void* A, const void* B, const float* bi
         return (int)cudaErrorInvalidValue;
     }
     if (epilogue != 0) return (int)cudaErrorInvalidValue;
+    if (tall) switch (bn) {
+        case 192: return launch_pair<192, 5, false, 2>(A, B, rows_a, rows_b, k, lda, ldb, p, st);
+        case 224: return launch_pair<224, 4, false, 2>(A, B, rows_a, rows_b, k, lda, ldb, p, st);
+        case 256: return launch_pair<256, 4, false, 2>(A, B, rows_a, rows_b, k, lda, ldb, p, st);
+        default: return (int)cudaErrorInvalidValue;
+    }
     switch (bn) {
         case 128: return launch_pair<128, 8, false>(A, B, rows_a, rows_b, k, lda, ldb, p, st);
         case 192: return launch_pair<192, 7, false>(A, B, rows_a, rows_b, k, lda, ldb, p, st);

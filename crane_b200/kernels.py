@@ -26,8 +26,8 @@ _SIGNATURES = {
     "crane_to_float": [I, P, P, L, P],
     "crane_sum_parts": [P, I, L, L, P, L, I, I, P],
     "crane_gemm_simt": [I, I, P, P, P, P, I, I, I, L, L, L, P],
-    "crane_gemm_bf16_tcgen05": [P, P, P, P, I, I, I, L, L, L, I, I, I, I, L, I, P, L, P, P],
-    "crane_gemm_bf16_pair": [P, P, P, P, I, I, I, L, L, L, I, I, P, P],
+    "crane_gemm_bf16_tcgen05": [P, P, P, P, I, I, I, L, L, L, I, I, I, I, I, L, I, P, L, P, P],
+    "crane_gemm_bf16_pair": [P, P, P, P, I, I, I, L, L, L, I, I, I, P, P],
     "crane_paged_attention_simt": [I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P],
     "crane_paged_decode_attention_supports": [I, I, I],
     "crane_paged_decode_attention": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P],
@@ -233,17 +233,19 @@ class Kernels:
 
     PAIR_TILES = (256, 224, 192, 128)
 
-    def gemm_pair(self, x, w, bias, out, err, bn: int = 256, silu_mul: bool = False) -> None:
+    def gemm_pair(self, x, w, bias, out, err, bn: int = 256, silu_mul: bool = False,
+                  tile_rows: int = 256) -> None:
         """out[M,N] (bf16) = x[M,K] @ w[N,K]^T (+ bias) for many tokens, every
         256 x ``bn`` tile computed by two SMs together (tcgen05 cta_group::2).
-        ``silu_mul`` as in ``gemm_tcgen05``."""
+        ``silu_mul`` as in ``gemm_tcgen05``.  ``tile_rows`` 512: tiles of 512
+        tokens x ``bn`` (192, 224 or 256) features, two accumulators per SM."""
         M, K = x.shape
         N = w.shape[0]
         assert out.dtype == torch.bfloat16 and out.stride(1) == 1 and bn in self.PAIR_TILES
         assert tuple(out.shape) == ((M, N // 2) if silu_mul else (M, N))
         self._check(self.lib.crane_gemm_bf16_pair(
             x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K, x.stride(0), w.stride(0),
-            out.stride(0), bn, 1 if silu_mul else 0, err.data_ptr(), self._stream(x)), "gemm_pair")
+            out.stride(0), bn, tile_rows, 1 if silu_mul else 0, err.data_ptr(), self._stream(x)), "gemm_pair")
 
     WIDE_TILES = (256, 224, 192, 160, 128)
 
@@ -257,6 +259,26 @@ class Kernels:
             tiles = -(-m // 128) * -(-n // bn)
             cost = -(-tiles // sms) * (bn + 16)
             if best_cost is None or cost < best_cost:
+                best, best_cost = bn, cost
+        return best
+
+    TALL_TILES = (256, 192)
+
+    @classmethod
+    def tall_width_for(cls, m: int, n: int, sms: int) -> int:
+        """The width of 256 x width tiles on one SM where they beat the 128-row
+        tiles of ``tile_width_for``, else 0: a product whose 128-row tiles need a
+        second, partly empty round over the SMs and whose 256-row tiles need one
+        (measured at 2048 x 3072 x 2048: 27.9 -> 25.1 us in 256 x 192 tiles; the
+        factor below is that measurement)."""
+        if m <= 128:
+            return 0
+        bn1 = cls.tile_width_for(m, n, sms)
+        best, best_cost = 0, -(-(-(-m // 128) * -(-n // bn1)) // sms) * (bn1 + 16)
+        for bn in cls.TALL_TILES:
+            tiles = -(-m // 256) * -(-n // bn)
+            cost = -(-tiles // sms) * 2 * (bn + 16) * 0.92
+            if cost < best_cost:
                 best, best_cost = bn, cost
         return best
 
@@ -276,15 +298,57 @@ class Kernels:
                 best, best_cost = bn, cost
         return best
 
+    TALL_PAIR_TILES = (256, 224, 192)
+
+    @classmethod
+    def pair_plan(cls, m: int, n: int, k: int, sms: int, silu_mul: bool = False):
+        """(tile width, tile rows) for ``gemm_pair``, (0, 0) where the single-SM
+        kernel is the better choice.
+
+        A model of the time of one round of tiles, in microseconds, fitted to
+        measurements of 13 shapes (2048 .. 8192 tokens, inner dimensions 2048 ..
+        14336): an SM takes its operands in from L2 at about 83 GB/s (all of them
+        together 12.3 TB/s: (256 + width) x 128 bytes per 64-wide k-block for its
+        128 rows of a 256-row tile, (512 + width) x 128 for its 256 rows of a
+        512-row tile) and multiplies 128 rows x width x 16 in width / 2 clocks;
+        the two overlap, not perfectly (a 3-norm).  Tiles of 512 rows move the
+        least bytes per product but have no second accumulator to work into while
+        the epilogue reads the first, so their epilogue adds to every round: they
+        win with a long inner dimension (2048 x 3072 x 8192: 86.6 -> 74.6 us,
+        8192^3: 807 -> 740 us) and lose with a short one and with the silu
+        epilogue.  Among near-equal costs the wider 256-row tile is taken (it
+        runs a little better than the model says)."""
+        if not cls.pair_width_for(m, n, k, sms):
+            return 0, 0
+        pairs = sms // 2
+
+        def norm3(a, b):
+            return (a ** 3 + b ** 3) ** (1.0 / 3.0)
+
+        cands = []
+        for bn in cls.PAIR_TILES:
+            rounds = -(-(-(-m // 256) * -(-n // bn)) // pairs)
+            cands.append((rounds * norm3((256 + bn) * k * 1.2e-5, k * bn / 56000.0), bn, 256))
+        for bn in cls.TALL_PAIR_TILES:
+            rounds = -(-(-(-m // 512) * -(-n // bn)) // pairs)
+            epilogue = bn * (0.024 if silu_mul else 0.018)
+            cands.append((rounds * (norm3((512 + bn) * k * 1.2e-5, k * bn / 28000.0) + epilogue), bn, 512))
+        least = min(c[0] for c in cands)
+        near = [c for c in cands if c[0] <= 1.03 * least]
+        _, bn, rows = min(near, key=lambda c: (c[2], -c[1]))
+        return bn, rows
+
     def gemm_tcgen05(self, x, w, bias, out, err, split_k: int = 1, swap: bool = False,
-                     bn: int = 128, silu_mul: bool = False, prefetch=None) -> None:
+                     bn: int = 128, silu_mul: bool = False, prefetch=None, tile_rows: int = 128) -> None:
         """out[M,N] = x[M,K] @ w[N,K]^T (+ bias).  ``swap``: the weight fills the
         128-row side of the MMA and ``bn`` (16..64) covers the tokens.  With
         ``split_k`` > 1 ``out`` is float [slices, M, N] of partial sums.
         ``silu_mul``: w's rows come as 16 gate rows then the 16 up rows of the same
         features, and out[M, N/2] = silu(gate) * up.  ``prefetch``: (address,
         bytes) of what the step's next product will stream, asked into L2 by the
-        narrow-tile kernel while it runs (a hint; ignored by the other kernels)."""
+        narrow-tile kernel while it runs (a hint; ignored by the other kernels).
+        ``tile_rows`` 256: tiles of 256 tokens x ``bn`` (128, 192 or 256) features
+        (bf16 output, no slices, no swap, no silu)."""
         M, K = x.shape
         N = w.shape[0]
         if silu_mul:
@@ -299,7 +363,7 @@ class Kernels:
         a, b = (w, x) if swap else (x, w)
         self._check(self.lib.crane_gemm_bf16_tcgen05(
             a.data_ptr(), b.data_ptr(), _ptr(bias), out.data_ptr(), a.shape[0], b.shape[0], K,
-            a.stride(0), b.stride(0), ld, bn, 1 if out.dtype == torch.float32 else 0,
+            a.stride(0), b.stride(0), ld, bn, tile_rows, 1 if out.dtype == torch.float32 else 0,
             1 if swap else 0, split_k, stride, 1 if silu_mul else 0,
             prefetch[0] if prefetch else None, prefetch[1] if prefetch else 0, err.data_ptr(),
             self._stream(x)), "gemm_tcgen05")

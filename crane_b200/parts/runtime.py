@@ -120,9 +120,9 @@ class Runtime:
             return False
         if w.shape[0] % 32 or out.stride(0) % 8 or out.data_ptr() % 16:
             return False
-        pair = self.kernels.pair_width_for(M, w.shape[0], x.shape[1], self.num_sms)
+        pair, rows = self.kernels.pair_plan(M, w.shape[0], x.shape[1], self.num_sms, silu_mul=True)
         if pair:
-            self.kernels.gemm_pair(x, w, None, out, self.err, bn=pair, silu_mul=True)
+            self.kernels.gemm_pair(x, w, None, out, self.err, bn=pair, silu_mul=True, tile_rows=rows)
         else:
             self.kernels.gemm_tcgen05(x, w, None, out, self.err,
                                       bn=self.kernels.tile_width_for(M, w.shape[0], self.num_sms), silu_mul=True)
@@ -162,7 +162,7 @@ class Runtime:
                     return Partials(parts)
                 k.gemm_tcgen05(x, w, bias, out, self.err, swap=True, bn=bn, prefetch=nxt)
             else:
-                pair = k.pair_width_for(M, N, K, self.num_sms) if out.dtype == torch.bfloat16 else 0
+                pair, pair_rows = k.pair_plan(M, N, K, self.num_sms) if out.dtype == torch.bfloat16 else (0, 0)
                 bn = k.tile_width_for(M, N, self.num_sms)
                 if not pair and out.dtype == torch.bfloat16 and M <= 4 * self.split_rows:
                     # A few hundred tokens and a long inner dimension (the down projection): 128 x 128
@@ -180,8 +180,11 @@ class Runtime:
                         return Partials(parts)
                 if out.dtype == torch.float32 and bn not in (128, 256):
                     bn = 256 if N >= 2048 else 128
+                tall = 0 if pair or out.dtype != torch.bfloat16 else k.tall_width_for(M, N, self.num_sms)
                 if pair:
-                    k.gemm_pair(x, w, bias, out, self.err, bn=pair)       # two SMs per 256-row tile
+                    k.gemm_pair(x, w, bias, out, self.err, bn=pair, tile_rows=pair_rows)   # two SMs per tile
+                elif tall:
+                    k.gemm_tcgen05(x, w, bias, out, self.err, bn=tall, tile_rows=256)
                 else:
                     k.gemm_tcgen05(x, w, bias, out, self.err, bn=bn)
             self.launches += 1

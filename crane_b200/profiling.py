@@ -109,10 +109,11 @@ def gemm(a):
         def fn():
             w = ws[state["i"] % a.sets]; state["i"] += 1
             if a.pair:
-                K.gemm_pair(x, w, None, out, err, bn=bn, silu_mul=a.silu_mul)
+                K.gemm_pair(x, w, None, out, err, bn=bn, silu_mul=a.silu_mul, tile_rows=512 if a.tall else 256)
             else:
-                K.gemm_tcgen05(x, w, None, out, err, bn=bn, silu_mul=a.silu_mul)
-        extra = {"mode": "pairs of SMs" if a.pair else "persistent", "bn": bn, "silu_mul": a.silu_mul}
+                K.gemm_tcgen05(x, w, None, out, err, bn=bn, silu_mul=a.silu_mul, tile_rows=256 if a.tall else 128)
+        extra = {"mode": "pairs of SMs" if a.pair else "persistent", "bn": bn, "silu_mul": a.silu_mul,
+                 "tile_rows": (256 if a.tall else 128) * (2 if a.pair else 1)}
     t = _time(fn, a.warmup, a.reps)
     assert int(err.item()) == 0
     nbytes = 2 * (a.m * a.k + a.n * a.k) + out.numel() * out.element_size()
@@ -202,6 +203,7 @@ def main(argv=None) -> int:
     g.add_argument("--silu-mul", action="store_true")
     g.add_argument("--swap", action="store_true", help="weights on the 128-row side also for more than 64 tokens")
     g.add_argument("--pair", action="store_true", help="many tokens: the kernel in which two SMs share a tile")
+    g.add_argument("--tall", action="store_true", help="many tokens: tiles of 256 rows on one SM (bn 128, 192, 256), of 512 rows with --pair (bn 192, 224, 256)")
     for name in ("decode-attention", "prefill-attention"):
         p = sub.add_parser(name)
         p.add_argument("--q-heads", type=int, default=16); p.add_argument("--kv-heads", type=int, default=4)

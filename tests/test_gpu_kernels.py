@@ -517,6 +517,64 @@ def test_gemm_on_pairs_of_sms(K, err, M, N, K_, bn):
     assert rel_err(out, a.double() @ w.double().T) < 5e-3
 
 
+@pytest.mark.parametrize("M,N,K_,bn", [(256, 256, 64, 256), (300, 520, 160, 128), (2048, 3072, 2048, 192),
+                                       (700, 1000, 352, 192), (5000, 4100, 512, 256), (129, 192, 64, 192),
+                                       (100, 200, 72, 128)])
+def test_gemm_in_tiles_of_256_rows(K, err, M, N, K_, bn):
+    """Tiles of 256 tokens on one SM (two accumulators of one tile): the second
+    128 rows must land 128 rows further down, also where they reach past the end
+    of the tokens, and a CTA that takes several tiles must keep them apart."""
+    torch.manual_seed(M + N)
+    a = torch.randn(M, K_, device=DEV).bfloat16()
+    w = torch.randn(N, K_, device=DEV).bfloat16()
+    bias = torch.randn(N, device=DEV)
+    out = torch.full((M + 3, N), 7.0, device=DEV, dtype=torch.bfloat16)
+    K.gemm_tcgen05(a, w, bias, out[:M], err, bn=bn, tile_rows=256)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    assert rel_err(out[:M], a.double() @ w.double().T + bias.double()) < 5e-3
+    assert bool((out[M:] == 7.0).all())                    # nothing written past the last row
+    K.gemm_tcgen05(a, w, None, out[:M], err, bn=bn, tile_rows=256)
+    assert rel_err(out[:M], a.double() @ w.double().T) < 5e-3
+    # the same rows as the 128-row tiles give, bit for bit (same order of the sums)
+    ref = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    K.gemm_tcgen05(a, w, None, ref, err, bn=bn if bn != 192 else 192)
+    assert torch.equal(ref, out[:M])
+
+
+@pytest.mark.parametrize("M,N,K_,bn", [(512, 256, 64, 256), (300, 520, 160, 192), (2048, 3072, 2048, 224),
+                                       (700, 1000, 352, 224), (5000, 9000, 512, 256), (257, 192, 64, 192),
+                                       (100, 200, 72, 256)])
+def test_gemm_on_pairs_of_sms_in_tiles_of_512_rows(K, err, M, N, K_, bn):
+    """Two SMs, two accumulators each: rows 0..127 and 256..383 of a tile in the
+    first SM, 128..255 and 384..511 in the second; bit for bit what the 256-row
+    tiles of the pair kernel give."""
+    torch.manual_seed(M + N)
+    a = torch.randn(M, K_, device=DEV).bfloat16()
+    w = torch.randn(N, K_, device=DEV).bfloat16()
+    bias = torch.randn(N, device=DEV)
+    out = torch.full((M + 3, N), 7.0, device=DEV, dtype=torch.bfloat16)
+    K.gemm_pair(a, w, bias, out[:M], err, bn=bn, tile_rows=512)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    assert rel_err(out[:M], a.double() @ w.double().T + bias.double()) < 5e-3
+    assert bool((out[M:] == 7.0).all())
+    K.gemm_pair(a, w, None, out[:M], err, bn=bn, tile_rows=512)
+    ref = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    K.gemm_pair(a, w, None, ref, err, bn=bn)
+    assert torch.equal(ref, out[:M])
+    # with the silu(gate) * up epilogue (N / 2 output columns; needs N % 32 == 0)
+    if N % 32 == 0:
+        o1 = torch.full((M, N // 2), 7.0, device=DEV, dtype=torch.bfloat16)
+        o2 = torch.full((M, N // 2), 7.0, device=DEV, dtype=torch.bfloat16)
+        ws = (w.float() * 0.05).bfloat16()
+        K.gemm_pair(a, ws, None, o1, err, bn=bn, silu_mul=True, tile_rows=512)
+        K.gemm_pair(a, ws, None, o2, err, bn=bn, silu_mul=True)
+        assert torch.equal(o1, o2)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+
+
 @pytest.mark.parametrize("M,I,K_,bn", [(256, 128, 64, 128), (300, 352, 160, 192), (2048, 6144, 2048, 224),
                                        (130, 1008, 64, 256)])
 def test_gemm_on_pairs_of_sms_with_silu_mul(K, err, M, I, K_, bn):

@@ -49,6 +49,29 @@ def test_tile_widths():
     assert Kernels.tile_width_for(2048, 3072, SMS) == 192              # 256 tiles: two rounds, the narrowest that does it
 
 
+def test_tile_rows():
+    """Which products take the tiles of twice the rows (the rules are fitted to
+    measurements; these are the measured cases)."""
+    for m in (200, 256, 300, 2048, 5000, 32768):
+        for n in (2048, 3072, 6144, 28672):
+            for k in (2048, 4096, 14336):
+                for silu in (False, True):
+                    bn, rows = Kernels.pair_plan(m, n, k, SMS, silu)
+                    assert (bn, rows) == (0, 0) or rows == 256 and bn in Kernels.PAIR_TILES or \
+                        rows == 512 and bn in Kernels.TALL_PAIR_TILES
+                    assert (bn == 0) == (Kernels.pair_width_for(m, n, k, SMS) == 0)
+            t = Kernels.tall_width_for(m, n, SMS)
+            assert t == 0 or t in Kernels.TALL_TILES
+    assert Kernels.pair_plan(2048, 12288, 2048, SMS, True) == (224, 256)   # gate/up, 2,048 tokens: epilogue in the way
+    assert Kernels.pair_plan(2048, 3072, 8192, SMS) == (192, 512)          # a long inner dimension
+    assert Kernels.pair_plan(8192, 8192, 8192, SMS) == (256, 512)
+    assert Kernels.pair_plan(8192, 3072, 2048, SMS) == (256, 256)          # a short one
+    assert Kernels.pair_plan(2048, 2048, 6144, SMS) == (256, 256)          # 512-row tiles would be too few
+    assert Kernels.tall_width_for(2048, 3072, SMS) == 192                  # one round of 128 tiles instead of two
+    assert Kernels.tall_width_for(2048, 2048, SMS) == 0                    # 128 x 256 tiles already take one round
+    assert Kernels.tall_width_for(128, 3072, SMS) == 0
+
+
 class _Ctx:
     pass
 
