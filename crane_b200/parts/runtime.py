@@ -172,9 +172,9 @@ class Runtime:
                     tiles = -(-N // 128) * -(-M // 256)
                     slices = min(self.num_sms // tiles, 4)
                     if slices >= 2 and K // slices >= 1536:
-                        parts = self.ws.get("splitk_wide:" + str(N), 12 * self.split_rows, N, torch.float32,
-                                            cap=12 * self.split_rows)
-                        parts = parts[:slices * M].view(slices, M, N)
+                        # at most 4 slices of 4 * split_rows tokens: the buffer never has to grow
+                        parts = self.ws.get("splitk_wide:" + str(N), slices * M, N, torch.float32,
+                                            cap=16 * self.split_rows).view(slices, M, N)
                         k.gemm_tcgen05(x, w, bias, parts, self.err, split_k=slices, swap=True, bn=256)
                         self.launches += 1
                         return Partials(parts)

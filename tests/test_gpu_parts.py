@@ -87,6 +87,23 @@ def test_linear_on_widths_the_tensor_core_kernel_refuses_rounds_once(M, N, K_, o
         assert ((got.double() - want).abs() <= tol * want.abs() + 1e-4).all()     # (+ cancellation in the float sum)
 
 
+@pytest.mark.parametrize("M,N,K_", [(798, 320, 8960), (1024, 128, 6144), (300, 2048, 6144), (513, 136, 7000)])
+def test_linear_of_hundreds_of_tokens_in_wide_slices_has_room_for_every_slice(M, N, K_):
+    """A narrow output and a long inner dimension take 4 slices of up to 1,024
+    tokens: the buffer of partial sums must hold all of them."""
+    from crane_b200.kernels import Partials
+    rt = runtime(torch.bfloat16, rows=1024)
+    torch.manual_seed(M + N)
+    x = torch.randn(M, K_, device=DEV).bfloat16()
+    w = (torch.randn(N, K_, device=DEV) / K_ ** 0.5).bfloat16()
+    got = rt.linear(x, w, None, "o")
+    if K_ % 8 == 0:
+        assert isinstance(got, Partials)
+    torch.cuda.synchronize()
+    assert rel_err(whole(got, torch.bfloat16), x.double() @ w.double().T) < 5e-3
+    rt.check_errors()
+
+
 def test_float_logits_from_split_k_slices():
     """A head narrow enough to be computed in slices of the inner dimension: the
     float result is the slices' sum in float (no rounding to bfloat16 between)."""
