@@ -955,3 +955,72 @@ def test_the_two_heads_per_cta_attention_on_the_shapes_of_these_tests():
                        capture_output=True, text=True, env=env, timeout=900)
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-2000:]
     assert " passed" in p.stdout
+
+
+def _dense_attention(qs, ks, vs, lens, q_lens, nq, nkv, d, window):
+    """Every row of every entry in float64 on the device: [sum of q_lens, nq * d]."""
+    outs = []
+    for q, k, v, n, ql in zip(qs, ks, vs, lens, q_lens):
+        q, k, v = q.to(DEV).double(), k.to(DEV).double(), v.to(DEV).double()
+        kk, vv = k.repeat_interleave(nq // nkv, dim=1), v.repeat_interleave(nq // nkv, dim=1)
+        s = torch.einsum("qhd,thd->hqt", q, kk) * d ** -0.5
+        pos = torch.arange(n - ql, n, device=DEV)[:, None]
+        t = torch.arange(n, device=DEV)[None, :]
+        mask = t <= pos
+        if window > 0:
+            mask &= t > pos - window
+        p = torch.softmax(s.masked_fill(~mask[None], float("-inf")), dim=-1)
+        outs.append(torch.einsum("hqt,thd->qhd", p, vv).reshape(ql, nq * d))
+    return torch.cat(outs)
+
+
+def test_attention_kernels_at_random_shapes(K, err):
+    """The split-KV decode kernel, the warp-level and the tcgen05 prefill kernel
+    at shapes drawn at random: up to 8 entries of 1 to 4,200 keys, portions that
+    end on, before and after the edges of the 64- and 128-row tiles, pages of 16
+    to 256, odd group sizes, windows, 1 to 64 key slices."""
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    worst = 0.0
+    for i in range(72):
+        rng = np.random.default_rng(5000 + i)
+        torch.manual_seed(5000 + i)
+        kind = ["decode", "mma", "tc"][i % 3]
+        d = 128 if kind == "tc" else int(rng.choice([64, 128, 128, 80, 256, 16, 48]))
+        nkv = int(rng.choice([1, 2, 4, 5]))
+        nq = nkv * int(rng.choice([1, 2, 4, 7, 8]))
+        ps = int(rng.choice([16, 32, 64, 128, 256]))
+        n_req = int(rng.integers(1, 9))
+        lens = [int(rng.integers(1, 4200)) if rng.random() < 0.6 else int(rng.integers(1, 140)) for _ in range(n_req)]
+        q_lens = [1] * n_req if kind == "decode" else \
+            [int(min(n, rng.choice([1, 2, 63, 64, 65, 127, 128, 129, 300, 1000, n]))) for n in lens]
+        window = 0 if rng.random() < 0.6 else int(rng.integers(1, 700))
+        splits = int(rng.choice([1, 2, 3, 5, 8, 9, 16, 33, 64]))
+        label = f"{i}: {kind} d={d} heads {nq}/{nkv} page {ps} keys {lens} rows {q_lens} window {window} slices {splits}"
+        if kind == "tc" and not K.prefill_attention_tc_supports(d, nq, nkv, ps):
+            continue
+        ks = [torch.randn(n, nkv, d).bfloat16().float() for n in lens]
+        vs = [torch.randn(n, nkv, d).bfloat16().float() for n in lens]
+        qs = [torch.randn(ql, nq, d).bfloat16().float() for ql in q_lens]
+        k_pool, v_pool, table = paged_cache(ks, vs, ps, torch.bfloat16, seed=i)
+        cu = i32(np.concatenate([[0], np.cumsum(q_lens)]).tolist())
+        q = torch.cat(qs).to(DEV).bfloat16().reshape(-1, nq * d)
+        out = torch.full_like(q, 9.0)
+        if kind == "decode":
+            part_o = torch.empty(n_req * nq * splits * d, device=DEV)
+            part_ml = torch.empty(n_req * nq * splits * 2, device=DEV)
+            K.paged_decode_attention(q, out, k_pool, v_pool, cu, i32(lens), table, ps, nq, nkv, d, window,
+                                     d ** -0.5, splits, part_o, part_ml, err)
+        elif kind == "mma":
+            K.paged_prefill_attention(q, out, k_pool, v_pool, cu, i32(lens), table, ps,
+                                      sum((n + 63) // 64 for n in q_lens), nq, nkv, d, window, d ** -0.5, err)
+        else:
+            K.prefill_attention_tc(q, out, k_pool, v_pool, cu, i32(lens), table, ps,
+                                   sum((n + 127) // 128 for n in q_lens), nq, nkv, d, window, d ** -0.5, err)
+        torch.cuda.synchronize()
+        assert int(err.item()) == 0, label
+        want = _dense_attention(qs, ks, vs, lens, q_lens, nq, nkv, d, window)
+        e = float(((out.double() - want).abs().max(dim=1).values /
+                   want.abs().max(dim=1).values.clamp_min(1e-30)).max())
+        assert e < 1.5e-2, (label, e)
+        worst = max(worst, e)
+    print(f"worst row error {worst:.2e}")
