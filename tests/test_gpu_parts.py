@@ -104,6 +104,48 @@ def test_linear_of_hundreds_of_tokens_in_wide_slices_has_room_for_every_slice(M,
     rt.check_errors()
 
 
+def test_linear_at_random_shapes():
+    """Products drawn at random through the runtime's choice of kernel (few
+    tokens with the weights on the wide side and slices of the inner dimension,
+    wide slices for hundreds of tokens, one SM or two per tile, tiles of once or
+    twice the rows, the silu epilogue, the kernels for shapes the tensor-core
+    kernels refuse), with and without a bias, bfloat16 and float results."""
+    from crane_b200.kernels import Partials
+    rt = runtime(torch.bfloat16, rows=8192)
+    worst = 0.0
+    for i in range(160):
+        rng = np.random.default_rng(9000 + i)
+        torch.manual_seed(9000 + i)
+        M = int(rng.choice([1, 2, 7, 8, 16, 17, 33, 64, 65, 100, 128, 129, 200, 256, 257, 300, 512, 700, 798,
+                            1000, 1024, 1025, 1500, 2048, 3000, 4096, 5000]))
+        N = int(rng.choice([8, 16, 64, 100, 128, 136, 256, 320, 384, 1000, 1001, 2048, 3072, 4096, 6144, 12288]))
+        K_ = int(rng.choice([64, 72, 128, 136, 256, 1000, 1536, 2048, 3072, 4096, 6144, 8960, 14336]))
+        if M * N * K_ > 4096 * 12288 * 4096:
+            K_ = 2048
+        bias = torch.randn(N, device=DEV) if rng.random() < 0.4 else None
+        out_dtype = torch.float32 if rng.random() < 0.25 else torch.bfloat16
+        silu = rng.random() < 0.25 and N % 32 == 0 and bias is None and out_dtype == torch.bfloat16
+        label = f"{i}: {M} x {N} x {K_}, bias {bias is not None}, {out_dtype}, silu {silu}"
+        x = torch.randn(M, K_, device=DEV).bfloat16()
+        w = (torch.randn(N, K_, device=DEV) / K_ ** 0.5).bfloat16()
+        want = x.double() @ w.double().T + (bias.double() if bias is not None else 0.0)
+        if silu:
+            got = torch.full((M, N // 2), 7.0, device=DEV, dtype=torch.bfloat16)
+            if not rt.linear_silu_mul(x, w, got):
+                continue
+            gu = want.view(M, N // 32, 2, 16)                # the weights' rows: 16 of gate, 16 of up, ...
+            g, u = gu[:, :, 0].reshape(M, N // 2), gu[:, :, 1].reshape(M, N // 2)
+            want = g / (1 + torch.exp(-g)) * u
+        else:
+            got = whole(rt.linear(x, w, bias, "t" + str(i % 3), out_dtype=out_dtype), out_dtype)
+        torch.cuda.synchronize()
+        rt.check_errors()
+        e = rel_err(got, want)
+        assert e < (6e-3 if out_dtype == torch.bfloat16 else 2e-5 * max(1.0, (K_ / 256) ** 0.5)), (label, e)
+        worst = max(worst, e)
+    print(f"worst error {worst:.2e}")
+
+
 def test_float_logits_from_split_k_slices():
     """A head narrow enough to be computed in slices of the inner dimension: the
     float result is the slices' sum in float (no rounding to bfloat16 between)."""
