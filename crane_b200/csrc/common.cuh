@@ -172,7 +172,8 @@ static inline int crane_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, si
     cfg.attrs = attr;
     cfg.numAttrs = g_crane_pdl ? 1 : 0;
     const cudaError_t rc = cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
-    return rc != cudaSuccess ? (int)rc : (int)cudaGetLastError();
+    const cudaError_t last = cudaGetLastError();        // read, and with that cleared, in either case:
+    return rc != cudaSuccess ? (int)rc : (int)last;     // a refused launch must not fail the next one too
 }
 
 // The same for a kernel whose CTAs form thread-block clusters of `cluster` CTAs.
@@ -194,5 +195,6 @@ static inline int crane_launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 b
     cfg.attrs = attr;
     cfg.numAttrs = g_crane_pdl ? 2 : 1;
     const cudaError_t rc = cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
-    return rc != cudaSuccess ? (int)rc : (int)cudaGetLastError();
+    const cudaError_t last = cudaGetLastError();        // read, and with that cleared, in either case:
+    return rc != cudaSuccess ? (int)rc : (int)last;     // a refused launch must not fail the next one too
 }

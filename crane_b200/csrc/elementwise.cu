@@ -96,23 +96,29 @@ __global__ void embed_gather_kernel(const int* __restrict__ tokens, const T* __r
 // over the wanted positions only).
 // A thread keeps its up to PER elements of the row in registers between the
 // sum of squares and the scaling, so the row is read once.
+// (Up to 1024 threads: the registers of a thread are bounded to what such a block can have.  Rows
+// of more than 8192 elements, 16 or 32 per thread, fetch the norm's weights when they scale.)
 template <typename T, int PER>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, GemmOut<T> delta, int has_delta,
-                                   const float* __restrict__ w, const int* __restrict__ rows,
-                                   T* __restrict__ out, int hidden, float eps) {
+__global__ void __launch_bounds__(1024)
+add_rmsnorm_kernel(float* __restrict__ x, GemmOut<T> delta, int has_delta,
+                   const float* __restrict__ w, const int* __restrict__ rows,
+                   T* __restrict__ out, int hidden, float eps) {
     __shared__ float scratch[32];
+    constexpr bool EARLY_W = PER <= 8;
     const int r = blockIdx.x;
     const int row = rows ? rows[r] : r;          // written by the host's copy, long before
     float* xr = x + (long long)row * hidden;
     const long long dbase = (long long)row * hidden;
     const bool write_x = (rows == nullptr) && has_delta;
-    float v[PER], wv[PER];
+    float v[PER], wv[EARLY_W ? PER : 1];
     float ss = 0.f;
     pdl_launch_dependents();
+    if (EARLY_W) {
 #pragma unroll
-    for (int k = 0; k < PER; ++k) {                 // the norm's weight depends on no earlier kernel
-        const int c = threadIdx.x + k * blockDim.x;
-        wv[k] = c < hidden ? w[c] : 0.f;
+        for (int k = 0; k < PER; ++k) {             // the norm's weight depends on no earlier kernel
+            const int c = threadIdx.x + k * blockDim.x;
+            wv[k] = c < hidden ? w[c] : 0.f;
+        }
     }
     pdl_wait();
 #pragma unroll
@@ -139,7 +145,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, GemmOut<T> delta, int 
 #pragma unroll
     for (int k = 0; k < PER; ++k) {
         const int c = threadIdx.x + k * blockDim.x;
-        if (c < hidden) o[c] = from_f32<T>(v[k] * rstd * wv[k]);
+        if (c < hidden) o[c] = from_f32<T>(v[k] * rstd * (EARLY_W ? wv[k] : w[c]));
     }
 }
 

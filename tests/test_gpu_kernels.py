@@ -72,6 +72,39 @@ def test_add_rmsnorm(K, dtype, hidden):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,hidden", [(3, 10000), (64, 16384), (9, 32768), (2, 8200)])
+def test_add_rmsnorm_of_rows_wider_than_8192(K, dtype, rows, hidden):
+    """16 or 32 elements per thread at up to 1024 threads: the kernel must fit a
+    block of that size (it once asked for more registers than such a block has)."""
+    torch.manual_seed(hidden)
+    x0 = torch.randn(rows, hidden, device=DEV) * 2
+    delta = torch.randn(rows, hidden, device=DEV).to(dtype)
+    w = torch.rand(hidden, device=DEV) + 0.5
+    x = x0.clone()
+    out = torch.empty(rows, hidden, device=DEV, dtype=dtype)
+    K.add_rmsnorm(x, delta, w, 1e-5, out)
+    want_x = x0 + delta.float()
+    assert torch.equal(x, want_x)
+    want = want_x.double() * torch.rsqrt((want_x.double() ** 2).mean(-1, keepdim=True) + 1e-5) * w.double()
+    assert rel_err(out, want) < (2e-6 if dtype == torch.float32 else 5e-3)
+    idx = torch.tensor([rows - 1, 0], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(2, hidden, device=DEV, dtype=dtype)
+    K.add_rmsnorm(x, None, w, 1e-5, out2, idx)
+    assert rel_err(out2, want[[rows - 1, 0]]) < (2e-6 if dtype == torch.float32 else 5e-3)
+
+
+def test_a_refused_launch_does_not_fail_the_next_one(K):
+    from crane_b200.kernels import KernelError
+    x = torch.randn(2, 40000, device=DEV)                      # wider than the norm kernels take
+    with pytest.raises(KernelError):
+        K.add_rmsnorm(x, None, torch.ones(40000, device=DEV), 1e-5, torch.empty_like(x))
+    y = torch.randn(2, 64, device=DEV)
+    out = torch.empty_like(y)
+    K.add_rmsnorm(y, None, torch.ones(64, device=DEV), 1e-5, out)
+    assert rel_err(out, y.double() * torch.rsqrt((y.double() ** 2).mean(-1, keepdim=True) + 1e-5)) < 2e-6
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_add_rmsnorm_from_partial_sums(K, dtype):
     from crane_b200.kernels import Partials
     n, hidden = 5, 300
