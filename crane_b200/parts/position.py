@@ -34,7 +34,9 @@ class Rope(Part):
         base = float(self.params["theta"])
         alpha = float(self.params.get("alpha") or 0.0)
         if alpha > 0.0:
-            base = base * alpha ** (d / (d - 2.0))
+            # a head of 2 elements: the reference's float division gives an infinite exponent, the base
+            # becomes infinite (or 0, or stays), and its power 0 is 1 either way
+            base = base * alpha ** (d / (d - 2.0) if d != 2 else float("inf"))
         powers = np.array([base ** (i / d) for i in range(0, d, 2)], dtype=np.float64)
         return (np.float32(1.0) / powers.astype(np.float32)).astype(np.float32)
 

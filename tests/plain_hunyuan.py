@@ -114,7 +114,8 @@ def rope_inv_freq(head_dim: int, theta: float, alpha: float) -> np.ndarray:
     float32 division (modeling.rs:197-239)."""
     base = float(theta)
     if alpha > 0.0:
-        base = base * float(alpha) ** (head_dim / (head_dim - 2.0))
+        # (head_dim 2: the reference's f64 division by zero gives +inf; powf(0) of the result is 1)
+        base = base * float(alpha) ** (head_dim / (head_dim - 2.0) if head_dim != 2 else float("inf"))
     out = np.empty(head_dim // 2, dtype=np.float32)
     for n, i in enumerate(range(0, head_dim, 2)):
         out[n] = np.float32(1.0) / np.float32(base ** (i / head_dim))

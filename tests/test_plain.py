@@ -44,6 +44,22 @@ def test_rope_depends_on_relative_position_only():
     assert np.allclose(y[..., 3] ** 2 + y[..., 19] ** 2, x[..., 3] ** 2 + x[..., 19] ** 2)
 
 
+def test_rope_of_a_head_of_two_elements_with_alpha():
+    """d / (d - 2) divides by zero: the reference's float arithmetic gives an
+    infinite exponent and a frequency of 1 (modeling.rs:203-208); the engine's
+    position part and the plain function follow it, neither raises."""
+    from crane_b200.config import PartSpec
+    from crane_b200.parts import build_part
+    assert ph.rope_inv_freq(2, 10000.0, 1000.0).tolist() == [1.0]
+    assert ph.rope_inv_freq(2, 10000.0, 0.5).tolist() == [1.0]
+    rope = build_part(PartSpec("position", "rope", {"head_dim": 2, "theta": 10000.0, "alpha": 1000.0,
+                                                    "max_positions": 16}))
+    assert rope.inv_freq().tolist() == [1.0]
+    for d in (4, 6, 128):
+        rope = build_part(PartSpec("position", "rope", {"head_dim": d, "theta": 1e4, "alpha": 7.0, "max_positions": 16}))
+        assert np.array_equal(rope.inv_freq(), ph.rope_inv_freq(d, 1e4, 7.0))
+
+
 def test_rms_norm_formula():
     x = np.array([[3.0, 4.0]])
     w = np.array([2.0, 0.5])
