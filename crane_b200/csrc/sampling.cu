@@ -141,7 +141,7 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
     if (k > MAXK) k = MAXK;
     if (k > vocab) k = vocab;
 
-    if (k <= 0 || k >= vocab) {                                  // whole vocabulary
+    if (k <= 0 || (k >= vocab && !p_active)) {                   // whole vocabulary (top-p needs the sorted candidates)
         for (int i = threadIdx.x; i < vocab; i += THREADS) {
             const float v = gumbel_score(row[i], inv_t, key, i);
             if (better(v, i, b)) { b.v = v; b.i = i; }

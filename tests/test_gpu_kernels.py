@@ -497,6 +497,24 @@ def test_top_k_and_top_p(K):
     assert seen_p == set(int(i) for i in keep) == set(best[:2])      # .64 <= .7, plus the one after
 
 
+def test_top_p_in_a_vocabulary_smaller_than_the_candidate_list(K):
+    """top-p applies also where top-k cannot restrict anything (a vocabulary of
+    at most 64 entries, or top-k >= vocabulary)."""
+    logits = torch.tensor([[0.0, 5.0, 1.0, -2.0, 4.0]], device=DEV)       # p ~ .72 .26 .01 ...
+    out = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for topk in (0, 5, 64, 100):
+        seen = set()
+        for c in range(200):
+            K.sample(logits, out, **_host_opts([1.0], [topk], [0.3], [9], [c]))
+            seen.add(int(out[0]))
+        assert seen == {1}, (topk, seen)          # .72 > .3: the first candidate alone
+        seen = set()
+        for c in range(200):
+            K.sample(logits, out, **_host_opts([1.0], [topk], [0.8], [9], [c]))
+            seen.add(int(out[0]))
+        assert seen == {1, 4}, (topk, seen)       # .72 <= .8, plus the one after
+
+
 def test_sampling_frequencies_follow_the_softmax(K):
     vocab = 7
     logits = torch.tensor([[0.0, 1.0, 2.0, -1.0, 0.5, 1.5, -3.0]], device=DEV)
