@@ -15,18 +15,20 @@ pytestmark = pytest.mark.gpu
 
 
 def draw(rng, big):
+    """(config, page size, prompt lengths, weight scale).  The weights' scale falls with the width,
+    as a trained model's does: a product then neither grows nor shrinks its input much, and the
+    bounds measure rounding, not a draw's amplification of it (at a scale of 0.08 and a width of
+    2,056 four layers amplify float32 rounding to 2e-5 and bfloat16 rounding to 5e-2)."""
     if big:      # sizes at which the tensor-core kernels run
         d = int(rng.choice([64, 128, 128, 256, 96]))
         hidden = int(rng.choice([256, 512, 1024, 1536, 320, 2048]))
         inter = int(rng.choice([512, 1024, 1536, 2816, 352]))
-        # weights of the scale a trained model starts from: a product neither grows nor shrinks its
-        # input much, so that the bfloat16 bound measures rounding and not this draw's amplification
         layers, longest, std = int(rng.choice([1, 2])), 900, min(0.08, 0.9 / hidden ** 0.5)
     else:
         d = int(rng.choice([16, 32, 48, 64, 80, 96, 112, 128, 144, 160, 192, 208, 256, 6, 20, 40]))
         hidden = int(rng.choice([64, 72, 100, 136, 200, 264, 520, 1000, 50, 36]))
         inter = int(rng.choice([96, 100, 250, 352, 1000, 1336, 80, 24]))
-        layers, longest, std = int(rng.choice([1, 2, 3, 4])), 330, 0.08
+        layers, longest, std = int(rng.choice([1, 2, 3, 4])), 330, min(0.08, 0.9 / hidden ** 0.5)
     nkv = int(rng.choice([1, 2, 3, 5]))
     cfg = {
         "architectures": ["HunYuanDenseV1ForCausalLM"], "model_type": "hunyuan_v1_dense",
