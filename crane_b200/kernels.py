@@ -307,10 +307,10 @@ class Kernels:
 
         A model of the time of one round of tiles, in microseconds, fitted to
         measurements of 13 shapes (2048 .. 8192 tokens, inner dimensions 2048 ..
-        14336): an SM takes its operands in from L2 at about 83 GB/s (all of them
-        together 12.3 TB/s: (256 + width) x 128 bytes per 64-wide k-block for its
-        128 rows of a 256-row tile, (512 + width) x 128 for its 256 rows of a
-        512-row tile) and multiplies 128 rows x width x 16 in width / 2 clocks;
+        14336): the operand bytes a CTA moves through its shared memory ((256 +
+        width) x 128 bytes per 64-wide k-block for its 128 rows of a 256-row
+        tile, (512 + width) x 128 for its 256 rows of a 512-row tile) cost 1.2e-5
+        us each, and 128 rows x width x 16 are multiplied in width / 2 clocks;
         the two overlap, not perfectly (a 3-norm).  Tiles of 512 rows move the
         least bytes per product but have no second accumulator to work into while
         the epilogue reads the first, so their epilogue adds to every round: they
