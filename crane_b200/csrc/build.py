@@ -257,5 +257,16 @@ def load_kernels(head_sizes: Sequence[int] = ()) -> ctypes.CDLL:
         return _loaded[key]
 
 
+def load_microbench() -> ctypes.CDLL:
+    """The two measurements of the machine in microbench.cu (a small library of
+    its own: no model needs it, so no first call compiles it)."""
+    with _lock:
+        if "microbench" not in _loaded:
+            path = _build("libcrane_microbench", ["microbench.cu"], nvcc_path(), NVCC_FLAGS, [])
+            _loaded["microbench"] = ctypes.CDLL(path)
+        return _loaded["microbench"]
+
+
 def build_all() -> Dict[str, str]:
-    return {"host": build_host(), "kernels": build_kernels()}
+    return {"host": build_host(), "kernels": build_kernels(),
+            "microbench": _build("libcrane_microbench", ["microbench.cu"], nvcc_path(), NVCC_FLAGS, [])}

@@ -190,6 +190,44 @@ def rmsnorm(a):
     _report(f"add_rmsnorm {a.rows}x{a.hidden}", t, a.rows * a.hidden * (4 + 2 + 4 + 2), 0.0, {"sets": a.sets})
 
 
+def hardware(a):
+    """What one thread can issue and what a barrier across the SMs costs."""
+    from ctypes import c_int, c_void_p
+    from .csrc import build
+    lib = build.load_microbench()
+    lib.crane_microbench_mma_issue.argtypes = [c_int, c_int, c_void_p, c_void_p]
+    lib.crane_microbench_mma_issue.restype = c_int
+    lib.crane_microbench_grid_barrier.argtypes = [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+    lib.crane_microbench_grid_barrier.restype = c_int
+    st = torch.cuda.current_stream(DEV).cuda_stream
+    out = torch.zeros(3, dtype=torch.int64, device=DEV)
+    reps = 500
+    for n in (64, 128, 256):
+        for _ in range(2):                                   # the second run is reported
+            rc = lib.crane_microbench_mma_issue(n, reps, out.data_ptr(), st)
+            assert rc == 0, rc
+            torch.cuda.synchronize()
+        issue, done, ok = out.tolist()
+        print(json.dumps({"measurement": f"tcgen05.mma 128x{n}x16 issued back to back by one thread",
+                          "products": 4 * reps, "cycles_per_product_issue_loop": round(issue / (4 * reps), 1),
+                          "cycles_per_product_until_complete": round(done / (4 * reps), 1),
+                          "tensor_core_cycles_per_product": n // 2, "completed": bool(ok)}))
+    sms = torch.cuda.get_device_properties(DEV).multi_processor_count
+    counter = torch.zeros(1, dtype=torch.int32, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    cycles = torch.zeros(1, dtype=torch.int64, device=DEV)
+    rounds = 1000
+    for ctas in (sms, sms // 2, 32):
+        for _ in range(2):
+            counter.zero_(); err.zero_()
+            rc = lib.crane_microbench_grid_barrier(ctas, rounds, counter.data_ptr(), cycles.data_ptr(), err.data_ptr(), st)
+            assert rc == 0, rc
+            torch.cuda.synchronize()
+        print(json.dumps({"measurement": "barrier across the SMs (release-add, acquire-loads)", "ctas": ctas,
+                          "rounds": rounds, "cycles_per_barrier": round(int(cycles.item()) / rounds),
+                          "wait_ran_out": bool(int(err.item()))}))
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--warmup", type=int, default=3)
@@ -211,6 +249,7 @@ def main(argv=None) -> int:
         p.add_argument("--batch", type=int, default=8); p.add_argument("--context", type=int, default=8192)
         p.add_argument("--tokens", type=int, default=2048); p.add_argument("--splits", type=int, default=0)
         p.add_argument("--kernel", default="auto", choices=["auto", "mma"])
+    sub.add_parser("hardware", help="issue rate of tcgen05.mma from one thread; cost of a barrier across the SMs")
     r = sub.add_parser("rmsnorm")
     r.add_argument("--rows", type=int, default=2048); r.add_argument("--hidden", type=int, default=2048)
     r.add_argument("--sets", type=int, default=1)
@@ -218,7 +257,7 @@ def main(argv=None) -> int:
     global GRAPH
     GRAPH = not a.no_graph
     {"gemm": gemm, "decode-attention": decode_attention, "prefill-attention": prefill_attention,
-     "rmsnorm": rmsnorm}[a.what](a)
+     "rmsnorm": rmsnorm, "hardware": hardware}[a.what](a)
     return 0
 
 
