@@ -398,10 +398,13 @@ class ModelRunner:
 
     # ---- captured decode steps -----------------------------------------
     def _bucket(self, n: int) -> int:
+        """The batch size a decode step of ``n`` entries is padded to: the next power
+        of two, or the most entries a step can have where that is less (a limit
+        of 96 requests has the buckets 1, 2, ..., 64, 96)."""
         b = 1
         while b < n:
             b *= 2
-        return min(b, self.cap_entries) if b <= self.cap_entries else 0
+        return min(b, self.cap_entries)
 
     MAX_SHAPE_GRAPHS = 256      # graphs of small steps kept; the least recently used one goes first
 

@@ -121,8 +121,9 @@ class GqaAttention(Part):
             # single decoded tokens: rotary encoding, head norms, the cache write, attention over
             # key slices (enough of them to fill the device) in one kernel, their merge in a second
             splits = k.decode_splits(ctx.n_entries, self.nkv, rt.num_sms, self.max_splits)
-            # slices x entries never exceed two CTAs per SM: that bounds the slices' scratch rows
-            rows = self.nq * (2 * rt.num_sms // self.nkv + 1)
+            # slices x entries never exceed two CTAs per SM, or the slices are 4 at most: that bounds
+            # the slices' scratch rows
+            rows = self.nq * max(2 * rt.num_sms // self.nkv + 1, 4 * rt.max_decode_rows)
             part_o = rt.ws.get("attn_part_o", rows, self.d, torch.float32, cap=rows)
             part_ml = rt.ws.get("attn_part_ml", rows, 2, torch.float32, cap=rows)
             k.paged_decode_attention_fused(qkv, self.qkv_cols, self.own_kv, cos, sin, self.q_norm,

@@ -332,6 +332,42 @@ def test_small_steps_replay_graphs_with_the_same_logits(name, model_folders):
         assert (a - b).abs().max() <= 2e-3 * a.abs().max()
 
 
+def test_decode_steps_under_a_limit_that_is_no_power_of_two(model_folders):
+    """Six requests at most: decode steps of five or six entries are padded to six
+    (not to eight, which the step's buffers could not hold, and not left to the
+    path of mixed steps, which once took them: rotary kernel, decode kernel and
+    prefill kernel over padding rows instead of the one fused kernel)."""
+    from crane_b200.engine import StepEntry
+    folder = model_folders("S18", "bfloat16")
+    vocab = tiny_configs.TINY["S18"]["config"]["vocab_size"]
+    rng = np.random.default_rng(8)
+    prompts = [rng.integers(0, vocab, n).tolist() for n in (40, 70, 33, 90, 65, 50)]
+    outs = {}
+    for limit in (6, 8):
+        m = load(folder, "bf16", page_size=64, num_pages=32, max_concurrent=limit, max_batched_tokens=512)
+        r = m.runner
+        assert [r._bucket(n) for n in (1, 2, 3, 4, 5, 6)] == [1, 2, 4, 4, min(8, limit), min(8, limit)]
+        for i, p in enumerate(prompts):
+            r.step([StepEntry(i, p, [])])
+        got, per_step = [], []
+        for t in range(3):
+            toks = [int(rng.integers(0, vocab)) for _ in range(5)]
+            before = r.rt.launches
+            got.append(r.step([StepEntry(i, [toks[i]], [0]) for i in range(5)]).float().cpu())
+            per_step.append(r.rt.launches - before)
+        r.rt.check_errors()
+        outs[limit] = (got, per_step[-1])
+        rng = np.random.default_rng(8)
+        prompts = [rng.integers(0, vocab, n).tolist() for n in (40, 70, 33, 90, 65, 50)]
+    # the decode step's kernels under either limit: per layer norm, q/k/v, fused attention, output, norm,
+    # gate/up, silu, down; embedding, final norm, head in slices and their sum.  (Six entries take 12
+    # key slices each, whose merge is a launch of its own; eight take 8, which merge in their cluster.)
+    layers = tiny_configs.TINY["S18"]["config"]["num_hidden_layers"]
+    assert outs[6][1] == 9 * layers + 4 and outs[8][1] == 8 * layers + 4, (outs[6][1], outs[8][1])
+    for a, b in zip(outs[6][0], outs[8][0]):
+        assert (a - b).abs().max() <= 2e-3 * a.abs().max()
+
+
 def test_refusals(model_folders):
     folder = model_folders("A", "float32")
     m = load(folder, "fp32", page_size=16, num_pages=16, max_concurrent=2, max_batched_tokens=64)

@@ -16,12 +16,15 @@ def test_decode_splits_fill_the_device_and_fit_the_scratch(nkv):
         s = Kernels.decode_splits(entries, nkv, SMS)
         assert 1 <= s <= 64
         if s > 1:
-            # never more CTAs than two per SM, which is also what the slices' scratch is sized for
-            assert entries * nkv * s <= 2 * SMS
+            # never more CTAs than two per SM, or at most 4 slices (more CTAs than fit at once are cut
+            # finer so that the last round over the SMs is fuller): what the slices' scratch is sized for
+            assert entries * nkv * s <= 2 * SMS or s <= 4
         assert not 8 < s <= 11 and not 32 < s <= 40      # ranges that measured slower than 8 / 32
     assert Kernels.decode_splits(8, 4, SMS) == 8           # the headline shape: one cluster per (request, kv head)
     assert Kernels.decode_splits(1, 4, SMS) == 64
     assert Kernels.decode_splits(64, 4, SMS) == 1
+    # more CTAs than the 296 places: slices where the last round over the SMs would be nearly empty
+    assert [Kernels.decode_splits(b, 4, SMS) for b in (72, 80, 96, 112, 128, 160, 192, 256)] == [1, 4, 2, 1, 1, 2, 1, 1]
     assert Kernels.decode_splits(1, 4, SMS, cap=16) == 16
 
 
