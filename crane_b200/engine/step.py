@@ -29,6 +29,13 @@ from ..weights.loader import open_folder
 from ..weights.safetensors_io import DictSource
 
 
+# A decode step whose longest context is at most this many keys takes at most 8 key slices per
+# (request, kv head), which merge in their cluster without a second kernel (see
+# ``Kernels.decode_splits``).
+SHORT_CONTEXT = 2048
+SHORT_GRAPH_KEY = 1 << 20
+
+
 @dataclass
 class StepEntry:
     """A request's next tokens in this step and the places among them whose
@@ -389,7 +396,10 @@ class ModelRunner:
         self.steps += 1
         try:
             if ctx.graph_bucket:
-                return self._replay(ctx, ctx.graph_bucket)[:ctx.real_entries]
+                # (a graph holds the number of key slices its attention was recorded with: short
+                # contexts, which take fewer, have graphs of their own)
+                short = ctx.max_kv_len <= SHORT_CONTEXT
+                return self._replay(ctx, ctx.graph_bucket + (SHORT_GRAPH_KEY if short else 0))[:ctx.real_entries]
             if ctx.graph_key is not None and ctx.replay:
                 return self._replay(ctx, ctx.graph_key)[:ctx.real_want]
             return self.model.forward(ctx, self.pools.layers)[:ctx.real_want]

@@ -378,7 +378,7 @@ class Kernels:
             float(scale), err.data_ptr(), self._stream(q)), "paged_attention_simt")
 
     @staticmethod
-    def decode_splits(entries: int, nkv: int, sms: int, cap: int = 64) -> int:
+    def decode_splits(entries: int, nkv: int, sms: int, cap: int = 64, max_keys: int = 1 << 30) -> int:
         """Key slices per (request, kv head) of the fused decode attention: enough CTAs to fill
         the device twice over (two fit on an SM), at most ``cap`` (the merge kernel takes 64);
         beyond that, the number of slices that fills the rounds over the SMs best.
@@ -404,6 +404,11 @@ class Kernels:
                     best, best_cost = s, cost
             return best
         splits = max(1, min(cap, 64, slots // ctas))
+        if splits > 8 and max_keys <= 2048:
+            # few keys: 8 slices, which merge in their cluster, beat more slices and the merge kernel
+            # (one request at a context of 256 / 1,024: 1.366 -> 1.284 / 1.380 -> 1.313 ms per step; four
+            # requests: 1.440 -> 1.329 / 1.434 -> 1.387 ms; at 4,096 keys more slices win again)
+            return 8
         if 8 < splits <= 11:
             return 8
         if 32 < splits <= 40:

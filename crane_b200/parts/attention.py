@@ -120,7 +120,8 @@ class GqaAttention(Part):
         if decode and self.d % 4 == 0:
             # single decoded tokens: rotary encoding, head norms, the cache write, attention over
             # key slices (enough of them to fill the device) in one kernel, their merge in a second
-            splits = k.decode_splits(ctx.n_entries, self.nkv, rt.num_sms, self.max_splits)
+            splits = k.decode_splits(ctx.n_entries, self.nkv, rt.num_sms, self.max_splits,
+                                     max_keys=ctx.max_kv_len)
             # slices x entries never exceed two CTAs per SM, or the slices are 4 at most: that bounds
             # the slices' scratch rows
             rows = self.nq * max(2 * rt.num_sms // self.nkv + 1, 4 * rt.max_decode_rows)

@@ -26,6 +26,9 @@ def test_decode_splits_fill_the_device_and_fit_the_scratch(nkv):
     # more CTAs than the 296 places: slices where the last round over the SMs would be nearly empty
     assert [Kernels.decode_splits(b, 4, SMS) for b in (72, 80, 96, 112, 128, 160, 192, 256)] == [1, 4, 2, 1, 1, 2, 1, 1]
     assert Kernels.decode_splits(1, 4, SMS, cap=16) == 16
+    # few keys: at most the 8 slices that merge in their cluster
+    assert Kernels.decode_splits(1, 4, SMS, max_keys=1024) == 8 and Kernels.decode_splits(1, 4, SMS, max_keys=4096) == 64
+    assert Kernels.decode_splits(4, 4, SMS, max_keys=2048) == 8 and Kernels.decode_splits(16, 4, SMS, max_keys=100) == 4
 
 
 def test_slices_for_fills_the_last_wave():
