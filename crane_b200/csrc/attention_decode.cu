@@ -611,21 +611,32 @@ paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
     const uint32_t wbase = smem_u32(smem) + warp * NSTAGE * STAGE_BYTES;
     const uint32_t wbar = smem_u32(&full[warp * NSTAGE]);
     bool bad_page = false;
-    // lane 0 asks for local tile `idx` (global tile `tile`) of this warp
+    // A tile of 32 keys lies in one page, or, with pages of 8 or 16 tokens, in several: it comes in
+    // pieces of `piece` keys (the tensor maps' box), each asked for by a lane of its own.
+    const int piece = page_size < TILE ? page_size : TILE;
+    const int n_pieces = TILE / piece;
+    // lanes 0 .. n_pieces - 1 ask for local tile `idx` (global tile `tile`) of this warp
     auto issue = [&](int idx, int tile) {
-        if (lane == 0) {
-            const int key0 = tile * TILE;
+        if (lane < n_pieces) {
+            // a piece wholly behind the last key or wholly before the window's first one has no page
+            // of its own any more (or not yet): the nearest piece that has one is read in its place;
+            // its keys are masked by their positions, only the byte count has to be complete
+            int key0 = tile * TILE + lane * piece;
+            if (key0 > pos) key0 = pos / piece * piece;
+            if (key0 + piece <= lo) key0 = lo / piece * piece;
             int page = table[key0 / page_size];
             if (page < 0 || page >= num_pages) {
                 bad_page = true;                   // reported below; the copy reads page 0 instead
                 page = 0;
             }
             const int row = (page * nkv + g) * page_size + key0 % page_size;
-            const uint32_t st = wbase + (idx % NSTAGE) * STAGE_BYTES;
+            const uint32_t st = wbase + (idx % NSTAGE) * STAGE_BYTES + lane * piece * 128;
             const uint32_t bar = wbar + (idx % NSTAGE) * 8;
             // the warp's reads of this stage (generic proxy) come before the copies (async proxy)
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_expect_tx(bar, STAGE_BYTES);
+            // (the barrier's phase cannot end before lane 0 has arrived with the byte count, so the
+            // other lanes' copies may well land first)
+            if (lane == 0) mbar_expect_tx(bar, STAGE_BYTES);
             tma_tile_2d(st, &k_map, bar, 0, row);
             tma_tile_2d(st + HALF_TILE_BYTES, &k_map, bar, 64, row);
             tma_tile_2d(st + TILE128_BYTES, &v_map, bar, 0, row);
@@ -1124,13 +1135,14 @@ bool cluster_merge_enabled() {
     }
     return on == 1;
 }
-// The pool as [rows, 128] bf16; box of 64 elements x TILE rows, 128-byte swizzle.
-bool pool_map(CUtensorMap* map, const void* pool, long long rows) {
+// The pool as [rows, 128] bf16; box of 64 elements x box_rows rows (a tile's 32, or a page's 8 or 16),
+// 128-byte swizzle.
+bool pool_map(CUtensorMap* map, const void* pool, long long rows, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn || ((uintptr_t)pool & 15)) return false;
     cuuint64_t dims[2] = {(cuuint64_t)D128, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)D128 * 2};
-    cuuint32_t box[2] = {64u, (cuuint32_t)TILE};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1149,7 +1161,9 @@ int launch_decode_tma(const void* q, void* out, float* part_o, float* part_ml, c
     constexpr int smem = (tiles > merge ? tiles : merge) + 1024;
     CUtensorMap km, vm;
     const long long rows = (long long)num_pages * nkv * page_size;
-    if (!pool_map(&km, k_pool, rows) || !pool_map(&vm, v_pool, rows)) return (int)cudaErrorInvalidValue;
+    const int box_rows = page_size < TILE ? page_size : TILE;
+    if (!pool_map(&km, k_pool, rows, box_rows) || !pool_map(&vm, v_pool, rows, box_rows))
+        return (int)cudaErrorInvalidValue;
     if (cluster) {
         auto kern = paged_decode_attn_tma_kernel<FUSED, true, GENERAL>;
         static bool configured = false;
@@ -1192,7 +1206,10 @@ int launch_decode(const void* q, void* out, float* part_o, float* part_ml, const
         configured = true;
     }
     dim3 grid(n_splits, nkv, n_entries);
-    if (D == D128 && page_size % TILE == 0 && tma_path_enabled()) {
+    // pages of whole tiles, or tiles of whole pages (8 or 16 tokens: a piece of a tile is then a multiple
+    // of the 1024 bytes the swizzle pattern repeats after)
+    const bool pages_fit = page_size % TILE == 0 || (page_size >= 8 && TILE % page_size == 0);
+    if (D == D128 && pages_fit && tma_path_enabled()) {
         // 2 to 8 slices merge themselves in a cluster; more go through scratch memory and a second kernel
         const bool cluster = n_splits > 1 && n_splits <= 8 && cluster_merge_enabled();
         const int rc = launch_decode_tma<FUSED, GENERAL>(q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len,

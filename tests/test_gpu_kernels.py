@@ -704,7 +704,9 @@ def test_gemm_tcgen05_refuses_what_it_cannot_take(K, err):
     (128, 16, 4, 64, 0, 1), (128, 16, 4, 64, 0, 7), (64, 8, 8, 16, 0, 3), (16, 4, 2, 8, 0, 2),
     (32, 8, 2, 16, 50, 4), (48, 6, 3, 32, 0, 32), (128, 32, 2, 128, 300, 5),
     (80, 10, 5, 16, 0, 3), (96, 6, 2, 32, 0, 1), (112, 4, 4, 16, 90, 4), (160, 4, 2, 16, 0, 2),
-    (192, 6, 1, 32, 0, 5), (256, 8, 2, 64, 0, 6)])
+    (192, 6, 1, 32, 0, 5), (256, 8, 2, 64, 0, 6),
+    # head size 128 with pages smaller than the kernel's 32-key tiles: a tile comes in several pieces
+    (128, 8, 2, 16, 0, 3), (128, 16, 4, 16, 0, 8), (128, 4, 4, 8, 45, 2), (128, 8, 1, 16, 333, 12)])
 def test_paged_decode_attention(K, err, d, nq, nkv, page_size, window, splits):
     """Single tokens of requests of very different lengths, one of them with a
     far key that must dominate; every slicing of the keys gives the same."""
@@ -783,7 +785,8 @@ def test_paged_prefill_attention_mixed_batch(K, err, d, nq, nkv, page_size, wind
     (128, 16, 4, 64, 0, 8, True, 6), (128, 8, 8, 32, 0, 2, False, 0), (128, 12, 4, 64, 100, 5, True, 0),
     (128, 16, 4, 64, 0, 64, True, 0),
     (80, 10, 5, 16, 0, 3, True, 0), (96, 6, 2, 32, 0, 1, False, 4), (112, 8, 4, 16, 90, 4, True, 2),
-    (160, 4, 2, 16, 0, 2, True, 0), (192, 6, 1, 32, 0, 5, False, 0), (256, 8, 2, 64, 0, 6, True, 3)])
+    (160, 4, 2, 16, 0, 2, True, 0), (192, 6, 1, 32, 0, 5, False, 0), (256, 8, 2, 64, 0, 6, True, 3),
+    (128, 16, 4, 16, 0, 8, True, 6), (128, 8, 2, 16, 70, 3, True, 0), (128, 4, 4, 8, 0, 5, False, 2)])
 def test_fused_decode_attention_equals_the_separate_kernels(K, err, d, nq, nkv, page_size, window,
                                                             splits, qk_norm, parts):
     """Rotary encoding, head norms, cache write, attention and merge in one
