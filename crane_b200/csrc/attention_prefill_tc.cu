@@ -1,5 +1,5 @@
 // Flash attention for prompt portions on the 5th-generation tensor cores
-// (head size 128, bf16, pages of 16..128 tokens).  One CTA owns 128 query rows
+// (head size 128, bf16, pages of 16 tokens or a larger power of two).  One CTA owns 128 query rows
 // of one request and one query head and walks over the keys in tiles of 128:
 //
 //   warp 0 (all lanes)    TMA: the Q tile once, then K and V tiles from the
@@ -291,9 +291,10 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tma_load_2d(smem_u32(sm_q), &map_q, smem_u32(q_full), h * D, row0 + r_begin);
             tma_load_2d(smem_u32(sm_q + HALF_BYTES), &map_q, smem_u32(q_full), h * D + 64, row0 + r_begin);
         }
-        const int ps = p.page_size;                    // 16, 32, 64 or 128
+        const int ps = p.page_size;                    // 16, 32, 64, 128 or a larger power of two
         const int shift = 31 - __clz(ps);
-        const int chunks = BKV >> shift;               // pages per tile: 8, 4, 2 or 1
+        const int chunks = ps < BKV ? BKV >> shift : 1;   // pages per tile: 8, 4, 2 or 1 (or a tile is part of a page)
+        const int piece = ps < BKV ? ps : BKV;         // keys per copy
         const int per_kv = 2 * chunks;                 // copies per tile of K (or V)
         const bool worker = lane < 2 * per_kv;
         const int my_kv = lane / per_kv, c = (lane % per_kv) >> 1, hf = lane & 1;
@@ -310,7 +311,7 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 atomicOr(p.err, CRANE_ERR_PAGE_RANGE);
                 page = 0;
             }
-            const int row = (page * p.nkv + g) << shift;
+            const int row = ((page * p.nkv + g) << shift) + (ps > BKV ? ((t_begin + j) * BKV) & (ps - 1) : 0);
             for (int kv = 0; kv < 2; ++kv) {
                 uint64_t* full = kv ? &v_full[s] : &k_full[s];
                 uint64_t* empty = kv ? &v_empty[s] : &k_empty[s];
@@ -319,7 +320,7 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (lane == 0) mbar_expect_tx(smem_u32(full), TILE_BYTES);
                 __syncwarp();
                 if (worker && my_kv == kv)
-                    tma_load_2d(smem_u32(dst + hf * HALF_BYTES + c * ps * 128), kv ? &map_v : &map_k,
+                    tma_load_2d(smem_u32(dst + hf * HALF_BYTES + c * piece * 128), kv ? &map_v : &map_k,
                                 smem_u32(full), hf * 64, row);
             }
         }
@@ -630,9 +631,10 @@ prefill_attn_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                                 (h_a + x) * D + 64, row0 + r_begin);
                 }
             }
-            const int ps = p.page_size;                    // 16, 32, 64 or 128
+            const int ps = p.page_size;                    // 16, 32, 64, 128 or a larger power of two
             const int shift = 31 - __clz(ps);
-            const int chunks = BKV >> shift;               // pages per tile: 8, 4, 2 or 1
+            const int chunks = ps < BKV ? BKV >> shift : 1;   // pages per tile: 8, 4, 2 or 1 (or a tile is part of a page)
+            const int piece = ps < BKV ? ps : BKV;         // keys per copy
             const int per_kv = 2 * chunks;                 // copies per tile of K (or V)
             const bool worker = lane < 2 * per_kv;
             const int my_kv = lane / per_kv, c = (lane % per_kv) >> 1, hf = lane & 1;
@@ -646,7 +648,7 @@ prefill_attn_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     atomicOr(p.err, CRANE_ERR_PAGE_RANGE);
                     page = 0;
                 }
-                const int row = (page * p.nkv + g) << shift;
+                const int row = ((page * p.nkv + g) << shift) + (ps > BKV ? ((t_begin + j) * BKV) & (ps - 1) : 0);
                 for (int kv = 0; kv < 2; ++kv) {
                     uint64_t* full = kv ? &v_full[s] : &k_full[s];
                     uint64_t* empty = kv ? &v_empty[s] : &k_empty[s];
@@ -655,7 +657,7 @@ prefill_attn_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     if (lane == 0) mbar_expect_tx(smem_u32(full), TILE_BYTES);
                     __syncwarp();
                     if (worker && my_kv == kv)
-                        tma_load_2d(smem_u32(dst + hf * HALF_BYTES + c * ps * 128), kv ? &map_v : &map_k,
+                        tma_load_2d(smem_u32(dst + hf * HALF_BYTES + c * piece * 128), kv ? &map_v : &map_k,
                                     smem_u32(full), hf * 64, row);
                 }
             }
@@ -871,7 +873,8 @@ bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols,
 
 CRANE_API int crane_prefill_attention_tc_supports(int d, int nq, int nkv, int page_size) {
     if (nkv <= 0 || nq % nkv != 0) return 0;
-    return d == 128 && (page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128);
+    // pages of 16 to 128 tokens (a 128-key tile is 8 to 1 of them) or larger powers of two (a tile is part of one)
+    return d == 128 && page_size >= 16 && (page_size & (page_size - 1)) == 0;
 }
 
 // total_q_tiles: sum over the entries of ceil(q_len / 128) (or more).  q is [n_tokens, nq * 128].
@@ -885,8 +888,8 @@ CRANE_API int crane_prefill_attention_tc(const void* q, void* out, const void* k
     if (!crane_prefill_attention_tc_supports(d, nq, nkv, page_size)) return (int)cudaErrorInvalidValue;
     CUtensorMap mq, mk, mv;
     const long long pool_rows = (long long)num_pages * nkv * page_size;
-    if (!make_map(&mq, q, n_tokens, (long long)nq * D, BQ) || !make_map(&mk, k_pool, pool_rows, D, page_size) ||
-        !make_map(&mv, v_pool, pool_rows, D, page_size))
+    if (!make_map(&mq, q, n_tokens, (long long)nq * D, BQ) || !make_map(&mk, k_pool, pool_rows, D, page_size < BKV ? page_size : BKV) ||
+        !make_map(&mv, v_pool, pool_rows, D, page_size < BKV ? page_size : BKV))
         return (int)cudaErrorInvalidValue;
     Params p;
     p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.kv_len = kv_len; p.block_table = block_table;

@@ -857,7 +857,8 @@ def test_gemm_tcgen05_with_silu_mul_epilogue(K, err, M, I, K_, bn):
 
 
 @pytest.mark.parametrize("nq,nkv,page_size,window", [(8, 2, 64, 0), (4, 4, 16, 0), (4, 1, 128, 300),
-                                                     (16, 4, 32, 0)])
+                                                     (16, 4, 32, 0), (8, 2, 256, 0), (4, 2, 512, 300),
+                                                     (8, 4, 256, 77)])
 def test_prefill_attention_tcgen05_mixed_batch(K, err, nq, nkv, page_size, window):
     """The tensor-core flash attention (head size 128) on a mixed batch: a portion
     of 300 rows after 211 cached positions, a single decoded token far into a long
