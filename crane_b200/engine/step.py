@@ -156,9 +156,9 @@ class ModelRunner:
         has_state = any(n.kind == "state" for n in self.model.cache_needs())
         self._graphs_ok = (self.cfg.use_cuda_graphs and not self.rt.exact and self.model.capturable()
                            and (not has_state or self.model.state_graph_safe()))
-        # Steps of single tokens are padded to a batch-size bucket with copies of their first entry
-        # unless a mixer keeps state: a copy would advance that request's state twice.  Such a model's
-        # decode steps are padded like steps with prompt portions: rows of no entry, entries without rows.
+        # Steps of single tokens are padded to a batch-size bucket (rows of no entry, entries without
+        # rows) and replay that bucket's graph; with a mixer that keeps state they are padded as
+        # steps with prompt portions are, to a shape of their own.
         self._pad_with_copies = not has_state
         self.graph_replays = 0
         self.graph_captures = 0                    # steps that ran kernel by kernel and were recorded for their shape
@@ -260,8 +260,7 @@ class ModelRunner:
                 if not self.table.is_live(e.request_id):
                     self.table.admit(e.request_id)
                 self.table.extend(e.request_id, c)
-        # a pure decode step is padded to a fixed batch size (copies of one of its entries, which
-        # recompute and rewrite exactly what that entry does) so that a captured graph fits it
+        # a pure decode step is padded to a fixed batch size so that a captured graph fits it
         pad_to = 0
         if (self._graphs_ok and self._pad_with_copies and max(counts) == 1
                 and all(len(e.want) == 1 for e in entries)):
@@ -285,13 +284,6 @@ class ModelRunner:
         real_entries = n_entries
         ids = np.fromiter((entries[i].request_id for i in order), dtype=np.int64, count=n_entries)
         cnt = np.asarray(counts, dtype=np.int32)
-        if pad_to:
-            # (copies of the LAST entry, the shortest: they recompute and rewrite exactly what it does)
-            extra = pad_to - n_entries
-            ids = np.concatenate([ids, np.full(extra, ids[-1], dtype=np.int64)])
-            cnt = np.concatenate([cnt, np.ones(extra, dtype=np.int32)])
-            arrays = arrays + [arrays[-1]] * extra
-            n_entries = pad_to
         # one native call lays out positions, entry of each token, cu_q, kv_len, slots, block tables
         n_tokens = self.table.fill_step(ids, cnt, m.np, m.off["positions"], m.off["tok_entry"],
                                         m.off["cu_q"], m.off["kv_len"], m.off["slots"], m.bt_off_arr,
@@ -324,24 +316,30 @@ class ModelRunner:
                 key = shape
                 singles = shape[4]
         m.view("tokens", n_tokens, False)[:] = arrays[0] if len(arrays) == 1 else np.concatenate(arrays)
-        if key is not None and key[1] > n_tokens:
-            m.view("tokens", key[1], False)[n_tokens:] = 0
-            m.view("positions", key[1], False)[n_tokens:] = 0
-            m.view("tok_entry", key[1], False)[n_tokens:] = -1
-            n_tokens = key[1]
+        # A decode step is filled up to its bucket, a small step with prompt portions to its shape, with
+        # rows that belong to no entry (they write nothing into a cache) and entries without rows (no
+        # attention kernel has work for them): the padding costs the products' rows and nothing else.
+        # (Copies of a real entry, as decode steps were once padded with, read that entry's keys again:
+        # 40 requests in a bucket of 64 took the time of 64.)
+        pad_rows = pad_to if pad_to else (key[1] if key is not None else 0)
+        pad_entries = pad_to if pad_to else (key[2] if key is not None else 0)
+        if pad_rows > n_tokens:
+            m.view("tokens", pad_rows, False)[n_tokens:] = 0
+            m.view("positions", pad_rows, False)[n_tokens:] = 0
+            m.view("tok_entry", pad_rows, False)[n_tokens:] = -1
+            n_tokens = pad_rows
         cu = m.view("cu_q", n_entries + 1, False)
         kvl = m.view("kv_len", n_entries, False)
         slots = m.view("slots", n_entries, False)
-        if key is not None and key[2] > n_entries:
-            # entries without tokens and without a cache fill the shape up: no kernel has work for them
+        if pad_entries > n_entries:
             last = int(cu[n_entries])
-            cu = m.view("cu_q", key[2] + 1, False)
-            kvl = m.view("kv_len", key[2], False)
-            slots = m.view("slots", key[2], False)
+            cu = m.view("cu_q", pad_entries + 1, False)
+            kvl = m.view("kv_len", pad_entries, False)
+            slots = m.view("slots", pad_entries, False)
             cu[n_entries + 1:] = last
             kvl[n_entries:] = 0
             slots[n_entries:] = 0
-            n_entries = key[2]
+            n_entries = pad_entries
         if pad_to:
             n_want = pad_to
             rows_of = m.view("want_rows", n_want, False)
@@ -409,11 +407,18 @@ class ModelRunner:
     # ---- captured decode steps -----------------------------------------
     def _bucket(self, n: int) -> int:
         """The batch size a decode step of ``n`` entries is padded to: the next power
-        of two, or the most entries a step can have where that is less (a limit
-        of 96 requests has the buckets 1, 2, ..., 64, 96)."""
+        of two up to 16, finer steps above, or the most entries a step can have
+        where that is less."""
         b = 1
         while b < n:
             b *= 2
+        if b > 16:
+            # above 16 in steps of a sixteenth of the power of two (20, 24, 28, 32, 36, 40, ..., 64, 72, 80,
+            # ...): the attention's number of key slices is chosen for the bucket, and what suits 64
+            # requests suits neither 36 nor 40 (measured at 4 kv heads and a context of 8,192: 36
+            # requests 5.94 ms per step with one slice, 4.76 ms with two; 40 requests 5.90 and 6.55 ms)
+            step = max(4, b // 16)
+            b = -(-n // step) * step
         return min(b, self.cap_entries)
 
     MAX_SHAPE_GRAPHS = 256      # graphs of small steps kept; the least recently used one goes first

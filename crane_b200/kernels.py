@@ -409,6 +409,12 @@ class Kernels:
             # (one request at a context of 256 / 1,024: 1.366 -> 1.284 / 1.380 -> 1.313 ms per step; four
             # requests: 1.440 -> 1.329 / 1.434 -> 1.387 ms; at 4,096 keys more slices win again)
             return 8
+        while splits < 8 and splits & (splits - 1) and ctas * splits > 0.85 * slots:
+            # 2 to 8 slices are a thread-block cluster, which has to find its places in one GPC: clusters
+            # of 3 (5, 6, 7) that would take nearly every place do not all fit at once (24 requests of 4
+            # kv heads at a context of 8,192: 288 CTAs in clusters of 3 4.74 ms per step, 192 in clusters
+            # of 2 3.57 ms; 20 requests: 240 CTAs in clusters of 3 3.09 ms, 160 in clusters of 2 3.60 ms)
+            splits -= 1
         if 8 < splits <= 11:
             return 8
         if 32 < splits <= 40:

@@ -116,8 +116,8 @@ class Part:
     # replay graphs at all.  Its forward then reads the step's metadata on the device only (a graph
     # runs without the host), leaves rows whose ``tok_entry`` is -1 alone, and for an entry without
     # rows (``cu_q[e + 1] == cu_q[e]``, a padding entry) touches no slot, whatever ``slots[e]`` says.
-    # Steps of single tokens are then padded with such rows and entries, never with copies of an
-    # entry (a copy would advance its request's state twice).
+    # Steps are only ever padded with such rows and entries, never with copies of an entry (a copy
+    # would advance its request's state twice).
     state_graph_safe = False
 
     def __init__(self, spec: PartSpec):

@@ -20,6 +20,8 @@ def test_decode_splits_fill_the_device_and_fit_the_scratch(nkv):
             # finer so that the last round over the SMs is fuller): what the slices' scratch is sized for
             assert entries * nkv * s <= 2 * SMS or s <= 4
         assert not 8 < s <= 11 and not 32 < s <= 40      # ranges that measured slower than 8 / 32
+        # clusters of 3, 5, 6 or 7 slices only where they leave places free (they must fit into a GPC each)
+        assert s >= 8 or s in (1, 2, 4) or entries * nkv * s <= 0.85 * 2 * SMS
     assert Kernels.decode_splits(8, 4, SMS) == 8           # the headline shape: one cluster per (request, kv head)
     assert Kernels.decode_splits(1, 4, SMS) == 64
     assert Kernels.decode_splits(64, 4, SMS) == 1
