@@ -34,6 +34,8 @@ from ..weights.safetensors_io import DictSource
 # ``Kernels.decode_splits``).
 SHORT_CONTEXT = 2048
 SHORT_GRAPH_KEY = 1 << 20
+# A step whose every entry has at most this many keys in all (whole short prompts).
+SHORT_PROMPT = 64
 
 
 @dataclass
@@ -77,7 +79,8 @@ class StepContext:
                                         # the wanted rows beyond ``real_want`` repeat row 0
     real_want: int = 0
     replay: bool = False        # a step with a graph_key: replay its graph (else launch its kernels)
-    single_entries: int = 0     # > 0: a step with prompt portions whose entries of exactly one token
+    single_entries: int = 0
+    short_prompts: bool = False     # > 0: a step with prompt portions whose entries of exactly one token
                                 # (decoded tokens, about this many) are worth a kernel of their own:
                                 # an attention mixer may give them to its split-KV decode kernel and
                                 # the rest to its prefill kernel
@@ -291,6 +294,11 @@ class ModelRunner:
         # Decoded tokens beside prompt portions: when together they read enough cached keys, they are
         # worth the split-KV decode kernel (the prefill kernel would give each a whole query tile with
         # one live row and walk its context unsliced).
+        # Whole prompts of at most 64 tokens each (nothing cached before them): the warp-level flash
+        # attention, in tiles of 64 rows and several CTAs per SM, beats the tcgen05 kernel's 128-row
+        # tiles there (see the attention part); it is part of a small step's shape, since a graph holds
+        # the kernel it was recorded with.
+        short_prompts = int(m.view("kv_len", n_entries, False).max()) <= SHORT_PROMPT
         singles = 0
         if not pad_to and not self.rt.exact:
             one = cnt == 1
@@ -309,7 +317,8 @@ class ModelRunner:
             wanted = sum(len(e.want) for e in entries)
             shape = ("rows", rows, self._power_of_two(n_entries, self.cap_entries),
                      self._power_of_two(wanted, rows) if wanted else 0,
-                     self._power_of_two(singles, self.cap_entries) if singles else 0)
+                     self._power_of_two(singles, self.cap_entries) if singles else 0,
+                     1 if short_prompts else 0)
             seen = self._shape_seen.get(shape, 0) + 1
             self._shape_seen[shape] = seen
             if seen >= 2:
@@ -360,6 +369,7 @@ class ModelRunner:
         ctx.graph_bucket, ctx.real_entries = pad_to, real_entries
         ctx.graph_key = key
         ctx.single_entries = singles
+        ctx.short_prompts = short_prompts
         # While the device still runs the step before, the host launches this step's kernels
         # behind it at no cost, and launched one by one they ran a little faster than replayed
         # (a serving mix: 5 % per step): a graph pays when the device waits for the host.  The

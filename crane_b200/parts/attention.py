@@ -139,9 +139,14 @@ class GqaAttention(Part):
                           sin, self.q_norm, self.k_norm, self.eps, q, cache.k, cache.v,
                           cache.page_size, self.nq, self.nkv, self.d, self.own_kv,
                           self.position is not None, rt.err, rope=self.rope)
-        use_tc = (not rt.exact and rt.use_tc_attention
-                  and k.prefill_attention_tc_supports(self.d, self.nq, self.nkv, cache.page_size))
         use_mma = not rt.exact and k.prefill_attention_supports(self.d, self.nq, self.nkv)
+        # Whole prompts of at most 64 tokens take the warp-level kernel (64-row tiles, several CTAs per
+        # SM) also at head size 128.  Measured at 16 / 4 heads, tcgen05 against warp-level: 256 prompts of
+        # 8 tokens 244 / 144 us, 64 of 32: 44 / 28 us, 32 of 64: 22 / 19 us; 21 of 96: 22 / 23 us, 16 of 128:
+        # 16 / 21 us; 16 portions of 32 behind 2,000 cached keys 50 / 94 us.
+        short = bool(getattr(ctx, "short_prompts", False)) and use_mma
+        use_tc = (not rt.exact and rt.use_tc_attention and not short
+                  and k.prefill_attention_tc_supports(self.d, self.nq, self.nkv, cache.page_size))
         # Decoded tokens beside prompt portions: the entries of one token go to the split-KV decode
         # kernel (which skips the others), the prompt portions to the prefill kernel (which skips them).
         singles = getattr(ctx, "single_entries", 0) if (use_tc or use_mma) and not decode else 0
