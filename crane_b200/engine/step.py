@@ -79,11 +79,11 @@ class StepContext:
                                         # the wanted rows beyond ``real_want`` repeat row 0
     real_want: int = 0
     replay: bool = False        # a step with a graph_key: replay its graph (else launch its kernels)
-    single_entries: int = 0
-    short_prompts: bool = False     # > 0: a step with prompt portions whose entries of exactly one token
+    single_entries: int = 0     # > 0: a step with prompt portions whose entries of exactly one token
                                 # (decoded tokens, about this many) are worth a kernel of their own:
                                 # an attention mixer may give them to its split-KV decode kernel and
                                 # the rest to its prefill kernel
+    short_prompts: bool = False     # no entry has more than 64 keys in all (whole short prompts)
 
 
 class _MetaBuffers:
