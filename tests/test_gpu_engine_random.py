@@ -12,26 +12,29 @@ import tiny_configs
 pytestmark = pytest.mark.gpu
 
 
-def one_trial(seed, model_folders):
+def one_trial(seed, model_folders, many=False):
+    """``many``: up to 40 requests under a limit of up to 40 (decode buckets above 16, limits that are
+    no power of two), pages of 8 to 256 tokens, the layer sizes of a real model among the configurations."""
     from crane_b200.generation import ModelForCausalLM
     from crane_b200.sampling.sampler import SamplingParams
     rng = np.random.default_rng(seed)
-    name = str(rng.choice(["A", "B", "C"]))
+    name = str(rng.choice(["A", "B", "C", "S18", "S18"] if many else ["A", "B", "C"]))
     dt = str(rng.choice(["float32", "bfloat16"]))
     folder = model_folders(name, dt)
     pc, pw = ph.load_folder(folder)
-    ps = int(rng.choice([16, 32, 64]))
-    n_req = int(rng.integers(2, 9))
+    ps = int(rng.choice([8, 16, 32, 64, 128, 256] if many else [16, 32, 64]))
+    n_req = int(rng.integers(2, 41 if many else 9))
     longest = min(100, pc.max_position_embeddings - 45)
     prompts = [rng.integers(0, pc.vocab_size, int(rng.integers(1, longest))).tolist() for _ in range(n_req)]
-    new = [int(rng.integers(1, 40)) for _ in range(n_req)]
+    new = [int(rng.integers(1, 25 if many else 40)) for _ in range(n_req)]
     need = max(-(-(len(p) + n) // ps) for p, n in zip(prompts, new))       # pages of the largest request
     pages = int(need + rng.integers(0, 3 * need + 2))
-    opts = dict(page_size=ps, num_pages=pages, max_concurrent=int(rng.integers(1, 6)),
+    opts = dict(page_size=ps, num_pages=pages, max_concurrent=int(rng.integers(1, 41 if many else 6)),
                 max_batched_tokens=int(rng.choice([8, 16, 33, 64, 128])),
                 chunk_size=int(rng.choice([4, 8, 32, 64, 2048])),
                 use_cuda_graphs=bool(rng.random() < 0.7), async_scheduling=bool(rng.random() < 0.7),
                 mixed_decode_min_keys=int(rng.choice([0, 2048])))
+    opts["max_batched_tokens"] = max(opts["max_batched_tokens"], opts["max_concurrent"])
     label = f"seed {seed}: {name} {dt} {opts} prompts {[len(p) for p in prompts]} new {new}"
     m = ModelForCausalLM.from_pretrained(folder, dt, **opts)
     eng = m.engine
@@ -78,3 +81,8 @@ def one_trial(seed, model_folders):
 def test_random_settings_arrivals_cancellations_and_stop_tokens(model_folders):
     preemptions = sum(one_trial(1000 + i, model_folders) for i in range(24))
     assert preemptions > 0            # some of the pools were small enough to run out
+
+
+def test_many_requests_under_limits_that_are_no_power_of_two(model_folders):
+    for i in range(8):
+        one_trial(2000 + i, model_folders, many=True)
