@@ -1032,8 +1032,8 @@ def _dense_attention(qs, ks, vs, lens, q_lens, nq, nkv, d, window):
 def test_attention_kernels_at_random_shapes(K, err):
     """The split-KV decode kernel, the warp-level and the tcgen05 prefill kernel
     at shapes drawn at random: up to 8 entries of 1 to 4,200 keys, portions that
-    end on, before and after the edges of the 64- and 128-row tiles, pages of 16
-    to 256, odd group sizes, windows, 1 to 64 key slices."""
+    end on, before and after the edges of the 64- and 128-row tiles, pages of 8
+    to 512, odd group sizes, windows, 1 to 64 key slices."""
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
     worst = 0.0
     for i in range(72):
@@ -1043,7 +1043,7 @@ def test_attention_kernels_at_random_shapes(K, err):
         d = 128 if kind == "tc" else int(rng.choice([64, 128, 128, 80, 256, 16, 48]))
         nkv = int(rng.choice([1, 2, 4, 5]))
         nq = nkv * int(rng.choice([1, 2, 4, 7, 8]))
-        ps = int(rng.choice([16, 32, 64, 128, 256]))
+        ps = int(rng.choice([8, 16, 32, 64, 128, 256, 512]))
         n_req = int(rng.integers(1, 9))
         lens = [int(rng.integers(1, 4200)) if rng.random() < 0.6 else int(rng.integers(1, 140)) for _ in range(n_req)]
         q_lens = [1] * n_req if kind == "decode" else \
